@@ -1,0 +1,296 @@
+// Paged GQA decode: 32 query heads, 8 KV heads, head_dim 128, bf16.
+//
+// HBM-bound: every KV token costs 4096 bytes (8 heads x 128 x bf16 for K and again for V) and
+// only 4 query rows reuse it. One CTA owns (sequence, KV split, half of the KV heads): its 4
+// warps each run flash-decoding for one KV head (the 4 query heads of that group padded to an
+// m16 tile of mma.sync) over a 3-stage cp.async ring of 16-token tiles. A token's four K heads
+// are 1 KB contiguous in the cache, so each gather touches 1 KB for K and 1 KB for V. Tiles are
+// stored per head as [token][128] with the 16-byte chunks XOR-swizzled by (token & 7) so that
+// ldmatrix is bank-conflict free. Partials (m, l, acc) go to the workspace in fp32 and a second
+// kernel merges them; with one split the CTA writes o and lse itself.
+#include "lse_merge.cuh"
+
+namespace {
+
+constexpr int HQ = 32, HKV = 8, D = 128, GROUP = HQ / HKV;
+constexpr int HPC = 4;        // KV heads per CTA (one per warp)
+constexpr int TILE = 16;      // tokens per pipeline stage
+constexpr int STAGES = 3;
+constexpr int THREADS = HPC * 32;
+constexpr int TILE_ELEMS = HPC * TILE * D;                       // per K or V tile
+constexpr int STAGE_BYTES = 2 * TILE_ELEMS * 2;                  // K + V, bf16
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES;                 // 96 KB
+constexpr int MAX_SPLITS = 64;
+
+struct Params {
+  const __nv_bfloat16* q;
+  const __nv_bfloat16* k;
+  const __nv_bfloat16* v;
+  const int32_t* indptr;
+  const int32_t* indices;
+  __nv_bfloat16* o;
+  float* lse;
+  float* part_acc;  // [batch*32][splits][128]
+  float* part_ml;   // [batch*32][splits][2]
+  float scale_log2;
+  int page_size;
+  int num_splits;
+};
+
+// Issues the cp.async copies of one 16-token tile (K and V, HPC heads) into `stage`.
+__device__ __forceinline__ void load_tile(const Params& p, __nv_bfloat16* stage, int64_t idx_base,
+                                          int tok0, int tok_end, int head0) {
+  const int tid = threadIdx.x;
+  // 64 chunks of 16 B per token per tensor (4 heads x 256 B); 128 threads cover 2 tokens a pass.
+  const int c = tid & 63;
+  const int h = c >> 4, chunk = c & 15;
+#pragma unroll
+  for (int pass = 0; pass < TILE / 2; ++pass) {
+    const int i = pass * 2 + (tid >> 6);
+    const int tok = tok0 + i;
+    const bool valid = tok < tok_end;
+    int64_t row = 0;
+    if (valid) {
+      if (p.page_size == 1) {
+        row = __ldg(p.indices + idx_base + tok);
+      } else {
+        const int pg = tok / p.page_size;
+        row = (int64_t)__ldg(p.indices + idx_base + pg) * p.page_size + (tok - pg * p.page_size);
+      }
+    }
+    const int64_t src = row * (HKV * D) + (int64_t)(head0 + h) * D + chunk * 8;
+    const int dst = (h * TILE + i) * D + ((chunk ^ (i & 7)) << 3);
+    ako::cp_async16(ako::smem_u32(stage + dst), p.k + src, valid);
+    ako::cp_async16(ako::smem_u32(stage + TILE_ELEMS + dst), p.v + src, valid);
+  }
+}
+
+__global__ void __launch_bounds__(THREADS, 2) gqa_decode_kernel(Params p) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  __nv_bfloat16* smem = reinterpret_cast<__nv_bfloat16*>(smem_raw);
+
+  const int split = blockIdx.x % p.num_splits;
+  const int half = (blockIdx.x / p.num_splits) & 1;
+  const int b = blockIdx.x / (p.num_splits * 2);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int head0 = half * HPC;
+  const int kvh = head0 + warp;
+
+  ako::pdl_trigger();  // the merge kernel may be scheduled early; it waits for this grid to finish
+  const int64_t idx_base = p.indptr[b];
+  const int len = (int)(p.indptr[b + 1] - idx_base) * p.page_size;
+  int chunk = (int)ako::round_up(ako::cdiv(len, p.num_splits), TILE);
+  if (chunk < TILE) chunk = TILE;
+  const int tok_begin = min(len, split * chunk);
+  const int tok_end = min(len, tok_begin + chunk);
+  const int ntiles = (tok_end - tok_begin + TILE - 1) / TILE;
+
+  // Q fragments of this warp's group (rows g<4 real, others zero).
+  uint32_t qa[8][2];
+  {
+    const __nv_bfloat16* qrow = p.q + ((int64_t)b * HQ + kvh * GROUP + (g & 3)) * D;
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) {
+      uint32_t v0 = *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 2 * t);
+      uint32_t v1 = *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 8 + 2 * t);
+      qa[ks][0] = (g < GROUP) ? v0 : 0u;
+      qa[ks][1] = (g < GROUP) ? v1 : 0u;
+    }
+  }
+
+  float oacc[16][4];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) oacc[i][0] = oacc[i][1] = oacc[i][2] = oacc[i][3] = 0.f;
+  float m_run = -INFINITY, l_run = 0.f;
+
+#pragma unroll
+  for (int s = 0; s < STAGES - 1; ++s) {
+    if (s < ntiles) load_tile(p, smem + s * (STAGE_BYTES / 2), idx_base, tok_begin + s * TILE, tok_end, head0);
+    ako::cp_async_commit();
+  }
+
+  for (int it = 0; it < ntiles; ++it) {
+    ako::cp_async_wait<STAGES - 2>();
+    __syncthreads();
+    // prefetch tile it+STAGES-1 into the stage consumed at iteration it-1
+    {
+      const int nt = it + STAGES - 1;
+      if (nt < ntiles)
+        load_tile(p, smem + (nt % STAGES) * (STAGE_BYTES / 2), idx_base, tok_begin + nt * TILE, tok_end, head0);
+      ako::cp_async_commit();
+    }
+    const __nv_bfloat16* Ks = smem + (it % STAGES) * (STAGE_BYTES / 2) + warp * TILE * D;
+    const __nv_bfloat16* Vs = Ks + TILE_ELEMS;
+
+    // S = Q K^T : 2 n-tiles of 8 tokens
+    float sacc[2][4];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) sacc[i][0] = sacc[i][1] = sacc[i][2] = sacc[i][3] = 0.f;
+    {
+      const int tok = ((lane >> 4) << 3) + (lane & 7);
+      const int csel = (lane >> 3) & 1;
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) {
+        uint32_t b00, b01, b10, b11;
+        const int chunk_id = (2 * ks + csel) ^ (tok & 7);
+        ako::ldmatrix_x4(b00, b01, b10, b11, ako::smem_u32(Ks + tok * D + (chunk_id << 3)));
+        const uint32_t a[4] = {qa[ks][0], 0u, qa[ks][1], 0u};
+        ako::mma_bf16_16816(sacc[0], a, b00, b01);
+        ako::mma_bf16_16816(sacc[1], a, b10, b11);
+      }
+    }
+    // online softmax on row g (tokens: n-tile i, columns 2t, 2t+1)
+    const int tile_tok0 = tok_begin + it * TILE;
+    float mx = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int tk = tile_tok0 + i * 8 + 2 * t + j;
+        float s = sacc[i][j] * p.scale_log2;
+        s = (tk < tok_end) ? s : -INFINITY;
+        sacc[i][j] = s;
+        mx = fmaxf(mx, s);
+      }
+    }
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    const float m_new = fmaxf(m_run, mx);  // finite: every tile holds at least one valid token
+    const float corr = ako::fast_exp2(m_run - m_new);
+    float psum = 0.f;
+    uint32_t pa[4];
+    {
+      const float p00 = ako::fast_exp2(sacc[0][0] - m_new), p01 = ako::fast_exp2(sacc[0][1] - m_new);
+      const float p10 = ako::fast_exp2(sacc[1][0] - m_new), p11 = ako::fast_exp2(sacc[1][1] - m_new);
+      psum = (p00 + p01) + (p10 + p11);
+      pa[0] = ako::pack_bf16x2(p00, p01);
+      pa[1] = 0u;
+      pa[2] = ako::pack_bf16x2(p10, p11);
+      pa[3] = 0u;
+    }
+    psum += __shfl_xor_sync(0xffffffffu, psum, 1);
+    psum += __shfl_xor_sync(0xffffffffu, psum, 2);
+    l_run = l_run * corr + psum;
+    m_run = m_new;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      oacc[i][0] *= corr;
+      oacc[i][1] *= corr;
+    }
+    // O += P V : 16 n-tiles of 8 dims, k = 16 tokens
+    {
+      const int tok = (((lane >> 3) & 1) << 3) + (lane & 7);
+      const int csel = lane >> 4;
+#pragma unroll
+      for (int nd = 0; nd < 16; nd += 2) {
+        uint32_t v00, v01, v10, v11;
+        const int chunk_id = (nd + csel) ^ (tok & 7);
+        ako::ldmatrix_x4_trans(v00, v01, v10, v11, ako::smem_u32(Vs + tok * D + (chunk_id << 3)));
+        ako::mma_bf16_16816(oacc[nd], pa, v00, v01);
+        ako::mma_bf16_16816(oacc[nd + 1], pa, v10, v11);
+      }
+    }
+  }
+  ako::cp_async_wait<0>();
+
+  if (g < GROUP) {
+    const int64_t rh = (int64_t)b * HQ + kvh * GROUP + g;
+    if (p.num_splits == 1) {
+      const float inv = (l_run > 0.f) ? 1.f / l_run : 0.f;
+      __nv_bfloat16* op = p.o + rh * D;
+#pragma unroll
+      for (int nd = 0; nd < 16; ++nd)
+        *reinterpret_cast<uint32_t*>(op + nd * 8 + 2 * t) =
+            ako::pack_bf16x2(oacc[nd][0] * inv, oacc[nd][1] * inv);
+      if (t == 0) p.lse[rh] = (l_run > 0.f) ? m_run + log2f(l_run) : -INFINITY;
+    } else {
+      float* pa_out = p.part_acc + (rh * p.num_splits + split) * D;
+#pragma unroll
+      for (int nd = 0; nd < 16; ++nd)
+        *reinterpret_cast<float2*>(pa_out + nd * 8 + 2 * t) = make_float2(oacc[nd][0], oacc[nd][1]);
+      if (t == 0) {
+        float* ml = p.part_ml + (rh * p.num_splits + split) * 2;
+        ml[0] = m_run;
+        ml[1] = l_run;
+      }
+    }
+  }
+}
+
+int pick_splits(int64_t batch, int64_t num_kv_indices, int64_t page_size) {
+  if (batch <= 0) return 1;
+  const int64_t avg_len = num_kv_indices * page_size / batch;
+  int64_t want = ako::cdiv(1184, 2 * batch);          // ~4 resident waves of 148 SMs x 2 CTAs
+  int64_t cap = avg_len / 128;                         // keep chunks >= 128 tokens on average
+  if (cap < 1) cap = 1;
+  int64_t s = want < cap ? want : cap;
+  if (s < 1) s = 1;
+  if (s > MAX_SPLITS) s = MAX_SPLITS;
+  return (int)s;
+}
+
+}  // namespace
+
+extern "C" size_t ako4x_gqa_paged_decode_workspace_bytes(int64_t batch, int64_t num_kv_indices,
+                                                         int64_t page_size) {
+  const int s = pick_splits(batch, num_kv_indices, page_size);
+  if (s == 1) return 0;
+  return (size_t)batch * HQ * s * (D + 2) * sizeof(float);
+}
+
+extern "C" int ako4x_gqa_paged_decode(const void* q, const void* k_cache, const void* v_cache,
+                                      const int32_t* kv_indptr, const int32_t* kv_indices,
+                                      float sm_scale, void* o, float* lse, int64_t batch,
+                                      int64_t num_kv_indices, int64_t page_size, void* workspace,
+                                      size_t workspace_bytes, void* stream) {
+  if (batch < 0 || num_kv_indices < 0 || page_size < 1) return AKO4X_EINVAL;
+  if (batch == 0) return AKO4X_OK;
+  if (!q || !k_cache || !v_cache || !kv_indptr || !o || !lse) return AKO4X_EINVAL;
+  if (num_kv_indices > 0 && !kv_indices) return AKO4X_EINVAL;
+  if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)o) & 15) return AKO4X_EINVAL;
+  const int splits = pick_splits(batch, num_kv_indices, page_size);
+  const size_t need = ako4x_gqa_paged_decode_workspace_bytes(batch, num_kv_indices, page_size);
+  if (need > 0 && (!workspace || workspace_bytes < need)) return AKO4X_EWORKSPACE;
+  cudaStream_t st = (cudaStream_t)stream;
+
+  Params p;
+  p.q = (const __nv_bfloat16*)q;
+  p.k = (const __nv_bfloat16*)k_cache;
+  p.v = (const __nv_bfloat16*)v_cache;
+  p.indptr = kv_indptr;
+  p.indices = kv_indices;
+  p.o = (__nv_bfloat16*)o;
+  p.lse = lse;
+  p.part_acc = (float*)workspace;
+  p.part_ml = p.part_acc ? p.part_acc + (size_t)batch * HQ * splits * D : nullptr;
+  p.scale_log2 = sm_scale * AKO_LOG2E;
+  p.page_size = (int)page_size;
+  p.num_splits = splits;
+
+  if (!ako::ensure_dynamic_smem(gqa_decode_kernel, SMEM_BYTES)) return AKO4X_ELAUNCH;
+  const int64_t grid = batch * 2 * splits;
+  if (grid > 0x7fffffffLL) return AKO4X_EINVAL;
+  gqa_decode_kernel<<<(unsigned)grid, THREADS, SMEM_BYTES, st>>>(p);
+  AKO_CHECK_LAUNCH();
+  if (splits > 1) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(batch * HQ));
+    cfg.blockDim = dim3(D / 4);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const float* pacc = p.part_acc;
+    const float* pml = p.part_ml;
+    __nv_bfloat16* op = p.o;
+    float* lp = p.lse;
+    int ns = splits;
+    if (cudaLaunchKernelEx(&cfg, ako::lse_merge_kernel<D, 4>, pacc, pml, op, lp, ns) != cudaSuccess)
+      return AKO4X_ELAUNCH;
+  }
+  return AKO4X_OK;
+}

@@ -1,0 +1,503 @@
+// MLA attention core shared by paged MLA decode, DSA sparse attention and causal MLA prefill:
+// 16 heads, ckv dim 512 (keys and values), kpe dim 64, bf16, fp32 accumulation.
+//
+// A "row" is one query token (16 heads = one m16 tile of mma.sync). Its keys are a list of cache
+// rows: the paged KV list of its sequence (decode), its sparse index list with -1 holes (DSA), or
+// the causally visible prefix of its sequence's KV list (prefill). One CTA of 8 warps owns
+// (row, KV split) and streams 64-token tiles (72 KB: 1024 B ckv + 128 B kpe per token) through a
+// 2-stage cp.async ring; the gather indices of tile i+2 travel in the same cp.async group as the
+// data of tile i+1, so no index load sits in front of a data load.
+//   S phase : warp w computes logits of tokens 16*(w&3).. over one half of the 576-wide
+//             reduction (w>>2) with its Q fragments held in registers; halves meet in shared memory.
+//   PV phase: every warp rebuilds P (softmax is recomputed per warp, which removes two barriers)
+//             and accumulates its own 64 of the 512 output columns.
+// Each token costs 1152 bytes of HBM traffic and 34816 flop, so the kernel is gather-bandwidth
+// bound; shared-memory traffic per token (about 4.4 KB) is the second limit.
+#include "lse_merge.cuh"
+
+namespace {
+
+constexpr int H = 16, DC = 512, DP = 64;
+constexpr int TILE = 64;
+constexpr int THREADS = 256;
+constexpr int CKV_TILE_ELEMS = TILE * DC;
+constexpr int KPE_TILE_ELEMS = TILE * DP;
+constexpr int STAGE_ELEMS = CKV_TILE_ELEMS + KPE_TILE_ELEMS;
+constexpr int STAGES = 2;
+constexpr int SROW = 72;  // padded fp32 row stride of the logit exchange buffer
+constexpr int SBUF_FLOATS = 2 * H * SROW;
+constexpr int IDX_RING = 3;
+constexpr int SMEM_BYTES = STAGES * STAGE_ELEMS * 2 + SBUF_FLOATS * 4 + IDX_RING * TILE * 4;
+constexpr int MAX_SPLITS = 64;
+
+enum Mode { kDecode = 0, kSparse = 1, kPrefill = 2 };
+
+struct Params {
+  const __nv_bfloat16* q_nope;
+  const __nv_bfloat16* q_pe;
+  const __nv_bfloat16* ckv;
+  const __nv_bfloat16* kpe;
+  const int32_t* qo_indptr;   // prefill only
+  const int32_t* kv_indptr;   // decode / prefill
+  const int32_t* indices;     // kv_indices or sparse_indices
+  __nv_bfloat16* o;
+  float* lse;
+  float* part_acc;            // [rows*16][splits][512]
+  float* part_ml;             // [rows*16][splits][2]
+  float scale_log2;
+  int page_size;
+  int num_splits;
+  int topk;                   // sparse only
+  int batch;                  // prefill only (number of sequences)
+};
+
+struct RowDesc {
+  const int32_t* idx;  // index list of the row
+  int count;           // number of key positions (holes included)
+};
+
+template <int MODE>
+__device__ __forceinline__ RowDesc describe_row(const Params& p, int64_t row) {
+  RowDesc d;
+  if (MODE == kDecode) {
+    const int s = p.kv_indptr[row], e = p.kv_indptr[row + 1];
+    d.idx = p.indices + s;
+    d.count = max(0, e - s) * p.page_size;
+  } else if (MODE == kSparse) {
+    d.idx = p.indices + row * p.topk;
+    d.count = p.topk;
+  } else {
+    // binary search: largest b with qo_indptr[b] <= row
+    int lo = 0, hi = p.batch;
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (p.qo_indptr[mid] <= row) lo = mid; else hi = mid;
+    }
+    const int qs = p.qo_indptr[lo], qe = p.qo_indptr[lo + 1];
+    const int ks = p.kv_indptr[lo], ke = p.kv_indptr[lo + 1];
+    const int kv_len = max(0, ke - ks) * p.page_size;
+    const int q_len = qe - qs;
+    const int visible = (kv_len - q_len) + (int)(row - qs) + 1;
+    d.idx = p.indices + ks;
+    d.count = min(kv_len, max(0, visible));
+  }
+  return d;
+}
+
+// cp.async of the gather indices of tile `tile` (positions tok0..tok0+63) into ring slot `slot`.
+// Entries past the end become -1.
+__device__ __forceinline__ void load_indices_async(const Params& p, const RowDesc& rd, int32_t* ring,
+                                                   int slot, int tok0, int tok_end) {
+  if (threadIdx.x < TILE) {
+    const int tok = tok0 + threadIdx.x;
+    const bool valid = tok < tok_end;
+    const int32_t* src = rd.idx + (valid ? (p.page_size == 1 ? tok : tok / p.page_size) : 0);
+    const uint32_t dst = ako::smem_u32(ring + slot * TILE + threadIdx.x);
+    const int sz = valid ? 4 : 0;
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;\n" ::"r"(dst), "l"(src), "r"(sz));
+  }
+}
+
+// cp.async of one 64-token tile. Ring entries: page id (or cache row), 0 after zero-fill means
+// "past the end" only when the position test says so; negative entries are holes.
+__device__ __forceinline__ void load_tile(const Params& p, __nv_bfloat16* stage, const int32_t* ring_slot,
+                                          int tok0, int tok_end) {
+  const int tid = threadIdx.x;
+  {
+    const int chunk = tid & 63;
+#pragma unroll
+    for (int pass = 0; pass < TILE / 4; ++pass) {
+      const int i = pass * 4 + (tid >> 6);
+      const int tok = tok0 + i;
+      const int32_t e = ring_slot[i];
+      const bool valid = (tok < tok_end) && (e >= 0);
+      int64_t row = 0;
+      if (valid) row = (p.page_size == 1) ? (int64_t)e : (int64_t)e * p.page_size + (tok % p.page_size);
+      const int dst = i * DC + ((chunk ^ (i & 7)) << 3);
+      ako::cp_async16(ako::smem_u32(stage + dst), p.ckv + row * DC + chunk * 8, valid);
+    }
+  }
+  {
+    const int chunk = tid & 7;
+#pragma unroll
+    for (int pass = 0; pass < 2; ++pass) {
+      const int i = pass * 32 + (tid >> 3);
+      const int tok = tok0 + i;
+      const int32_t e = ring_slot[i];
+      const bool valid = (tok < tok_end) && (e >= 0);
+      int64_t row = 0;
+      if (valid) row = (p.page_size == 1) ? (int64_t)e : (int64_t)e * p.page_size + (tok % p.page_size);
+      const int dst = CKV_TILE_ELEMS + i * DP + ((chunk ^ (i & 7)) << 3);
+      ako::cp_async16(ako::smem_u32(stage + dst), p.kpe + row * DP + chunk * 8, valid);
+    }
+  }
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(THREADS, 1) mla_attention_kernel(Params p) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  __nv_bfloat16* tiles = reinterpret_cast<__nv_bfloat16*>(smem_raw);
+  float* sbuf = reinterpret_cast<float*>(smem_raw + STAGES * STAGE_ELEMS * 2);
+  int32_t* ring = reinterpret_cast<int32_t*>(sbuf + SBUF_FLOATS);
+
+  const int split = blockIdx.x % p.num_splits;
+  const int64_t row = blockIdx.x / p.num_splits;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int pw = warp & 3;   // token group of the S phase
+  const int kh = warp >> 2;  // reduction half of the S phase
+
+  ako::pdl_trigger();
+  const RowDesc rd = describe_row<MODE>(p, row);
+  int chunk = (int)ako::round_up(ako::cdiv(rd.count, p.num_splits), TILE);
+  if (chunk < TILE) chunk = TILE;
+  const int tok_begin = min(rd.count, split * chunk);
+  const int tok_end = min(rd.count, tok_begin + chunk);
+  const int ntiles = (tok_end - tok_begin + TILE - 1) / TILE;
+
+  // Q fragments of this warp's reduction half: 18 k-steps of 16.
+  uint32_t qa[18][4];
+  {
+    const __nv_bfloat16* qn0 = p.q_nope + (row * H + g) * DC;
+    const __nv_bfloat16* qn1 = qn0 + 8 * DC;
+    const __nv_bfloat16* qp0 = p.q_pe + (row * H + g) * DP;
+    const __nv_bfloat16* qp1 = qp0 + 8 * DP;
+#pragma unroll
+    for (int ks = 0; ks < 18; ++ks) {
+      const __nv_bfloat16 *r0, *r1;
+      int k0;
+      if (kh == 0) { r0 = qn0; r1 = qn1; k0 = ks * 16; }
+      else if (ks < 14) { r0 = qn0; r1 = qn1; k0 = 288 + ks * 16; }
+      else { r0 = qp0; r1 = qp1; k0 = (ks - 14) * 16; }
+      qa[ks][0] = *reinterpret_cast<const uint32_t*>(r0 + k0 + 2 * t);
+      qa[ks][1] = *reinterpret_cast<const uint32_t*>(r1 + k0 + 2 * t);
+      qa[ks][2] = *reinterpret_cast<const uint32_t*>(r0 + k0 + 8 + 2 * t);
+      qa[ks][3] = *reinterpret_cast<const uint32_t*>(r1 + k0 + 8 + 2 * t);
+    }
+  }
+
+  float oacc[8][4];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) oacc[i][0] = oacc[i][1] = oacc[i][2] = oacc[i][3] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+
+  if (ntiles > 0) {
+    // prologue: indices of tile 0 (synchronous), then data of tile 0 + indices of tile 1 (async)
+    if (threadIdx.x < TILE) {
+      const int tok = tok_begin + threadIdx.x;
+      int32_t e = -1;
+      if (tok < tok_end) e = rd.idx[p.page_size == 1 ? tok : tok / p.page_size];
+      ring[threadIdx.x] = e;
+    }
+    __syncthreads();
+    load_tile(p, tiles, ring, tok_begin, tok_end);
+    if (ntiles > 1) load_indices_async(p, rd, ring, 1, tok_begin + TILE, tok_end);
+    ako::cp_async_commit();
+  }
+
+  for (int it = 0; it < ntiles; ++it) {
+    ako::cp_async_wait<0>();
+    __syncthreads();
+    if (it + 1 < ntiles) {
+      load_tile(p, tiles + ((it + 1) & 1) * STAGE_ELEMS, ring + ((it + 1) % IDX_RING) * TILE,
+                tok_begin + (it + 1) * TILE, tok_end);
+      if (it + 2 < ntiles)
+        load_indices_async(p, rd, ring, (it + 2) % IDX_RING, tok_begin + (it + 2) * TILE, tok_end);
+    }
+    ako::cp_async_commit();
+
+    const __nv_bfloat16* Cs = tiles + (it & 1) * STAGE_ELEMS;
+    const __nv_bfloat16* Ps = Cs + CKV_TILE_ELEMS;
+    const int32_t* ring_cur = ring + (it % IDX_RING) * TILE;
+    const int tile_tok0 = tok_begin + it * TILE;
+
+    // ---- S phase: 16 tokens x half of the reduction --------------------------------------
+    {
+      float sacc[2][4];
+#pragma unroll
+      for (int i = 0; i < 2; ++i) sacc[i][0] = sacc[i][1] = sacc[i][2] = sacc[i][3] = 0.f;
+      const int tok = 16 * pw + ((lane >> 4) << 3) + (lane & 7);
+      const int csel = (lane >> 3) & 1;
+      const int sw = tok & 7;
+#pragma unroll
+      for (int ks = 0; ks < 18; ++ks) {
+        uint32_t b00, b01, b10, b11;
+        uint32_t addr;
+        if (kh == 0 || ks < 14) {
+          const int c = (kh == 0 ? 0 : 36) + 2 * ks + csel;  // 16-byte chunk of the 512-wide row
+          addr = ako::smem_u32(Cs + tok * DC + ((c ^ sw) << 3));
+        } else {
+          const int c = 2 * (ks - 14) + csel;
+          addr = ako::smem_u32(Ps + tok * DP + ((c ^ sw) << 3));
+        }
+        ako::ldmatrix_x4(b00, b01, b10, b11, addr);
+        ako::mma_bf16_16816(sacc[0], qa[ks], b00, b01);
+        ako::mma_bf16_16816(sacc[1], qa[ks], b10, b11);
+      }
+      float* sb = sbuf + kh * H * SROW;
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt) {
+        const int c0 = 16 * pw + 8 * nt + 2 * t;
+        float v0 = sacc[nt][0], v1 = sacc[nt][1], v2 = sacc[nt][2], v3 = sacc[nt][3];
+        if (kh == 0) {  // the first half carries the validity mask
+          const bool ok0 = (tile_tok0 + c0 < tok_end) && (ring_cur[c0] >= 0);
+          const bool ok1 = (tile_tok0 + c0 + 1 < tok_end) && (ring_cur[c0 + 1] >= 0);
+          if (!ok0) { v0 = -INFINITY; v2 = -INFINITY; }
+          if (!ok1) { v1 = -INFINITY; v3 = -INFINITY; }
+        }
+        *reinterpret_cast<float2*>(sb + g * SROW + c0) = make_float2(v0, v1);
+        *reinterpret_cast<float2*>(sb + (g + 8) * SROW + c0) = make_float2(v2, v3);
+      }
+    }
+    __syncthreads();
+
+    // ---- softmax (per warp, rows g and g+8 over the 64 tokens) ----------------------------
+    float sv[2][16];
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const float* s0 = sbuf + (g + 8 * r) * SROW + 2 * t;
+      const float* s1 = s0 + H * SROW;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float2 a = *reinterpret_cast<const float2*>(s0 + 8 * i);
+        const float2 b = *reinterpret_cast<const float2*>(s1 + 8 * i);
+        const float x0 = (a.x + b.x) * p.scale_log2, x1 = (a.y + b.y) * p.scale_log2;
+        sv[r][2 * i] = x0;
+        sv[r][2 * i + 1] = x1;
+        mx[r] = fmaxf(mx[r], fmaxf(x0, x1));
+      }
+      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+    }
+    uint32_t pa[4][4];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const float m_new = fmaxf(m_run[r], mx[r]);
+      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+      const float corr = ako::fast_exp2(m_run[r] - m_use);
+      float psum = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float p0 = ako::fast_exp2(sv[r][2 * i] - m_use);
+        const float p1 = ako::fast_exp2(sv[r][2 * i + 1] - m_use);
+        psum += p0 + p1;
+        // tokens 8i+2t, 8i+2t+1 -> k-step i/2, low (i even) or high (i odd) half
+        pa[i >> 1][(i & 1) * 2 + r] = ako::pack_bf16x2(p0, p1);
+      }
+      psum += __shfl_xor_sync(0xffffffffu, psum, 1);
+      psum += __shfl_xor_sync(0xffffffffu, psum, 2);
+      l_run[r] = l_run[r] * corr + psum;
+      m_run[r] = m_new;
+#pragma unroll
+      for (int nd = 0; nd < 8; ++nd) {
+        oacc[nd][2 * r] *= corr;
+        oacc[nd][2 * r + 1] *= corr;
+      }
+    }
+
+    // ---- PV phase: this warp's 64 output columns ---------------------------------------------
+    {
+      const int trow = (((lane >> 3) & 1) << 3) + (lane & 7);
+      const int csel = lane >> 4;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int tok = 16 * j + trow;
+        const int sw = tok & 7;
+#pragma unroll
+        for (int nd = 0; nd < 8; nd += 2) {
+          uint32_t v00, v01, v10, v11;
+          const int c = 8 * warp + nd + csel;
+          ako::ldmatrix_x4_trans(v00, v01, v10, v11, ako::smem_u32(Cs + tok * DC + ((c ^ sw) << 3)));
+          ako::mma_bf16_16816(oacc[nd], pa[j], v00, v01);
+          ako::mma_bf16_16816(oacc[nd + 1], pa[j], v10, v11);
+        }
+      }
+    }
+  }
+  ako::cp_async_wait<0>();
+
+  // ---- epilogue ---------------------------------------------------------------------------------
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int64_t rh = row * H + g + 8 * r;
+    if (p.num_splits == 1) {
+      const float inv = (l_run[r] > 0.f) ? 1.f / l_run[r] : 0.f;
+      __nv_bfloat16* op = p.o + rh * DC + 64 * warp + 2 * t;
+#pragma unroll
+      for (int nd = 0; nd < 8; ++nd)
+        *reinterpret_cast<uint32_t*>(op + nd * 8) =
+            ako::pack_bf16x2(oacc[nd][2 * r] * inv, oacc[nd][2 * r + 1] * inv);
+      if (warp == 0 && t == 0)
+        p.lse[rh] = (l_run[r] > 0.f) ? m_run[r] + log2f(l_run[r]) : -INFINITY;
+    } else {
+      float* pa_out = p.part_acc + (rh * p.num_splits + split) * DC + 64 * warp + 2 * t;
+#pragma unroll
+      for (int nd = 0; nd < 8; ++nd)
+        *reinterpret_cast<float2*>(pa_out + nd * 8) = make_float2(oacc[nd][2 * r], oacc[nd][2 * r + 1]);
+      if (warp == 0 && t == 0) {
+        float* ml = p.part_ml + (rh * p.num_splits + split) * 2;
+        ml[0] = m_run[r];
+        ml[1] = l_run[r];
+      }
+    }
+  }
+}
+
+int pick_splits(int64_t rows, int64_t avg_keys) {
+  if (rows <= 0) return 1;
+  int64_t want = ako::cdiv(592, rows);       // ~4 waves of 148 single-CTA SMs
+  int64_t cap = avg_keys / 128;               // at least two tiles per CTA on average
+  if (cap < 1) cap = 1;
+  int64_t s = want < cap ? want : cap;
+  if (s < 1) s = 1;
+  if (s > MAX_SPLITS) s = MAX_SPLITS;
+  return (int)s;
+}
+
+size_t workspace_for(int64_t rows, int splits) {
+  if (splits == 1) return 0;
+  return (size_t)rows * H * splits * (DC + 2) * sizeof(float);
+}
+
+template <int MODE>
+int launch(Params& p, int64_t rows, int splits, void* workspace, cudaStream_t st) {
+  p.num_splits = splits;
+  p.part_acc = (float*)workspace;
+  p.part_ml = workspace ? p.part_acc + (size_t)rows * H * splits * DC : nullptr;
+  if (!ako::ensure_dynamic_smem(mla_attention_kernel<MODE>, SMEM_BYTES)) return AKO4X_ELAUNCH;
+  const int64_t grid = rows * splits;
+  if (grid > 0x7fffffffLL) return AKO4X_EINVAL;
+  mla_attention_kernel<MODE><<<(unsigned)grid, THREADS, SMEM_BYTES, st>>>(p);
+  AKO_CHECK_LAUNCH();
+  if (splits > 1) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(rows * H));
+    cfg.blockDim = dim3(DC / 4);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const float* pacc = p.part_acc;
+    const float* pml = p.part_ml;
+    __nv_bfloat16* op = p.o;
+    float* lp = p.lse;
+    int ns = splits;
+    if (cudaLaunchKernelEx(&cfg, ako::lse_merge_kernel<DC, 4>, pacc, pml, op, lp, ns) != cudaSuccess)
+      return AKO4X_ELAUNCH;
+  }
+  return AKO4X_OK;
+}
+
+bool misaligned(const void* a, const void* b, const void* c, const void* d, const void* e) {
+  return (((uintptr_t)a | (uintptr_t)b | (uintptr_t)c | (uintptr_t)d | (uintptr_t)e) & 15) != 0;
+}
+
+}  // namespace
+
+// ---- paged MLA decode ----------------------------------------------------------------------------
+extern "C" size_t ako4x_mla_paged_decode_workspace_bytes(int64_t batch, int64_t num_kv_indices,
+                                                         int64_t page_size) {
+  if (batch <= 0) return 0;
+  return workspace_for(batch, pick_splits(batch, num_kv_indices * page_size / batch));
+}
+
+extern "C" int ako4x_mla_paged_decode(const void* q_nope, const void* q_pe, const void* ckv_cache,
+                                      const void* kpe_cache, const int32_t* kv_indptr,
+                                      const int32_t* kv_indices, float sm_scale, void* o, float* lse,
+                                      int64_t batch, int64_t num_kv_indices, int64_t page_size,
+                                      void* workspace, size_t workspace_bytes, void* stream) {
+  if (batch < 0 || num_kv_indices < 0 || page_size < 1) return AKO4X_EINVAL;
+  if (batch == 0) return AKO4X_OK;
+  if (!q_nope || !q_pe || !ckv_cache || !kpe_cache || !kv_indptr || !o || !lse) return AKO4X_EINVAL;
+  if (num_kv_indices > 0 && !kv_indices) return AKO4X_EINVAL;
+  if (misaligned(q_nope, q_pe, ckv_cache, kpe_cache, o)) return AKO4X_EINVAL;
+  const int splits = pick_splits(batch, num_kv_indices * page_size / batch);
+  const size_t need = workspace_for(batch, splits);
+  if (need > 0 && (!workspace || workspace_bytes < need)) return AKO4X_EWORKSPACE;
+  Params p = {};
+  p.q_nope = (const __nv_bfloat16*)q_nope;
+  p.q_pe = (const __nv_bfloat16*)q_pe;
+  p.ckv = (const __nv_bfloat16*)ckv_cache;
+  p.kpe = (const __nv_bfloat16*)kpe_cache;
+  p.kv_indptr = kv_indptr;
+  p.indices = kv_indices;
+  p.o = (__nv_bfloat16*)o;
+  p.lse = lse;
+  p.scale_log2 = sm_scale * AKO_LOG2E;
+  p.page_size = (int)page_size;
+  return launch<kDecode>(p, batch, splits, workspace, (cudaStream_t)stream);
+}
+
+// ---- DSA sparse attention ------------------------------------------------------------------------
+extern "C" size_t ako4x_dsa_sparse_attention_workspace_bytes(int64_t tokens, int64_t topk) {
+  if (tokens <= 0) return 0;
+  return workspace_for(tokens, pick_splits(tokens, topk));
+}
+
+extern "C" int ako4x_dsa_sparse_attention(const void* q_nope, const void* q_pe, const void* ckv_cache,
+                                          const void* kpe_cache, const int32_t* sparse_indices,
+                                          float sm_scale, void* o, float* lse, int64_t tokens,
+                                          int64_t topk, int64_t num_cache_rows, void* workspace,
+                                          size_t workspace_bytes, void* stream) {
+  (void)num_cache_rows;
+  if (tokens < 0 || topk < 0 || topk > 0x7fffffffLL) return AKO4X_EINVAL;
+  if (tokens == 0) return AKO4X_OK;
+  if (!q_nope || !q_pe || !ckv_cache || !kpe_cache || !o || !lse) return AKO4X_EINVAL;
+  if (topk > 0 && !sparse_indices) return AKO4X_EINVAL;
+  if (misaligned(q_nope, q_pe, ckv_cache, kpe_cache, o)) return AKO4X_EINVAL;
+  const int splits = pick_splits(tokens, topk);
+  const size_t need = workspace_for(tokens, splits);
+  if (need > 0 && (!workspace || workspace_bytes < need)) return AKO4X_EWORKSPACE;
+  Params p = {};
+  p.q_nope = (const __nv_bfloat16*)q_nope;
+  p.q_pe = (const __nv_bfloat16*)q_pe;
+  p.ckv = (const __nv_bfloat16*)ckv_cache;
+  p.kpe = (const __nv_bfloat16*)kpe_cache;
+  p.indices = sparse_indices;
+  p.o = (__nv_bfloat16*)o;
+  p.lse = lse;
+  p.scale_log2 = sm_scale * AKO_LOG2E;
+  p.page_size = 1;
+  p.topk = (int)topk;
+  return launch<kSparse>(p, tokens, splits, workspace, (cudaStream_t)stream);
+}
+
+// ---- causal paged MLA prefill --------------------------------------------------------------------
+extern "C" size_t ako4x_mla_paged_prefill_workspace_bytes(int64_t total_q, int64_t batch,
+                                                          int64_t num_kv_indices, int64_t page_size) {
+  (void)total_q; (void)batch; (void)num_kv_indices; (void)page_size;
+  return 0;
+}
+
+extern "C" int ako4x_mla_paged_prefill(const void* q_nope, const void* q_pe, const void* ckv_cache,
+                                       const void* kpe_cache, const int32_t* qo_indptr,
+                                       const int32_t* kv_indptr, const int32_t* kv_indices,
+                                       float sm_scale, void* o, float* lse, int64_t total_q,
+                                       int64_t batch, int64_t num_kv_indices, int64_t page_size,
+                                       void* workspace, size_t workspace_bytes, void* stream) {
+  (void)workspace; (void)workspace_bytes;
+  if (total_q < 0 || batch < 0 || num_kv_indices < 0 || page_size < 1) return AKO4X_EINVAL;
+  if (total_q == 0) return AKO4X_OK;
+  if (batch == 0) return AKO4X_EINVAL;
+  if (!q_nope || !q_pe || !ckv_cache || !kpe_cache || !qo_indptr || !kv_indptr || !o || !lse)
+    return AKO4X_EINVAL;
+  if (num_kv_indices > 0 && !kv_indices) return AKO4X_EINVAL;
+  if (misaligned(q_nope, q_pe, ckv_cache, kpe_cache, o)) return AKO4X_EINVAL;
+  Params p = {};
+  p.q_nope = (const __nv_bfloat16*)q_nope;
+  p.q_pe = (const __nv_bfloat16*)q_pe;
+  p.ckv = (const __nv_bfloat16*)ckv_cache;
+  p.kpe = (const __nv_bfloat16*)kpe_cache;
+  p.qo_indptr = qo_indptr;
+  p.kv_indptr = kv_indptr;
+  p.indices = kv_indices;
+  p.o = (__nv_bfloat16*)o;
+  p.lse = lse;
+  p.scale_log2 = sm_scale * AKO_LOG2E;
+  p.page_size = (int)page_size;
+  p.batch = (int)batch;
+  return launch<kPrefill>(p, total_q, 1, nullptr, (cudaStream_t)stream);
+}

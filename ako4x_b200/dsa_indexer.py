@@ -1,0 +1,77 @@
+"""DSA FP8 top-k indexer (64 index heads, dim 128, 64-token pages, top-2048).
+
+Same signature and return convention as the reference plug-in
+``run(q_index_fp8, k_index_cache_fp8, weights, seq_lens, block_table) -> (topk_indices,)``
+(reference/dsa-topk-indexer/variants/v8_radix_bt256/kernel.py:569-655). The cache may arrive as
+any dtype/shape whose first dimension is the page count and which holds 8448 bytes per page.
+
+Selection ranks the fp32 scores exactly (ties: lower token position); each row lists its selected
+global cache slots in ascending token position, then -1.
+"""
+import torch
+
+from . import _cabi
+
+PAGE_BYTES = 8448
+TOPK = 2048
+
+
+def _check(q_index_fp8, k_index_cache_fp8, weights, seq_lens, block_table):
+    rows = q_index_fp8.shape[0]
+    if q_index_fp8.shape[1:] != (64, 128) or q_index_fp8.element_size() != 1:
+        raise _cabi.Ako4xError("dsa_indexer: q_index_fp8 must be e4m3 [rows, 64, 128]")
+    npages = k_index_cache_fp8.shape[0]
+    if k_index_cache_fp8.numel() * k_index_cache_fp8.element_size() != npages * PAGE_BYTES:
+        raise _cabi.Ako4xError("dsa_indexer: cache must hold 8448 bytes per page")
+    if weights.dtype != torch.float32 or weights.shape != (rows, 64):
+        raise _cabi.Ako4xError("dsa_indexer: weights must be fp32 [rows, 64]")
+    if seq_lens.dtype != torch.int32 or block_table.dtype != torch.int32 \
+            or seq_lens.numel() != rows or block_table.shape[0] != rows:
+        raise _cabi.Ako4xError("dsa_indexer: seq_lens int32 [rows], block_table int32 [rows, pages]")
+    return rows, npages, block_table.shape[1]
+
+
+@torch.no_grad()
+def run(q_index_fp8, k_index_cache_fp8, weights, seq_lens, block_table):
+    rows, npages, max_pages = _check(q_index_fp8, k_index_cache_fp8, weights, seq_lens, block_table)
+    L = _cabi.lib()
+    dev = q_index_fp8.device
+    out = torch.empty((rows, TOPK), dtype=torch.int32, device=dev)
+    ws_bytes = L.ako4x_dsa_topk_indexer_workspace_bytes(rows, max_pages)
+    ws = _cabi.workspace(ws_bytes, dev)
+    st = L.ako4x_dsa_topk_indexer(
+        _cabi.ptr(q_index_fp8.contiguous()), _cabi.ptr(k_index_cache_fp8.contiguous()),
+        _cabi.ptr(weights.contiguous()), _cabi.ptr(seq_lens.contiguous()),
+        _cabi.ptr(block_table.contiguous()), _cabi.ptr(out), rows, max_pages, npages,
+        _cabi.ptr(ws), ws_bytes, _cabi.stream())
+    _cabi.check(st, "ako4x_dsa_topk_indexer")
+    return (out,)
+
+
+@torch.no_grad()
+def index_scores(q_index_fp8, k_index_cache_fp8, weights, seq_lens, block_table):
+    """fp32 scores [rows, max_pages*64] (entries at t >= seq_len are -inf or unwritten pages)."""
+    rows, npages, max_pages = _check(q_index_fp8, k_index_cache_fp8, weights, seq_lens, block_table)
+    scores = torch.full((rows, max_pages * 64), float("-inf"), dtype=torch.float32,
+                        device=q_index_fp8.device)
+    st = _cabi.lib().ako4x_dsa_index_scores(
+        _cabi.ptr(q_index_fp8.contiguous()), _cabi.ptr(k_index_cache_fp8.contiguous()),
+        _cabi.ptr(weights.contiguous()), _cabi.ptr(seq_lens.contiguous()),
+        _cabi.ptr(block_table.contiguous()), _cabi.ptr(scores), rows, max_pages, npages,
+        _cabi.stream())
+    _cabi.check(st, "ako4x_dsa_index_scores")
+    return scores
+
+
+@torch.no_grad()
+def topk_select(scores, seq_lens, block_table):
+    """Exact top-2048 selection on given fp32 scores [rows, max_pages*64]."""
+    rows, max_pages = block_table.shape
+    if scores.dtype != torch.float32 or scores.shape != (rows, max_pages * 64):
+        raise _cabi.Ako4xError("topk_select: scores must be fp32 [rows, max_pages*64]")
+    out = torch.empty((rows, TOPK), dtype=torch.int32, device=scores.device)
+    st = _cabi.lib().ako4x_dsa_topk_select(
+        _cabi.ptr(scores.contiguous()), _cabi.ptr(seq_lens.contiguous()),
+        _cabi.ptr(block_table.contiguous()), _cabi.ptr(out), rows, max_pages, _cabi.stream())
+    _cabi.check(st, "ako4x_dsa_topk_select")
+    return out

@@ -1,0 +1,161 @@
+/*
+ * ako4x_b200 — C ABI of the B200 (sm_100a) operator library.
+ *
+ * One entry point per operator of the AKO4X / FlashInfer-Bench operator set. Every function
+ *   - takes raw DEVICE pointers, sizes and scalars only (no framework types),
+ *   - launches on the CUDA stream it is given (a cudaStream_t passed as void*) and never
+ *     synchronises the host, reads device memory from the host, allocates or frees,
+ *   - keeps no state between calls (no pointer-keyed caches, no cached outputs),
+ *   - initialises whatever part of `workspace` it later reads, so the workspace may hold garbage,
+ *   - returns AKO4X_OK or a negative status; nothing throws across this boundary.
+ * The matching `*_workspace_bytes` function gives the scratch size a call with the same
+ * dimensions needs; the caller owns that buffer (256-byte aligned) for the duration of the call.
+ *
+ * Each declaration cites the reference plug-in (`kernel.py::run`, a Python function called by the
+ * FlashInfer-Bench engine) whose arithmetic the entry point replaces. Paths are relative to the
+ * reference project root.
+ */
+#ifndef AKO4X_B200_H_
+#define AKO4X_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define AKO4X_OK 0
+#define AKO4X_EINVAL (-1)            /* null pointer, negative size, misaligned pointer */
+#define AKO4X_EUNSUPPORTED_SHAPE (-2) /* a compile-time dimension (heads, head_dim, ...) differs */
+#define AKO4X_ELAUNCH (-3)           /* the CUDA runtime refused a launch */
+#define AKO4X_EWORKSPACE (-4)        /* workspace_bytes smaller than *_workspace_bytes() */
+
+/* Version of this ABI; bumped when a signature changes. */
+int ako4x_abi_version(void);
+
+/* ---- a1. RMSNorm, hidden = 128 -------------------------------------------------------------
+ * Replaces run(hidden_states, weight):
+ *   reference/rmsnorm-h128/variants/triton_tiered_rows/kernel.py:261-278 (kernel :205-239).
+ * y = bf16( f32(x) * rsqrt(mean(f32(x)^2) + 1e-6) * f32(w) ); x, y bf16 [rows,128]; w bf16 [128].
+ */
+int ako4x_rmsnorm_h128(const void* x, const void* weight, void* y, int64_t rows, void* stream);
+
+/* ---- a2. Paged GQA decode, 32 query heads, 8 KV heads, head_dim 128 -----------------------
+ * Replaces run(q, k_cache, v_cache, kv_indptr, kv_indices, sm_scale):
+ *   reference/gqa-paged-decode-h32-kv8-d128-ps1/variants/triton_pdl_grid_dispatch/kernel.py:420-532.
+ * q bf16 [batch,32,128]; k_cache, v_cache bf16 [pages,page_size,8,128]; kv_indptr int32
+ * [batch+1]; kv_indices int32 [kv_indptr[batch]] (page ids); o bf16 [batch,32,128];
+ * lse fp32 [batch,32] = log2(sum exp(logit)); empty sequence gives o = 0, lse = -inf.
+ * `num_kv_indices` (the length of kv_indices) only sizes the split heuristic; it is a shape,
+ * not device data.
+ */
+size_t ako4x_gqa_paged_decode_workspace_bytes(int64_t batch, int64_t num_kv_indices,
+                                              int64_t page_size);
+int ako4x_gqa_paged_decode(const void* q, const void* k_cache, const void* v_cache,
+                           const int32_t* kv_indptr, const int32_t* kv_indices, float sm_scale,
+                           void* o, float* lse, int64_t batch, int64_t num_kv_indices,
+                           int64_t page_size, void* workspace, size_t workspace_bytes,
+                           void* stream);
+
+/* ---- a3. Paged MLA decode, 16 heads, ckv 512, kpe 64 ---------------------------------------
+ * Replaces run(q_nope, q_pe, ckv_cache, kpe_cache, kv_indptr, kv_indices, sm_scale):
+ *   reference/mla-paged-decode-h16-ckv512-kpe64-ps1/variants/triton_split_kv_2d_reduce_pdl_rw2/kernel.py:369-435.
+ * logit = (q_nope.ckv + q_pe.kpe) * sm_scale; o = softmax(logit) . ckv; lse base 2.
+ * q_nope bf16 [batch,16,512]; q_pe bf16 [batch,16,64]; ckv_cache bf16 [pages,page_size,512];
+ * kpe_cache bf16 [pages,page_size,64]; o bf16 [batch,16,512]; lse fp32 [batch,16].
+ */
+size_t ako4x_mla_paged_decode_workspace_bytes(int64_t batch, int64_t num_kv_indices,
+                                              int64_t page_size);
+int ako4x_mla_paged_decode(const void* q_nope, const void* q_pe, const void* ckv_cache,
+                           const void* kpe_cache, const int32_t* kv_indptr,
+                           const int32_t* kv_indices, float sm_scale, void* o, float* lse,
+                           int64_t batch, int64_t num_kv_indices, int64_t page_size,
+                           void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---- a4. Paged causal MLA prefill ----------------------------------------------------------
+ * Replaces run(q_nope, q_pe, ckv_cache, kpe_cache, qo_indptr, kv_indptr, kv_indices, sm_scale):
+ *   reference/mla-paged-prefill-causal-h16-ckv512-kpe64-ps1/variants/
+ *   iter6-triton-split-K-grid-pid0-kvsplit/submission_no_cache.py:537-692.
+ * Ragged batch; query i of a sequence sees keys j <= (kv_len - q_len) + i; a query that sees no
+ * key gets o = 0, lse = -inf. q_nope bf16 [total_q,16,512]; q_pe bf16 [total_q,16,64].
+ */
+size_t ako4x_mla_paged_prefill_workspace_bytes(int64_t total_q, int64_t batch,
+                                               int64_t num_kv_indices, int64_t page_size);
+int ako4x_mla_paged_prefill(const void* q_nope, const void* q_pe, const void* ckv_cache,
+                            const void* kpe_cache, const int32_t* qo_indptr,
+                            const int32_t* kv_indptr, const int32_t* kv_indices, float sm_scale,
+                            void* o, float* lse, int64_t total_q, int64_t batch,
+                            int64_t num_kv_indices, int64_t page_size, void* workspace,
+                            size_t workspace_bytes, void* stream);
+
+/* ---- a5. DSA FP8 top-k indexer, 64 index heads, dim 128, page 64, top-2048 -----------------
+ * Replaces run(q_index_fp8, k_index_cache_fp8, weights, seq_lens, block_table):
+ *   reference/dsa-topk-indexer/variants/v8_radix_bt256/kernel.py:569-655
+ *   (score :506-546, select :298-451).
+ * score[r,t] = (sum_h w[r,h] * relu(q[r,h,:] . k[t,:])) * kscale[t] for t < seq_lens[r]; token t
+ * of row r lives in page block_table[r, t/64], slot t%64. Each cache page is 8448 bytes: 64x128
+ * e4m3 values, then 64 fp32 scales. Output int32 [rows,2048]: the global slots page*64+slot of
+ * the 2048 highest fp32 scores (ties: lower token position wins), listed in ascending token
+ * position, then -1 padding; a row with seq_len <= 2048 lists all its tokens.
+ */
+size_t ako4x_dsa_topk_indexer_workspace_bytes(int64_t rows, int64_t max_pages);
+int ako4x_dsa_topk_indexer(const void* q_index_fp8, const void* k_index_cache, const float* weights,
+                           const int32_t* seq_lens, const int32_t* block_table,
+                           int32_t* topk_indices, int64_t rows, int64_t max_pages,
+                           int64_t num_cache_pages, void* workspace, size_t workspace_bytes,
+                           void* stream);
+/* The two halves of the indexer, exported so that selection can be checked on given scores.
+ * scores fp32 [rows, max_pages*64] (entries at t >= seq_len are ignored). */
+int ako4x_dsa_index_scores(const void* q_index_fp8, const void* k_index_cache, const float* weights,
+                           const int32_t* seq_lens, const int32_t* block_table, float* scores,
+                           int64_t rows, int64_t max_pages, int64_t num_cache_pages, void* stream);
+int ako4x_dsa_topk_select(const float* scores, const int32_t* seq_lens, const int32_t* block_table,
+                          int32_t* topk_indices, int64_t rows, int64_t max_pages, void* stream);
+
+/* ---- a6. DSA sparse MLA attention ----------------------------------------------------------
+ * Replaces run(q_nope, q_pe, ckv_cache, kpe_cache, sparse_indices, sm_scale):
+ *   reference/dsa-sparse-attention/variants/hybrid_pdl_v2/kernel.py:557-626
+ *   (arithmetic: variants/pure_triton/kernel.py:24-155).
+ * Keys of token t are rows sparse_indices[t,:] (int32 [tokens,topk], -1 ignored) of the caches
+ * flattened to [pages*page_size, 512] and [.., 64]. An all -1 row gives o = 0, lse = -inf.
+ */
+size_t ako4x_dsa_sparse_attention_workspace_bytes(int64_t tokens, int64_t topk);
+int ako4x_dsa_sparse_attention(const void* q_nope, const void* q_pe, const void* ckv_cache,
+                               const void* kpe_cache, const int32_t* sparse_indices,
+                               float sm_scale, void* o, float* lse, int64_t tokens, int64_t topk,
+                               int64_t num_cache_rows, void* workspace, size_t workspace_bytes,
+                               void* stream);
+
+/* ---- a7. FP8 block-scale MoE, DeepSeek-V3 routing ------------------------------------------
+ * Replaces run(routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights,
+ *              gemm1_weights_scale, gemm2_weights, gemm2_weights_scale, local_expert_offset,
+ *              routed_scaling_factor):
+ *   reference/moe-fp8-block-scale/variants/fused_routing_v2/kernel.py:509-667.
+ * 256 global experts in 8 groups, top-4 groups by top-2 sum, top-8 experts; hidden 7168,
+ * intermediate 2048, `num_local_experts` local experts starting at `local_expert_offset`.
+ * routing_logits fp32 [tokens,256]; routing_bias fp32 or bf16 [256] (bias_is_bf16);
+ * hidden_states e4m3 [tokens,7168]; hidden_states_scale fp32 [56,tokens];
+ * gemm1_weights e4m3 [E,4096,7168], scale fp32 [E,32,56]; gemm2_weights e4m3 [E,7168,2048],
+ * scale fp32 [E,56,16]; out bf16 [tokens,7168].
+ */
+size_t ako4x_moe_fp8_block_scale_workspace_bytes(int64_t tokens, int64_t num_local_experts);
+int ako4x_moe_fp8_block_scale(const float* routing_logits, const void* routing_bias,
+                              int bias_is_bf16, const void* hidden_states,
+                              const float* hidden_states_scale, const void* gemm1_weights,
+                              const float* gemm1_weights_scale, const void* gemm2_weights,
+                              const float* gemm2_weights_scale, int32_t local_expert_offset,
+                              float routed_scaling_factor, void* out, int64_t tokens,
+                              int64_t num_local_experts, void* workspace, size_t workspace_bytes,
+                              void* stream);
+/* Routing alone (same arithmetic as the first stage of the call above): the 8 selected global
+ * expert ids per token in ascending id order and their weights. topk_ids int32 [tokens,8];
+ * topk_weights fp32 [tokens,8]. Reference: fused_routing_v2/kernel.py:350-391. */
+int ako4x_moe_ds_routing(const float* routing_logits, const void* routing_bias, int bias_is_bf16,
+                         float routed_scaling_factor, int32_t* topk_ids, float* topk_weights,
+                         int64_t tokens, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* AKO4X_B200_H_ */

@@ -1,0 +1,116 @@
+"""Paged MLA decode, causal MLA prefill and DSA sparse attention parity through the C ABI."""
+import pytest
+import torch
+
+import oracle
+from ako4x_b200 import dsa_attention, mla_decode, mla_prefill, workloads as W
+from conftest import assert_close_bf16, assert_lse_close, load_golden
+
+pytestmark = pytest.mark.gpu
+DKEYS = ["q_nope", "q_pe", "ckv_cache", "kpe_cache", "kv_indptr", "kv_indices", "sm_scale"]
+PKEYS = ["q_nope", "q_pe", "ckv_cache", "kpe_cache", "qo_indptr", "kv_indptr", "kv_indices", "sm_scale"]
+SKEYS = ["q_nope", "q_pe", "ckv_cache", "kpe_cache", "sparse_indices", "sm_scale"]
+
+
+def _check(mod, fn, keys, a):
+    d = W.to_device(a, "cuda")
+    o, lse = mod.run(*[d[k] for k in keys])
+    ro, rlse = fn(*[a[k] for k in keys])
+    assert_close_bf16(o, ro)
+    assert_lse_close(lse, rlse)
+
+
+# ---- decode ------------------------------------------------------------------------------------
+def test_decode_golden(built_lib):
+    g = load_golden("mla_decode_b3")
+    d = W.to_device(g["inputs"], "cuda")
+    o, lse = mla_decode.run(*[d[k] for k in DKEYS])
+    assert_close_bf16(o, g["outputs"]["output"])
+    assert_lse_close(lse, g["outputs"]["lse"])
+
+
+@pytest.mark.parametrize("lens", [[1], [63], [64], [65], [129], [1000], [0, 2, 0], [512, 0, 77, 3000],
+                                  [8192]])
+def test_decode_ragged(built_lib, lens):
+    _check(mla_decode, oracle.mla_paged_decode, DKEYS,
+           W.make_mla_decode(len(lens), shape_id=sum(lens) % 83, lens=lens, extra_pages=11))
+
+
+@pytest.mark.parametrize("batch", [1, 32, 128])
+def test_decode_config_shapes(built_lib, batch):
+    _check(mla_decode, oracle.mla_paged_decode, DKEYS,
+           W.make_mla_decode(batch, shape_id=batch, len_lo=512, len_hi=1024 if batch > 1 else 8192))
+
+
+# ---- prefill -----------------------------------------------------------------------------------
+def test_prefill_golden(built_lib):
+    g = load_golden("mla_prefill_b3")
+    d = W.to_device(g["inputs"], "cuda")
+    o, lse = mla_prefill.run(*[d[k] for k in PKEYS])
+    assert_close_bf16(o, g["outputs"]["output"])
+    assert_lse_close(lse, g["outputs"]["lse"])
+
+
+@pytest.mark.parametrize("q_lens,kv_lens", [([1], [1]), ([16], [16]), ([16], [400]), ([70, 5], [70, 900]),
+                                             ([3, 0, 9], [10, 0, 9]), ([130, 64, 1], [200, 64, 333])])
+def test_prefill_ragged(built_lib, q_lens, kv_lens):
+    _check(mla_prefill, oracle.mla_paged_prefill, PKEYS,
+           W.make_mla_prefill(len(q_lens), shape_id=sum(kv_lens) % 79, q_lens=q_lens, kv_lens=kv_lens,
+                              extra_pages=9))
+
+
+def test_prefill_config_shape_reduced(built_lib):
+    """Batch 8 with the configured distributions at a quarter of the lengths (oracle cost)."""
+    _check(mla_prefill, oracle.mla_paged_prefill, PKEYS,
+           W.make_mla_prefill(8, shape_id=1, q_lo=16, q_hi=512, kv_hi=2048))
+
+
+def test_prefill_last_query_equals_decode(built_lib):
+    """Full-size property: the last query of every sequence attends to the whole KV list, which
+    is exactly a decode call on the same cache."""
+    a = W.make_mla_prefill(8, shape_id=2, device="cuda")
+    o, lse = mla_prefill.run(*[a[k] for k in PKEYS])
+    last = (a["qo_indptr"][1:] - 1).long()
+    od, lsed = mla_decode.run(a["q_nope"][last].contiguous(), a["q_pe"][last].contiguous(),
+                              a["ckv_cache"], a["kpe_cache"], a["kv_indptr"], a["kv_indices"],
+                              a["sm_scale"])
+    assert_close_bf16(o[last], od)
+    assert_lse_close(lse[last], lsed)
+    assert torch.isfinite(lse).all()
+
+
+# ---- DSA sparse attention ----------------------------------------------------------------------
+def test_sparse_golden(built_lib):
+    g = load_golden("dsa_attention_t4")
+    d = W.to_device(g["inputs"], "cuda")
+    o, lse = dsa_attention.run(*[d[k] for k in SKEYS])
+    assert_close_bf16(o, g["outputs"]["output"])
+    assert_lse_close(lse, g["outputs"]["lse"])
+
+
+@pytest.mark.parametrize("tokens,valid", [(1, 2048), (1, 100), (3, 1500), (64, 2048)])
+def test_sparse_against_oracle(built_lib, tokens, valid):
+    pages = 40
+    g = torch.Generator().manual_seed(tokens * 7 + valid)
+    idx = torch.full((tokens, 2048), -1, dtype=torch.int32)
+    for t in range(tokens):
+        idx[t, :valid] = torch.randperm(pages * 64, generator=g)[:valid].to(torch.int32)
+    if tokens > 1:
+        idx[1, ::3] = -1  # holes anywhere in the list
+    _check(dsa_attention, oracle.dsa_sparse_attention, SKEYS,
+           W.make_dsa_attention(tokens, pages * 64, idx, pages, shape_id=tokens))
+
+
+def test_sparse_order_invariance_full_size(built_lib):
+    """T=512 with 2048 indices each: permuting a row's index list must not change its result
+    beyond fp32 summation order."""
+    pages, T = 512, 512
+    g = torch.Generator(device="cuda").manual_seed(11)
+    idx = torch.stack([torch.randperm(pages * 64, generator=g, device="cuda")[:2048] for _ in range(8)])
+    idx = idx.repeat(T // 8, 1).to(torch.int32)
+    a = W.make_dsa_attention(T, pages * 64, idx, pages, shape_id=3, device="cuda")
+    o1, l1 = dsa_attention.run(*[a[k] for k in SKEYS])
+    a["sparse_indices"] = idx.flip(1).contiguous()
+    o2, l2 = dsa_attention.run(*[a[k] for k in SKEYS])
+    assert_close_bf16(o2, o1)
+    assert_lse_close(l2, l1)

@@ -1,0 +1,52 @@
+"""RMSNorm parity: CUDA kernel (through the C ABI) against the CPU oracle and the golden fixtures."""
+import pytest
+import torch
+
+import oracle
+from ako4x_b200 import rmsnorm, workloads as W
+from conftest import assert_close_bf16, load_golden
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("rows", [1, 2, 3, 64, 257, 4096, 70001])
+def test_against_oracle(built_lib, rows):
+    a = W.make_rmsnorm(rows, shape_id=rows % 97)
+    ref = oracle.rmsnorm(a["hidden_states"], a["weight"])
+    out = rmsnorm.run(a["hidden_states"].cuda(), a["weight"].cuda())
+    assert_close_bf16(out, ref)
+    # one bf16 rounding step at most, nearly all elements identical
+    assert (out.cpu() == ref).float().mean().item() > 0.99
+
+
+@pytest.mark.parametrize("rows", [1, 7, 64])
+def test_against_golden(built_lib, rows):
+    g = load_golden(f"rmsnorm_r{rows}")
+    out = rmsnorm.run(g["inputs"]["hidden_states"].cuda(), g["inputs"]["weight"].cuda())
+    assert_close_bf16(out, g["outputs"]["output"])
+
+
+def test_empty(built_lib):
+    x = torch.empty(0, 128, dtype=torch.bfloat16, device="cuda")
+    w = torch.ones(128, dtype=torch.bfloat16, device="cuda")
+    assert rmsnorm.run(x, w).shape == (0, 128)
+
+
+def test_full_size_properties(built_lib):
+    """520128 rows (largest reference workload): scale invariance and unit RMS, no oracle needed."""
+    a = W.make_rmsnorm(520128, shape_id=7, device="cuda")
+    x, w = a["hidden_states"], torch.ones(128, dtype=torch.bfloat16, device="cuda")
+    y = rmsnorm.run(x, w).float()
+    rms = y.pow(2).mean(dim=1).sqrt()
+    assert torch.all((rms - 1).abs() < 2e-2)
+    y2 = rmsnorm.run((x.float() * 4).to(torch.bfloat16), w).float()  # x4 is exact in bf16
+    assert torch.equal(y2, y)
+
+
+def test_same_buffers_new_contents(built_lib):
+    """No pointer-keyed caching: refilling the same tensors changes the result."""
+    a = W.make_rmsnorm(64, device="cuda")
+    y1 = rmsnorm.run(a["hidden_states"], a["weight"]).clone()
+    a["hidden_states"].mul_(-1)
+    y2 = rmsnorm.run(a["hidden_states"], a["weight"])
+    assert torch.equal(y2, -y1)
