@@ -10,7 +10,7 @@
 
 #define AKO_CHECK_LAUNCH()                                   \
   do {                                                       \
-    cudaError_t _e = cudaPeekAtLastError();                  \
+    cudaError_t _e = cudaGetLastError();                     \
     if (_e != cudaSuccess) return AKO4X_ELAUNCH;             \
   } while (0)
 
@@ -93,10 +93,11 @@ __device__ __forceinline__ float fast_exp2(float x) {
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;\n" ::); }
 
-// Opts a kernel into `bytes` of dynamic shared memory once per device. The flag is per call site
-// (one static array per instantiation); a race between host threads only repeats the call.
-template <typename K>
-inline bool ensure_dynamic_smem(K kernel, int bytes) {
+// Opts a kernel into `bytes` of dynamic shared memory once per device. The kernel is a template
+// argument so that every kernel gets its own flags; a race between host threads only repeats
+// the call.
+template <auto kernel>
+inline bool ensure_dynamic_smem(int bytes) {
   static bool done[64] = {};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;

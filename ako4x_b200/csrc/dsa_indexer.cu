@@ -182,6 +182,7 @@ __global__ void __launch_bounds__(SEL_THREADS) dsa_select_kernel(
     if (tid < 256) hist[tid] = 0;
     __syncthreads();
     const uint32_t prefix = s_prefix;
+    const int krem_in = s_krem;  // read before anyone updates it at the end of this pass
     const int shift = 8 * d;
     const uint32_t hi_mask = (d == 3) ? 0u : (0xffffffffu << (shift + 8));
     for (int it = 0; it < n_iter; ++it) {
@@ -207,11 +208,10 @@ __global__ void __launch_bounds__(SEL_THREADS) dsa_select_kernel(
     }
     // v = count(digit >= tid); pick the bin where the k-th largest lives
     if (tid < 256) {
-      const int krem = s_krem;
       const int gt = v - own;
-      if (gt < krem && krem <= v) {
+      if (gt < krem_in && krem_in <= v) {
         s_prefix = prefix | ((uint32_t)tid << shift);
-        s_krem = krem - gt;
+        s_krem = krem_in - gt;
       }
     }
     __syncthreads();
@@ -267,7 +267,7 @@ __global__ void __launch_bounds__(SEL_THREADS) dsa_select_kernel(
 int launch_scores(const void* q, const void* cache, const float* weights, const int32_t* seq_lens,
                   const int32_t* block_table, float* scores, int64_t rows, int64_t max_pages,
                   int64_t num_cache_pages, int skip_short, cudaStream_t st) {
-  if (!ako::ensure_dynamic_smem(dsa_score_kernel, SC_SMEM)) return AKO4X_ELAUNCH;
+  if (!ako::ensure_dynamic_smem<dsa_score_kernel>(SC_SMEM)) return AKO4X_ELAUNCH;
   dim3 grid((unsigned)rows, (unsigned)ako::cdiv(max_pages, SC_PAGES_PER_CTA));
   dsa_score_kernel<<<grid, SC_THREADS, SC_SMEM, st>>>(
       (const unsigned char*)q, (const unsigned char*)cache, weights, seq_lens, block_table, scores,

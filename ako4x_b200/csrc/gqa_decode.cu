@@ -268,7 +268,7 @@ extern "C" int ako4x_gqa_paged_decode(const void* q, const void* k_cache, const 
   p.page_size = (int)page_size;
   p.num_splits = splits;
 
-  if (!ako::ensure_dynamic_smem(gqa_decode_kernel, SMEM_BYTES)) return AKO4X_ELAUNCH;
+  if (!ako::ensure_dynamic_smem<gqa_decode_kernel>(SMEM_BYTES)) return AKO4X_ELAUNCH;
   const int64_t grid = batch * 2 * splits;
   if (grid > 0x7fffffffLL) return AKO4X_EINVAL;
   gqa_decode_kernel<<<(unsigned)grid, THREADS, SMEM_BYTES, st>>>(p);

@@ -365,7 +365,7 @@ int launch(Params& p, int64_t rows, int splits, void* workspace, cudaStream_t st
   p.num_splits = splits;
   p.part_acc = (float*)workspace;
   p.part_ml = workspace ? p.part_acc + (size_t)rows * H * splits * DC : nullptr;
-  if (!ako::ensure_dynamic_smem(mla_attention_kernel<MODE>, SMEM_BYTES)) return AKO4X_ELAUNCH;
+  if (!ako::ensure_dynamic_smem<mla_attention_kernel<MODE>>(SMEM_BYTES)) return AKO4X_ELAUNCH;
   const int64_t grid = rows * splits;
   if (grid > 0x7fffffffLL) return AKO4X_EINVAL;
   mla_attention_kernel<MODE><<<(unsigned)grid, THREADS, SMEM_BYTES, st>>>(p);

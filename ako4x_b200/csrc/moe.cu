@@ -1,0 +1,649 @@
+// FP8 block-scale MoE with DeepSeek-V3 routing (256 experts, 8 groups, top-4 groups, top-8
+// experts; hidden 7168, intermediate 2048).
+//
+// Pipeline (all on the caller's stream, no host synchronisation; the launch geometry depends on
+// shapes only and the kernels size their work from device-side counts):
+//   1. routing      one warp per token: sigmoid, bias, group top-2 sums, top-4 groups, top-8
+//                   experts (ties: lower index), weights; counts tokens per local expert.
+//   2. scatter      one CTA per local expert: stable (token-ordered) positions inside the
+//                   expert's segment, so the row order and every later sum is deterministic.
+//   3. GEMM1        grouped FP8 GEMM  g = x W13^T  with 128x128 block-scale promotion in fp32
+//                   registers, fused SwiGLU  h = silu(g[2048:]) * g[:2048],  and h written as TWO
+//                   e4m3 pieces per element (h ~ s*(hi + lo/16), s a power of two per row and
+//                   128 columns), which keeps about bf16 accuracy while GEMM2 stays a pure FP8
+//                   tensor-core GEMM.
+//   4. GEMM2        the same grouped FP8 GEMM over K = 2*2048 (hi piece, lo piece) against W2.
+//   5. combine      out[t] = bf16( sum over the token's local experts, in expert order, of
+//                   weight * y ): a gather-reduce, no atomics.
+// The grouped GEMM is persistent: each CTA walks a tile list (expert, n-tile, m-tile) derived from
+// the per-expert counts; tiles are 32*WM rows x 256 weight rows x 128 (one scale block) per step,
+// fed by a 4-stage cp.async ring with XOR-swizzled 128-byte rows and mma.sync.m16n8k32 e4m3.
+#include "common.cuh"
+
+namespace {
+
+constexpr int NE = 256;         // global experts
+constexpr int NG = 8;           // groups
+constexpr int TOPK_G = 4;
+constexpr int TOPK = 8;
+constexpr int HID = 7168;
+constexpr int INTER = 2048;
+constexpr int KB1 = HID / 128;  // 56 k-blocks in GEMM1
+constexpr int KB2 = 2 * INTER / 128;  // 32 k-blocks in GEMM2 (two pieces)
+constexpr int MAX_LOCAL = 256;
+
+struct Workspace {
+  int32_t* topk_ids;      // [T,8]
+  float* topk_w;          // [T,8]
+  int32_t* pair_pos;      // [T,8] row of the pair in expert-sorted order, -1 if not local
+  int32_t* counts;        // [MAX_LOCAL]
+  int32_t* offsets;       // [MAX_LOCAL+1]
+  int32_t* sorted_token;  // [cap]
+  float* h_scale;         // [16][cap]
+  uint8_t* hq;            // [cap][4096]  (hi piece | lo piece)
+  float* y;               // [cap][7168]
+  size_t total;
+};
+
+Workspace carve(void* base, int64_t tokens) {
+  const size_t cap = (size_t)tokens * TOPK;
+  uintptr_t p = (uintptr_t)base;
+  auto take = [&](size_t bytes) {
+    uintptr_t r = p;
+    p += (bytes + 255) & ~(size_t)255;
+    return r;
+  };
+  Workspace w;
+  w.topk_ids = (int32_t*)take(cap * 4);
+  w.topk_w = (float*)take(cap * 4);
+  w.pair_pos = (int32_t*)take(cap * 4);
+  w.counts = (int32_t*)take(MAX_LOCAL * 4);
+  w.offsets = (int32_t*)take((MAX_LOCAL + 1) * 4);
+  w.sorted_token = (int32_t*)take(cap * 4);
+  w.h_scale = (float*)take(16 * cap * 4);
+  w.hq = (uint8_t*)take(cap * 2 * INTER);
+  w.y = (float*)take(cap * (size_t)HID * 4);
+  w.total = p - (uintptr_t)base;
+  return w;
+}
+
+// ---------------------------------------------------------------------------------------------
+// 1. routing
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(128) moe_routing_kernel(
+    const float* __restrict__ logits, const void* __restrict__ bias, int bias_is_bf16, float factor,
+    int tokens, int32_t* __restrict__ topk_ids, float* __restrict__ topk_w,
+    int32_t* __restrict__ pair_pos, int32_t* __restrict__ counts, int local_off, int n_local) {
+  const int lane = threadIdx.x & 31;
+  const int token = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (token >= tokens) return;
+  float s[8], sb[8];
+  {
+    const float4* lp = reinterpret_cast<const float4*>(logits + (int64_t)token * NE + lane * 8);
+    const float4 a = lp[0], b = lp[1];
+    const float x[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    float bv[8];
+    if (bias_is_bf16) {
+      const uint4 u = *reinterpret_cast<const uint4*>((const __nv_bfloat16*)bias + lane * 8);
+      const uint32_t* p = reinterpret_cast<const uint32_t*>(&u);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { bv[2 * i] = ako::bf16_lo(p[i]); bv[2 * i + 1] = ako::bf16_hi(p[i]); }
+    } else {
+      const float4* bp = reinterpret_cast<const float4*>((const float*)bias + lane * 8);
+      const float4 c = bp[0], d = bp[1];
+      bv[0] = c.x; bv[1] = c.y; bv[2] = c.z; bv[3] = c.w;
+      bv[4] = d.x; bv[5] = d.y; bv[6] = d.z; bv[7] = d.w;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      s[j] = 1.0f / (1.0f + expf(-x[j]));
+      sb[j] = s[j] + bv[j];
+    }
+  }
+  // group score: sum of the two largest biased scores of the group (4 lanes x 8 values)
+  float m1 = -INFINITY, m2 = -INFINITY;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const float v = sb[j];
+    if (v > m1) { m2 = m1; m1 = v; } else if (v > m2) { m2 = v; }
+  }
+#pragma unroll
+  for (int off = 1; off <= 2; off <<= 1) {
+    const float o1 = __shfl_xor_sync(0xffffffffu, m1, off);
+    const float o2 = __shfl_xor_sync(0xffffffffu, m2, off);
+    const float n1 = fmaxf(m1, o1);
+    const float n2 = fmaxf(fminf(m1, o1), fmaxf(m2, o2));
+    m1 = n1; m2 = n2;
+  }
+  const float gscore = m1 + m2;
+  const int my_group = lane >> 2;
+  int rank = 0;
+#pragma unroll
+  for (int gi = 0; gi < NG; ++gi) {
+    const float og = __shfl_sync(0xffffffffu, gscore, gi * 4);
+    rank += (og > gscore || (og == gscore && gi < my_group)) ? 1 : 0;
+  }
+  const bool keep = rank < TOPK_G;
+  // top-8 by (biased score desc, index asc) among kept groups
+  unsigned selmask = 0;
+  for (int round = 0; round < TOPK; ++round) {
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    if (keep) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {  // ascending index, strict '>' : ties keep the lower index
+        if (!((selmask >> j) & 1u) && (bi == 0x7fffffff || sb[j] > bv)) { bv = sb[j]; bi = lane * 8 + j; }
+      }
+    }
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, off);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
+      const bool take = (oi != 0x7fffffff) && (bi == 0x7fffffff || ov > bv || (ov == bv && oi < bi));
+      if (take) { bv = ov; bi = oi; }
+    }
+    if ((bi >> 3) == lane) selmask |= 1u << (bi & 7);
+  }
+  // ascending-id positions and weights
+  float ssum = 0.f;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) ssum += ((selmask >> j) & 1u) ? s[j] : 0.f;
+#pragma unroll
+  for (int off = 16; off >= 1; off >>= 1) ssum += __shfl_xor_sync(0xffffffffu, ssum, off);
+  const int cnt = __popc(selmask);
+  int incl = cnt;
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) {
+    const int y = __shfl_up_sync(0xffffffffu, incl, off);
+    if (lane >= off) incl += y;
+  }
+  int pos = incl - cnt;
+  const float denom = ssum + 1e-20f;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    if ((selmask >> j) & 1u) {
+      const int e = lane * 8 + j;
+      topk_ids[(int64_t)token * TOPK + pos] = e;
+      topk_w[(int64_t)token * TOPK + pos] = (s[j] / denom) * factor;
+      if (pair_pos) {
+        pair_pos[(int64_t)token * TOPK + pos] = -1;
+        const int le = e - local_off;
+        if (le >= 0 && le < n_local) atomicAdd(&counts[le], 1);
+      }
+      ++pos;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// 2. scatter: stable positions per local expert
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(1024) moe_scatter_kernel(
+    const int32_t* __restrict__ topk_ids, const int32_t* __restrict__ counts,
+    int32_t* __restrict__ offsets, int32_t* __restrict__ sorted_token, int32_t* __restrict__ pair_pos,
+    int tokens, int local_off, int n_local) {
+  __shared__ int warp_tot[32];
+  __shared__ int s_base;   // pairs of this expert placed by earlier chunks
+  __shared__ int s_off;    // first row of this expert's segment
+  __shared__ int s_chunk;  // pairs found in the current chunk
+  const int le = blockIdx.x;
+  const int ge = local_off + le;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (warp == 0) {
+    int acc = 0;
+    for (int i = lane; i < le; i += 32) acc += counts[i];
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+    if (lane == 0) {
+      s_off = acc;
+      s_base = 0;
+      offsets[le] = acc;
+      if (le == n_local - 1) offsets[n_local] = acc + counts[le];
+    }
+  }
+  __syncthreads();
+  const int off_e = s_off;
+  if (counts[le] == 0) return;
+  for (int t0 = 0; t0 < tokens; t0 += 1024) {
+    const int t = t0 + tid;
+    int slot = -1;
+    if (t < tokens) {
+      const int4* ip = reinterpret_cast<const int4*>(topk_ids + (int64_t)t * TOPK);
+      const int4 a = ip[0], b = ip[1];
+      slot = (a.x == ge) ? 0 : (a.y == ge) ? 1 : (a.z == ge) ? 2 : (a.w == ge) ? 3
+           : (b.x == ge) ? 4 : (b.y == ge) ? 5 : (b.z == ge) ? 6 : (b.w == ge) ? 7 : -1;
+    }
+    const unsigned bal = __ballot_sync(0xffffffffu, slot >= 0);
+    if (lane == 0) warp_tot[warp] = __popc(bal);
+    __syncthreads();
+    if (warp == 0) {
+      const int x = warp_tot[lane];
+      int incl = x;
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        const int y = __shfl_up_sync(0xffffffffu, incl, off);
+        if (lane >= off) incl += y;
+      }
+      warp_tot[lane] = incl - x;
+      if (lane == 31) s_chunk = incl;
+    }
+    __syncthreads();
+    if (slot >= 0) {
+      const int pos = off_e + s_base + warp_tot[warp] + __popc(bal & ((1u << lane) - 1u));
+      sorted_token[pos] = t;
+      pair_pos[(int64_t)t * TOPK + slot] = pos;
+    }
+    __syncthreads();
+    if (tid == 0) s_base += s_chunk;
+    __syncthreads();
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// 3/4. grouped FP8 block-scale GEMM (persistent)
+// ---------------------------------------------------------------------------------------------
+constexpr int WN = 4;            // warps along N; each warp owns 8 n-tiles of 8 weight rows
+constexpr int BROWS = 256;       // weight rows per CTA tile (two 128-row scale blocks)
+constexpr int G_STAGES = 4;
+
+template <int WM>
+struct GemmCfg {
+  static constexpr int BM = 32 * WM;
+  static constexpr int THREADS = 32 * WM * WN;
+  static constexpr int A_BYTES = BM * 128;
+  static constexpr int B_BYTES = BROWS * 128;
+  static constexpr int S_BYTES = BM * 4;  // activation scales of the stage
+  static constexpr int STAGE = A_BYTES + B_BYTES + S_BYTES;
+  static constexpr int SMEM = G_STAGES * STAGE;
+};
+
+struct GemmParams {
+  const uint8_t* a;          // GEMM1: x [T,7168]; GEMM2: hq [cap,4096]
+  const float* a_scale;      // GEMM1: [56,T]; GEMM2: h_scale [16,cap]
+  const uint8_t* w;          // GEMM1: W13 [E,4096,7168]; GEMM2: W2 [E,7168,2048]
+  const float* w_scale;      // GEMM1: [E,32,56]; GEMM2: [E,56,16]
+  const int32_t* counts;
+  const int32_t* offsets;
+  const int32_t* sorted_token;
+  uint8_t* hq;               // GEMM1 out
+  float* h_scale;            // GEMM1 out
+  float* y;                  // GEMM2 out
+  int64_t a_scale_stride;    // T (GEMM1) or cap (GEMM2)
+  int64_t h_scale_stride;    // cap: row stride of the h_scale GEMM1 writes
+  int n_local;
+};
+
+template <int WM, int WHICH>  // WHICH: 1 = GEMM1 (+SwiGLU, two-piece quantisation), 2 = GEMM2
+__global__ void __launch_bounds__(GemmCfg<WM>::THREADS, 1) moe_grouped_gemm_kernel(GemmParams p) {
+  using C = GemmCfg<WM>;
+  constexpr int BM = C::BM;
+  constexpr int NKB = (WHICH == 1) ? KB1 : KB2;
+  constexpr int NT_TILES = (WHICH == 1) ? (INTER / 128) : (HID / BROWS);  // 16 or 28 n-tiles
+  extern __shared__ __align__(128) unsigned char smem[];
+  __shared__ int s_cum[MAX_LOCAL + 1];   // cumulative m-tiles per expert
+  __shared__ int s_tok[BM];              // A row of each tile row (token or pair row), -1 = none
+  __shared__ float s_bs[2][NKB];         // weight scales of the tile's two 128-row blocks
+  __shared__ int s_amax[BM];             // GEMM1 epilogue: per-row max |h| (float bits)
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int wm = warp / WN, wn = warp % WN;
+  const int g = lane >> 2, t = lane & 3;
+
+  if (tid == 0) {
+    int acc = 0;
+    for (int e = 0; e < p.n_local; ++e) {
+      s_cum[e] = acc;
+      acc += (p.counts[e] + BM - 1) / BM;
+    }
+    s_cum[p.n_local] = acc;
+  }
+  __syncthreads();
+  const int total_tiles = s_cum[p.n_local] * NT_TILES;
+
+  for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+    // tile -> (expert, n-tile, m-tile); m fastest so neighbouring CTAs share weight tiles
+    int e = 0;
+    while (s_cum[e + 1] * NT_TILES <= tile) ++e;
+    const int mt_e = s_cum[e + 1] - s_cum[e];
+    const int rem = tile - s_cum[e] * NT_TILES;
+    const int nt = rem / mt_e, mt = rem % mt_e;
+    const int cnt = p.counts[e];
+    const int row0 = p.offsets[e] + mt * BM;       // first pair row of the tile
+    const int rows = min(BM, cnt - mt * BM);
+
+    __syncthreads();  // previous tile's readers of s_tok / s_bs / smem are done
+    if (tid < BM) {
+      int src = -1;
+      if (tid < rows) src = (WHICH == 1) ? p.sorted_token[row0 + tid] : row0 + tid;
+      s_tok[tid] = src;
+      if (WHICH == 1) s_amax[tid] = 0;
+    }
+    for (int i = tid; i < 2 * NKB; i += C::THREADS) {
+      const int blk = i / NKB, kb = i % NKB;
+      float v;
+      if (WHICH == 1)
+        v = p.w_scale[((int64_t)e * (2 * INTER / 128) + blk * (INTER / 128) + nt) * KB1 + kb];
+      else
+        v = p.w_scale[((int64_t)e * (HID / 128) + nt * 2 + blk) * (INTER / 128) + (kb & 15)];
+      s_bs[blk][kb] = v;
+    }
+    __syncthreads();
+
+    const uint8_t* wbase = p.w + (int64_t)e * (WHICH == 1 ? (int64_t)2 * INTER * HID : (int64_t)HID * INTER);
+    constexpr int64_t W_ROW = (WHICH == 1) ? HID : INTER;   // bytes per weight row
+    constexpr int64_t A_ROW = (WHICH == 1) ? HID : 2 * INTER;
+
+    auto load_stage = [&](int kb, int stage) {
+      unsigned char* sa = smem + stage * C::STAGE;
+      unsigned char* sb = sa + C::A_BYTES;
+      float* ss = reinterpret_cast<float*>(sb + C::B_BYTES);
+      // A: BM rows x 8 chunks
+      for (int i = tid; i < BM * 8; i += C::THREADS) {
+        const int r = i >> 3, c = i & 7;
+        const int src = s_tok[r];
+        const uint8_t* gp = p.a + (int64_t)max(src, 0) * A_ROW + (int64_t)kb * 128 + c * 16;
+        ako::cp_async16(ako::smem_u32(sa + r * 128 + ((c ^ (r & 7)) << 4)), gp, src >= 0);
+      }
+      // B: 256 weight rows x 8 chunks
+      const int wkb = (WHICH == 1) ? kb : (kb & 15);
+      for (int i = tid; i < BROWS * 8; i += C::THREADS) {
+        const int r = i >> 3, c = i & 7;
+        int64_t wrow;
+        if (WHICH == 1) wrow = (r < 128) ? (nt * 128 + r) : (INTER + nt * 128 + (r - 128));
+        else wrow = (int64_t)nt * BROWS + r;
+        const uint8_t* gp = wbase + wrow * W_ROW + (int64_t)wkb * 128 + c * 16;
+        ako::cp_async16(ako::smem_u32(sb + r * 128 + ((c ^ (r & 7)) << 4)), gp, true);
+      }
+      // activation scales of the k-block
+      if (tid < BM) {
+        const int src = s_tok[tid];
+        const float* gp = p.a_scale + (int64_t)wkb * p.a_scale_stride + max(src, 0);
+        const int sz = (src >= 0) ? 4 : 0;
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;\n" ::"r"(ako::smem_u32(ss + tid)),
+                     "l"(gp), "r"(sz));
+      }
+    };
+
+    float acc[2][8][4];
+#pragma unroll
+    for (int mi = 0; mi < 2; ++mi)
+#pragma unroll
+      for (int ni = 0; ni < 8; ++ni) acc[mi][ni][0] = acc[mi][ni][1] = acc[mi][ni][2] = acc[mi][ni][3] = 0.f;
+
+#pragma unroll
+    for (int s = 0; s < G_STAGES - 1; ++s) {
+      load_stage(s, s);
+      ako::cp_async_commit();
+    }
+
+#pragma unroll 1
+    for (int kb = 0; kb < NKB; ++kb) {
+      ako::cp_async_wait<G_STAGES - 2>();
+      __syncthreads();
+      if (kb + G_STAGES - 1 < NKB) load_stage(kb + G_STAGES - 1, (kb + G_STAGES - 1) % G_STAGES);
+      ako::cp_async_commit();
+
+      const unsigned char* sa = smem + (kb % G_STAGES) * C::STAGE;
+      const unsigned char* sb = sa + C::A_BYTES;
+      const float* ss = reinterpret_cast<const float*>(sb + C::B_BYTES);
+
+      float blk[2][8][4];
+#pragma unroll
+      for (int mi = 0; mi < 2; ++mi)
+#pragma unroll
+        for (int ni = 0; ni < 8; ++ni) blk[mi][ni][0] = blk[mi][ni][1] = blk[mi][ni][2] = blk[mi][ni][3] = 0.f;
+
+#pragma unroll
+      for (int ks = 0; ks < 4; ++ks) {
+        uint32_t af[2][4];
+#pragma unroll
+        for (int mi = 0; mi < 2; ++mi) {
+          const int r = 32 * wm + 16 * mi + (lane & 7) + (((lane >> 3) & 1) << 3);
+          const int c = 2 * ks + (lane >> 4);
+          ako::ldmatrix_x4(af[mi][0], af[mi][1], af[mi][2], af[mi][3],
+                           ako::smem_u32(sa + r * 128 + ((c ^ (r & 7)) << 4)));
+        }
+#pragma unroll
+        for (int np = 0; np < 4; ++np) {  // pairs of n-tiles
+          // n-tiles 0-3 sit in rows [0,128), 4-7 in rows [128,256) of the weight tile
+          const int ni0 = 2 * np;
+          const int rbase = ((ni0 < 4) ? 0 : 128) + 32 * wn + 8 * (ni0 & 3);
+          const int r = rbase + ((lane >> 4) << 3) + (lane & 7);
+          const int c = 2 * ks + ((lane >> 3) & 1);
+          uint32_t b00, b01, b10, b11;
+          ako::ldmatrix_x4(b00, b01, b10, b11, ako::smem_u32(sb + r * 128 + ((c ^ (r & 7)) << 4)));
+#pragma unroll
+          for (int mi = 0; mi < 2; ++mi) {
+            ako::mma_e4m3_16832(blk[mi][ni0], af[mi], b00, b01);
+            ako::mma_e4m3_16832(blk[mi][ni0 + 1], af[mi], b10, b11);
+          }
+        }
+      }
+      // promotion: acc += blk * a_scale[row] * w_scale[block]
+      const float bs0 = s_bs[0][kb], bs1 = s_bs[1][kb];
+      const float piece = (WHICH == 2 && kb >= 16) ? 0.0625f : 1.0f;
+#pragma unroll
+      for (int mi = 0; mi < 2; ++mi) {
+        const int r = 32 * wm + 16 * mi + g;
+        const float sa0 = ss[r] * piece, sa1 = ss[r + 8] * piece;
+#pragma unroll
+        for (int ni = 0; ni < 8; ++ni) {
+          const float bsv = (ni < 4) ? bs0 : bs1;
+          acc[mi][ni][0] = fmaf(blk[mi][ni][0], sa0 * bsv, acc[mi][ni][0]);
+          acc[mi][ni][1] = fmaf(blk[mi][ni][1], sa0 * bsv, acc[mi][ni][1]);
+          acc[mi][ni][2] = fmaf(blk[mi][ni][2], sa1 * bsv, acc[mi][ni][2]);
+          acc[mi][ni][3] = fmaf(blk[mi][ni][3], sa1 * bsv, acc[mi][ni][3]);
+        }
+      }
+    }
+    ako::cp_async_wait<0>();
+
+    if (WHICH == 2) {
+      // y[pair_row][n] fp32
+#pragma unroll
+      for (int mi = 0; mi < 2; ++mi)
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {
+          const int r = 32 * wm + 16 * mi + g + 8 * hf;
+          if (r < rows) {
+            float* yp = p.y + (int64_t)(row0 + r) * HID + nt * BROWS;
+#pragma unroll
+            for (int ni = 0; ni < 8; ++ni) {
+              const int col = ((ni < 4) ? 0 : 128) + 32 * wn + 8 * (ni & 3) + 2 * t;
+              *reinterpret_cast<float2*>(yp + col) = make_float2(acc[mi][ni][2 * hf], acc[mi][ni][2 * hf + 1]);
+            }
+          }
+        }
+    } else {
+      // SwiGLU: n-tiles 0-3 hold the linear half, 4-7 the gate half of the same 32 columns
+      float hv[2][2][4][2];
+#pragma unroll
+      for (int mi = 0; mi < 2; ++mi)
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {
+          float mx = 0.f;
+#pragma unroll
+          for (int ni = 0; ni < 4; ++ni)
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+              const float x1 = acc[mi][ni][2 * hf + j];
+              const float x2 = acc[mi][ni + 4][2 * hf + j];
+              const float h = (x2 / (1.0f + __expf(-x2))) * x1;
+              hv[mi][hf][ni][j] = h;
+              mx = fmaxf(mx, fabsf(h));
+            }
+          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+          if (t == 0) atomicMax(&s_amax[32 * wm + 16 * mi + g + 8 * hf], __float_as_int(mx));
+        }
+      __syncthreads();
+#pragma unroll
+      for (int mi = 0; mi < 2; ++mi)
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {
+          const int r = 32 * wm + 16 * mi + g + 8 * hf;
+          if (r < rows) {
+            const float amax = __int_as_float(s_amax[r]);
+            // power-of-two scale with amax / scale < 256 (e4m3 holds up to 448)
+            int ex = ((__float_as_int(amax) >> 23) & 0xff) - 127 - 7;
+            ex = max(ex, -100);
+            const float sc = __int_as_float((ex + 127) << 23);
+            const float inv = __int_as_float((127 - ex) << 23);
+            uint8_t* hp = p.hq + (int64_t)(row0 + r) * (2 * INTER) + nt * 128 + 32 * wn + 2 * t;
+#pragma unroll
+            for (int ni = 0; ni < 4; ++ni) {
+              const float v0 = hv[mi][hf][ni][0] * inv, v1 = hv[mi][hf][ni][1] * inv;
+              const __nv_fp8x2_storage_t hi = __nv_cvt_float2_to_fp8x2(make_float2(v0, v1), __NV_SATFINITE, __NV_E4M3);
+              const __half2_raw hr = __nv_cvt_fp8x2_to_halfraw2(hi, __NV_E4M3);
+              const float2 hf2 = __half22float2(*reinterpret_cast<const __half2*>(&hr));
+              const __nv_fp8x2_storage_t lo = __nv_cvt_float2_to_fp8x2(
+                  make_float2((v0 - hf2.x) * 16.f, (v1 - hf2.y) * 16.f), __NV_SATFINITE, __NV_E4M3);
+              *reinterpret_cast<__nv_fp8x2_storage_t*>(hp + 8 * ni) = hi;
+              *reinterpret_cast<__nv_fp8x2_storage_t*>(hp + INTER + 8 * ni) = lo;
+            }
+            if (wn == 0 && t == 0) p.h_scale[(int64_t)nt * p.h_scale_stride + row0 + r] = sc;
+          }
+        }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// 5. combine
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) moe_combine_kernel(
+    const float* __restrict__ y, const int32_t* __restrict__ pair_pos, const float* __restrict__ topk_w,
+    __nv_bfloat16* __restrict__ out) {
+  const int64_t tkn = blockIdx.x;
+  int pos[TOPK];
+  float w[TOPK];
+#pragma unroll
+  for (int s = 0; s < TOPK; ++s) {
+    pos[s] = pair_pos[tkn * TOPK + s];
+    w[s] = topk_w[tkn * TOPK + s];
+  }
+  for (int c = threadIdx.x * 4; c < HID; c += 256 * 4) {
+    float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int s = 0; s < TOPK; ++s) {
+      if (pos[s] >= 0) {
+        const float4 v = *reinterpret_cast<const float4*>(y + (int64_t)pos[s] * HID + c);
+        a.x += v.x * w[s]; a.y += v.y * w[s]; a.z += v.z * w[s]; a.w += v.w * w[s];
+      }
+    }
+    uint2 pk;
+    pk.x = ako::pack_bf16x2(a.x, a.y);
+    pk.y = ako::pack_bf16x2(a.z, a.w);
+    *reinterpret_cast<uint2*>(out + tkn * HID + c) = pk;
+  }
+}
+
+template <int WM>
+int launch_gemms(const GemmParams& p1, const GemmParams& p2, int sms, cudaStream_t st) {
+  using C = GemmCfg<WM>;
+  if (!ako::ensure_dynamic_smem<moe_grouped_gemm_kernel<WM, 1>>(C::SMEM)) return AKO4X_ELAUNCH;
+  if (!ako::ensure_dynamic_smem<moe_grouped_gemm_kernel<WM, 2>>(C::SMEM)) return AKO4X_ELAUNCH;
+  moe_grouped_gemm_kernel<WM, 1><<<sms, C::THREADS, C::SMEM, st>>>(p1);
+  AKO_CHECK_LAUNCH();
+  moe_grouped_gemm_kernel<WM, 2><<<sms, C::THREADS, C::SMEM, st>>>(p2);
+  AKO_CHECK_LAUNCH();
+  return AKO4X_OK;
+}
+
+int sm_count() {
+  static int cached[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+}  // namespace
+
+extern "C" size_t ako4x_moe_fp8_block_scale_workspace_bytes(int64_t tokens, int64_t num_local_experts) {
+  (void)num_local_experts;
+  if (tokens <= 0) return 0;
+  return carve(nullptr, tokens).total;
+}
+
+extern "C" int ako4x_moe_ds_routing(const float* routing_logits, const void* routing_bias,
+                                    int bias_is_bf16, float routed_scaling_factor, int32_t* topk_ids,
+                                    float* topk_weights, int64_t tokens, void* stream) {
+  if (tokens < 0 || tokens > 0x7fffffffLL / NE) return AKO4X_EINVAL;
+  if (tokens == 0) return AKO4X_OK;
+  if (!routing_logits || !routing_bias || !topk_ids || !topk_weights) return AKO4X_EINVAL;
+  if (((uintptr_t)routing_logits | (uintptr_t)routing_bias) & 15) return AKO4X_EINVAL;
+  moe_routing_kernel<<<(unsigned)ako::cdiv(tokens, 4), 128, 0, (cudaStream_t)stream>>>(
+      routing_logits, routing_bias, bias_is_bf16, routed_scaling_factor, (int)tokens, topk_ids,
+      topk_weights, nullptr, nullptr, 0, 0);
+  AKO_CHECK_LAUNCH();
+  return AKO4X_OK;
+}
+
+extern "C" int ako4x_moe_fp8_block_scale(const float* routing_logits, const void* routing_bias,
+                                         int bias_is_bf16, const void* hidden_states,
+                                         const float* hidden_states_scale, const void* gemm1_weights,
+                                         const float* gemm1_weights_scale, const void* gemm2_weights,
+                                         const float* gemm2_weights_scale, int32_t local_expert_offset,
+                                         float routed_scaling_factor, void* out, int64_t tokens,
+                                         int64_t num_local_experts, void* workspace,
+                                         size_t workspace_bytes, void* stream) {
+  if (tokens < 0 || tokens > (1 << 24) || num_local_experts < 1 || num_local_experts > MAX_LOCAL)
+    return AKO4X_EINVAL;
+  if (tokens == 0) return AKO4X_OK;
+  if (!routing_logits || !routing_bias || !hidden_states || !hidden_states_scale || !gemm1_weights ||
+      !gemm1_weights_scale || !gemm2_weights || !gemm2_weights_scale || !out)
+    return AKO4X_EINVAL;
+  if (((uintptr_t)routing_logits | (uintptr_t)routing_bias | (uintptr_t)hidden_states |
+       (uintptr_t)gemm1_weights | (uintptr_t)gemm2_weights | (uintptr_t)out) & 15)
+    return AKO4X_EINVAL;
+  const size_t need = ako4x_moe_fp8_block_scale_workspace_bytes(tokens, num_local_experts);
+  if (!workspace || workspace_bytes < need || ((uintptr_t)workspace & 255)) return AKO4X_EWORKSPACE;
+  cudaStream_t st = (cudaStream_t)stream;
+  Workspace w = carve(workspace, tokens);
+  const int n_local = (int)num_local_experts;
+  const int64_t cap = tokens * TOPK;
+
+  if (cudaMemsetAsync(w.counts, 0, MAX_LOCAL * sizeof(int32_t), st) != cudaSuccess) return AKO4X_ELAUNCH;
+  moe_routing_kernel<<<(unsigned)ako::cdiv(tokens, 4), 128, 0, st>>>(
+      routing_logits, routing_bias, bias_is_bf16, routed_scaling_factor, (int)tokens, w.topk_ids,
+      w.topk_w, w.pair_pos, w.counts, local_expert_offset, n_local);
+  AKO_CHECK_LAUNCH();
+  moe_scatter_kernel<<<n_local, 1024, 0, st>>>(w.topk_ids, w.counts, w.offsets, w.sorted_token,
+                                                w.pair_pos, (int)tokens, local_expert_offset, n_local);
+  AKO_CHECK_LAUNCH();
+
+  GemmParams p1 = {};
+  p1.a = (const uint8_t*)hidden_states;
+  p1.a_scale = hidden_states_scale;
+  p1.w = (const uint8_t*)gemm1_weights;
+  p1.w_scale = gemm1_weights_scale;
+  p1.counts = w.counts;
+  p1.offsets = w.offsets;
+  p1.sorted_token = w.sorted_token;
+  p1.hq = w.hq;
+  p1.h_scale = w.h_scale;
+  p1.a_scale_stride = tokens;
+  p1.h_scale_stride = cap;
+  p1.n_local = n_local;
+  GemmParams p2 = p1;
+  p2.a = w.hq;
+  p2.a_scale = w.h_scale;
+  p2.w = (const uint8_t*)gemm2_weights;
+  p2.w_scale = gemm2_weights_scale;
+  p2.y = w.y;
+  p2.a_scale_stride = cap;
+  const int sms = sm_count();
+  int rc;
+  // average rows per local expert ~ tokens * 8 / 256
+  if (tokens >= 1024) rc = launch_gemms<2>(p1, p2, sms, st);
+  else rc = launch_gemms<1>(p1, p2, sms, st);
+  if (rc != AKO4X_OK) return rc;
+  moe_combine_kernel<<<(unsigned)tokens, 256, 0, st>>>(w.y, w.pair_pos, w.topk_w, (__nv_bfloat16*)out);
+  AKO_CHECK_LAUNCH();
+  return AKO4X_OK;
+}
