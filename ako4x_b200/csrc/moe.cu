@@ -538,13 +538,41 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(
   }
 }
 
-template <int WM>
-int launch_gemms(const GemmParams& p1, const GemmParams& p2, int sms, cudaStream_t st) {
+// Expert-parallel combine: out[t] = bf16( sum over ranks g, ascending, of rows[pos[t,g]] ), fp32
+// accumulation, pos < 0 skipped. `cols` is a multiple of 8.
+__global__ void __launch_bounds__(256) moe_ep_combine_kernel(
+    const __nv_bfloat16* __restrict__ rows, const int32_t* __restrict__ pos,
+    __nv_bfloat16* __restrict__ out, int world, int cols) {
+  const int64_t tkn = blockIdx.x;
+  for (int c = threadIdx.x * 8; c < cols; c += 256 * 8) {
+    float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int g = 0; g < world; ++g) {
+      const int p = pos[tkn * world + g];
+      if (p < 0) continue;
+      const uint4 v = *reinterpret_cast<const uint4*>(rows + (int64_t)p * cols + c);
+      const uint32_t* w = reinterpret_cast<const uint32_t*>(&v);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        a[2 * i] += ako::bf16_lo(w[i]);
+        a[2 * i + 1] += ako::bf16_hi(w[i]);
+      }
+    }
+    uint4 o;
+    uint32_t* q = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) q[i] = ako::pack_bf16x2(a[2 * i], a[2 * i + 1]);
+    *reinterpret_cast<uint4*>(out + tkn * cols + c) = o;
+  }
+}
+
+template <int WM, typename Mark>
+int launch_gemms(const GemmParams& p1, const GemmParams& p2, int sms, cudaStream_t st, Mark mark) {
   using C = GemmCfg<WM>;
   if (!ako::ensure_dynamic_smem<moe_grouped_gemm_kernel<WM, 1>>(C::SMEM)) return AKO4X_ELAUNCH;
   if (!ako::ensure_dynamic_smem<moe_grouped_gemm_kernel<WM, 2>>(C::SMEM)) return AKO4X_ELAUNCH;
   moe_grouped_gemm_kernel<WM, 1><<<sms, C::THREADS, C::SMEM, st>>>(p1);
   AKO_CHECK_LAUNCH();
+  mark(2);
   moe_grouped_gemm_kernel<WM, 2><<<sms, C::THREADS, C::SMEM, st>>>(p2);
   AKO_CHECK_LAUNCH();
   return AKO4X_OK;
@@ -584,14 +612,15 @@ extern "C" int ako4x_moe_ds_routing(const float* routing_logits, const void* rou
   return AKO4X_OK;
 }
 
-extern "C" int ako4x_moe_fp8_block_scale(const float* routing_logits, const void* routing_bias,
-                                         int bias_is_bf16, const void* hidden_states,
-                                         const float* hidden_states_scale, const void* gemm1_weights,
-                                         const float* gemm1_weights_scale, const void* gemm2_weights,
-                                         const float* gemm2_weights_scale, int32_t local_expert_offset,
-                                         float routed_scaling_factor, void* out, int64_t tokens,
-                                         int64_t num_local_experts, void* workspace,
-                                         size_t workspace_bytes, void* stream) {
+extern "C" int ako4x_moe_fp8_block_scale_staged(
+    const float* routing_logits, const void* routing_bias, int bias_is_bf16, const void* hidden_states,
+    const float* hidden_states_scale, const void* gemm1_weights, const float* gemm1_weights_scale,
+    const void* gemm2_weights, const float* gemm2_weights_scale, int32_t local_expert_offset,
+    float routed_scaling_factor, void* out, int64_t tokens, int64_t num_local_experts, void* workspace,
+    size_t workspace_bytes, void* stream, void* const* stage_events) {
+  auto mark = [&](int i) {
+    if (stage_events && stage_events[i]) cudaEventRecord((cudaEvent_t)stage_events[i], (cudaStream_t)stream);
+  };
   if (tokens < 0 || tokens > (1 << 24) || num_local_experts < 1 || num_local_experts > MAX_LOCAL)
     return AKO4X_EINVAL;
   if (tokens == 0) return AKO4X_OK;
@@ -608,6 +637,7 @@ extern "C" int ako4x_moe_fp8_block_scale(const float* routing_logits, const void
   const int n_local = (int)num_local_experts;
   const int64_t cap = tokens * TOPK;
 
+  mark(0);
   if (cudaMemsetAsync(w.counts, 0, MAX_LOCAL * sizeof(int32_t), st) != cudaSuccess) return AKO4X_ELAUNCH;
   moe_routing_kernel<<<(unsigned)ako::cdiv(tokens, 4), 128, 0, st>>>(
       routing_logits, routing_bias, bias_is_bf16, routed_scaling_factor, (int)tokens, w.topk_ids,
@@ -638,12 +668,42 @@ extern "C" int ako4x_moe_fp8_block_scale(const float* routing_logits, const void
   p2.y = w.y;
   p2.a_scale_stride = cap;
   const int sms = sm_count();
+  mark(1);
   int rc;
   // average rows per local expert ~ tokens * 8 / 256
-  if (tokens >= 1024) rc = launch_gemms<2>(p1, p2, sms, st);
-  else rc = launch_gemms<1>(p1, p2, sms, st);
+  if (tokens >= 1024) rc = launch_gemms<2>(p1, p2, sms, st, mark);
+  else rc = launch_gemms<1>(p1, p2, sms, st, mark);
   if (rc != AKO4X_OK) return rc;
+  mark(3);
   moe_combine_kernel<<<(unsigned)tokens, 256, 0, st>>>(w.y, w.pair_pos, w.topk_w, (__nv_bfloat16*)out);
+  AKO_CHECK_LAUNCH();
+  mark(4);
+  return AKO4X_OK;
+}
+
+extern "C" int ako4x_moe_fp8_block_scale(const float* routing_logits, const void* routing_bias,
+                                         int bias_is_bf16, const void* hidden_states,
+                                         const float* hidden_states_scale, const void* gemm1_weights,
+                                         const float* gemm1_weights_scale, const void* gemm2_weights,
+                                         const float* gemm2_weights_scale, int32_t local_expert_offset,
+                                         float routed_scaling_factor, void* out, int64_t tokens,
+                                         int64_t num_local_experts, void* workspace,
+                                         size_t workspace_bytes, void* stream) {
+  return ako4x_moe_fp8_block_scale_staged(
+      routing_logits, routing_bias, bias_is_bf16, hidden_states, hidden_states_scale, gemm1_weights,
+      gemm1_weights_scale, gemm2_weights, gemm2_weights_scale, local_expert_offset,
+      routed_scaling_factor, out, tokens, num_local_experts, workspace, workspace_bytes, stream,
+      nullptr);
+}
+
+extern "C" int ako4x_moe_ep_combine(const void* rows, const int32_t* pos, void* out, int64_t tokens,
+                                    int64_t world, int64_t cols, void* stream) {
+  if (tokens < 0 || world < 1 || cols < 8 || (cols & 7) || tokens > 0x7fffffffLL) return AKO4X_EINVAL;
+  if (tokens == 0) return AKO4X_OK;
+  if (!pos || !out) return AKO4X_EINVAL;  // rows may be null when no row was received
+  if (((uintptr_t)rows | (uintptr_t)out) & 15) return AKO4X_EINVAL;
+  moe_ep_combine_kernel<<<(unsigned)tokens, 256, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)rows, pos, (__nv_bfloat16*)out, (int)world, (int)cols);
   AKO_CHECK_LAUNCH();
   return AKO4X_OK;
 }

@@ -60,6 +60,21 @@ def run(routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_
 
 
 @torch.no_grad()
+def ep_combine(rows, pos):
+    """Expert-parallel combine: out[t] = bf16(sum over ranks, ascending, of rows[pos[t, g]])."""
+    tokens, world = pos.shape
+    cols = rows.shape[1]
+    if rows.dtype != torch.bfloat16 or pos.dtype != torch.int32:
+        raise _cabi.Ako4xError("ep_combine: rows bf16 [n, cols], pos int32 [tokens, world]")
+    out = torch.empty((tokens, cols), dtype=torch.bfloat16, device=pos.device)
+    st = _cabi.lib().ako4x_moe_ep_combine(
+        _cabi.ptr(rows.contiguous()) if rows.numel() else None, _cabi.ptr(pos.contiguous()),
+        _cabi.ptr(out), tokens, world, cols, _cabi.stream())
+    _cabi.check(st, "ako4x_moe_ep_combine")
+    return out
+
+
+@torch.no_grad()
 def ds_routing(routing_logits, routing_bias, routed_scaling_factor):
     """The routing stage alone: (topk_ids int32 [tokens,8] ascending, topk_weights fp32 [tokens,8])."""
     tokens = routing_logits.shape[0]

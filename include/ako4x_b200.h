@@ -148,12 +148,30 @@ int ako4x_moe_fp8_block_scale(const float* routing_logits, const void* routing_b
                               float routed_scaling_factor, void* out, int64_t tokens,
                               int64_t num_local_experts, void* workspace, size_t workspace_bytes,
                               void* stream);
+/* The same call with measurement hooks: `stage_events` is NULL or an array of 5 cudaEvent_t
+ * (as void*, entries may be NULL) recorded on `stream` before routing [0], before GEMM1 [1],
+ * between GEMM1 and GEMM2 [2], after GEMM2 [3] and after the combine [4]. */
+int ako4x_moe_fp8_block_scale_staged(const float* routing_logits, const void* routing_bias,
+                                     int bias_is_bf16, const void* hidden_states,
+                                     const float* hidden_states_scale, const void* gemm1_weights,
+                                     const float* gemm1_weights_scale, const void* gemm2_weights,
+                                     const float* gemm2_weights_scale, int32_t local_expert_offset,
+                                     float routed_scaling_factor, void* out, int64_t tokens,
+                                     int64_t num_local_experts, void* workspace,
+                                     size_t workspace_bytes, void* stream, void* const* stage_events);
 /* Routing alone (same arithmetic as the first stage of the call above): the 8 selected global
  * expert ids per token in ascending id order and their weights. topk_ids int32 [tokens,8];
  * topk_weights fp32 [tokens,8]. Reference: fused_routing_v2/kernel.py:350-391. */
 int ako4x_moe_ds_routing(const float* routing_logits, const void* routing_bias, int bias_is_bf16,
                          float routed_scaling_factor, int32_t* topk_ids, float* topk_weights,
                          int64_t tokens, void* stream);
+
+/* Expert-parallel combine (no counterpart in the reference, which is single-GPU): out[t] =
+ * bf16(sum over ranks g in ascending order of rows[pos[t,g]]) with fp32 accumulation; entries
+ * pos < 0 are skipped. rows bf16 [n, cols]; pos int32 [tokens, world]; out bf16 [tokens, cols];
+ * cols a multiple of 8. */
+int ako4x_moe_ep_combine(const void* rows, const int32_t* pos, void* out, int64_t tokens,
+                         int64_t world, int64_t cols, void* stream);
 
 #ifdef __cplusplus
 }
