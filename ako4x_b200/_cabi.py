@@ -22,6 +22,7 @@ STATUS = {
     -2: "AKO4X_EUNSUPPORTED_SHAPE",
     -3: "AKO4X_ELAUNCH",
     -4: "AKO4X_EWORKSPACE",
+    -5: "AKO4X_ETOOLARGE",
 }
 
 
@@ -64,6 +65,8 @@ _SIGNATURES = {
     "ako4x_rmsnorm_h128": (_INT, [_P, _P, _P, _I64, _P]),
     "ako4x_gqa_paged_decode_workspace_bytes": (_SZ, [_I64, _I64, _I64]),
     "ako4x_gqa_paged_decode": (_INT, [_P, _P, _P, _P, _P, _F32, _P, _P, _I64, _I64, _I64, _P, _SZ, _P]),
+    "ako4x_gqa_paged_decode_noalloc_max_scratch_bytes": (_SZ, []),
+    "ako4x_gqa_paged_decode_noalloc": (_INT, [_P, _P, _P, _P, _P, _F32, _P, _P, _I64, _I64, _I64, _P]),
     "ako4x_mla_paged_decode_workspace_bytes": (_SZ, [_I64, _I64, _I64]),
     "ako4x_mla_paged_decode": (_INT, [_P, _P, _P, _P, _P, _P, _F32, _P, _P, _I64, _I64, _I64, _P, _SZ, _P]),
     "ako4x_mla_paged_prefill_workspace_bytes": (_SZ, [_I64, _I64, _I64, _I64]),

@@ -30,6 +30,7 @@ extern "C" {
 #define AKO4X_EUNSUPPORTED_SHAPE (-2) /* a compile-time dimension (heads, head_dim, ...) differs */
 #define AKO4X_ELAUNCH (-3)           /* the CUDA runtime refused a launch */
 #define AKO4X_EWORKSPACE (-4)        /* workspace_bytes smaller than *_workspace_bytes() */
+#define AKO4X_ETOOLARGE (-5)         /* a fixed internal limit (built-in scratch) is exceeded */
 
 /* Version of this ABI; bumped when a signature changes. */
 int ako4x_abi_version(void);
@@ -57,6 +58,21 @@ int ako4x_gqa_paged_decode(const void* q, const void* k_cache, const void* v_cac
                            void* o, float* lse, int64_t batch, int64_t num_kv_indices,
                            int64_t page_size, void* workspace, size_t workspace_bytes,
                            void* stream);
+
+/* The same operator for callers that have no scratch memory to pass and cannot allocate any (a
+ * plug-in host that supplies only input and output tensors; a serving process whose HBM is fully
+ * committed to its KV-cache pool). It has no counterpart in the reference. The split-KV partials
+ * live in a 16 MiB array inside the library image (held by every GPU that loads the library);
+ * ako4x_gqa_paged_decode_noalloc_max_scratch_bytes() returns that limit. A call that would need
+ * more (compare ako4x_gqa_paged_decode_workspace_bytes) returns AKO4X_ETOOLARGE and launches
+ * nothing. Calls on one device share the array: calls that can overlap on the GPU race, so keep
+ * them on one stream. The first call on a device looks up the array's address; make it at
+ * start-up, before any stream capture. Nothing is allocated or freed by this call. */
+size_t ako4x_gqa_paged_decode_noalloc_max_scratch_bytes(void);
+int ako4x_gqa_paged_decode_noalloc(const void* q, const void* k_cache, const void* v_cache,
+                                   const int32_t* kv_indptr, const int32_t* kv_indices,
+                                   float sm_scale, void* o, float* lse, int64_t batch,
+                                   int64_t num_kv_indices, int64_t page_size, void* stream);
 
 /* ---- a3. Paged MLA decode, 16 heads, ckv 512, kpe 64 ---------------------------------------
  * Replaces run(q_nope, q_pe, ckv_cache, kpe_cache, kv_indptr, kv_indices, sm_scale):
