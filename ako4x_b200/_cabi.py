@@ -80,6 +80,7 @@ _SIGNATURES = {
     "ako4x_moe_fp8_block_scale_workspace_bytes": (_SZ, [_I64, _I64]),
     "ako4x_moe_fp8_block_scale": (_INT, [_P, _P, _INT, _P, _P, _P, _P, _P, _P, _I32, _F32, _P, _I64, _I64, _P, _SZ, _P]),
     "ako4x_moe_fp8_block_scale_staged": (_INT, [_P, _P, _INT, _P, _P, _P, _P, _P, _P, _I32, _F32, _P, _I64, _I64, _P, _SZ, _P, _P]),
+    "ako4x_moe_fp8_block_scale_status_offset": (_SZ, [_I64]),
     "ako4x_moe_ds_routing": (_INT, [_P, _P, _INT, _F32, _P, _P, _I64, _P]),
     "ako4x_moe_ep_combine": (_INT, [_P, _P, _P, _I64, _I64, _I64, _P]),
 }

@@ -18,7 +18,10 @@
 // The grouped GEMM is persistent: each CTA walks a tile list (expert, n-tile, m-tile) derived from
 // the per-expert counts; tiles are 32*WM rows x 256 weight rows x 128 (one scale block) per step,
 // fed by a 4-stage cp.async ring with XOR-swizzled 128-byte rows and mma.sync.m16n8k32 e4m3.
+#include <cstdlib>
+
 #include "common.cuh"
+#include "tcgen05.cuh"
 
 namespace {
 
@@ -57,7 +60,7 @@ Workspace carve(void* base, int64_t tokens) {
   w.topk_ids = (int32_t*)take(cap * 4);
   w.topk_w = (float*)take(cap * 4);
   w.pair_pos = (int32_t*)take(cap * 4);
-  w.counts = (int32_t*)take(MAX_LOCAL * 4);
+  w.counts = (int32_t*)take((MAX_LOCAL + 64) * 4);  // counts, then the error word (zeroed together)
   w.offsets = (int32_t*)take((MAX_LOCAL + 1) * 4);
   w.sorted_token = (int32_t*)take(cap * 4);
   w.h_scale = (float*)take(16 * cap * 4);
@@ -270,6 +273,7 @@ struct GemmParams {
   float* y;                  // GEMM2 out
   int64_t a_scale_stride;    // T (GEMM1) or cap (GEMM2)
   int64_t h_scale_stride;    // cap: row stride of the h_scale GEMM1 writes
+  int* error;                // device word, 0 = ok; set when a bounded wait gave up
   int n_local;
 };
 
@@ -508,6 +512,9 @@ __global__ void __launch_bounds__(GemmCfg<WM>::THREADS, 1) moe_grouped_gemm_kern
   }
 }
 
+// The tcgen05 / TMEM form of the grouped GEMM (same GemmParams, same tile-list convention).
+#include "moe_gemm_tc.cuh"
+
 // ---------------------------------------------------------------------------------------------
 // 5. combine
 // ---------------------------------------------------------------------------------------------
@@ -578,6 +585,18 @@ int launch_gemms(const GemmParams& p1, const GemmParams& p2, int sms, cudaStream
   return AKO4X_OK;
 }
 
+template <typename Mark>
+int launch_gemms_tc(const GemmParams& p1, const GemmParams& p2, int sms, cudaStream_t st, Mark mark) {
+  if (!ako::ensure_dynamic_smem<moe_gemm_tc_kernel<1>>(TC_SMEM)) return AKO4X_ELAUNCH;
+  if (!ako::ensure_dynamic_smem<moe_gemm_tc_kernel<2>>(TC_SMEM)) return AKO4X_ELAUNCH;
+  moe_gemm_tc_kernel<1><<<sms, TC_THREADS, TC_SMEM, st>>>(p1);
+  AKO_CHECK_LAUNCH();
+  mark(2);
+  moe_gemm_tc_kernel<2><<<sms, TC_THREADS, TC_SMEM, st>>>(p2);
+  AKO_CHECK_LAUNCH();
+  return AKO4X_OK;
+}
+
 int sm_count() {
   static int cached[64] = {};
   int dev = 0;
@@ -596,6 +615,12 @@ extern "C" size_t ako4x_moe_fp8_block_scale_workspace_bytes(int64_t tokens, int6
   (void)num_local_experts;
   if (tokens <= 0) return 0;
   return carve(nullptr, tokens).total;
+}
+
+extern "C" size_t ako4x_moe_fp8_block_scale_status_offset(int64_t tokens) {
+  if (tokens <= 0) return 0;
+  const Workspace w = carve(nullptr, tokens);
+  return (size_t)((uintptr_t)(w.counts + MAX_LOCAL));
 }
 
 extern "C" int ako4x_moe_ds_routing(const float* routing_logits, const void* routing_bias,
@@ -638,7 +663,7 @@ extern "C" int ako4x_moe_fp8_block_scale_staged(
   const int64_t cap = tokens * TOPK;
 
   mark(0);
-  if (cudaMemsetAsync(w.counts, 0, MAX_LOCAL * sizeof(int32_t), st) != cudaSuccess) return AKO4X_ELAUNCH;
+  if (cudaMemsetAsync(w.counts, 0, (MAX_LOCAL + 64) * sizeof(int32_t), st) != cudaSuccess) return AKO4X_ELAUNCH;
   moe_routing_kernel<<<(unsigned)ako::cdiv(tokens, 4), 128, 0, st>>>(
       routing_logits, routing_bias, bias_is_bf16, routed_scaling_factor, (int)tokens, w.topk_ids,
       w.topk_w, w.pair_pos, w.counts, local_expert_offset, n_local);
@@ -659,6 +684,7 @@ extern "C" int ako4x_moe_fp8_block_scale_staged(
   p1.h_scale = w.h_scale;
   p1.a_scale_stride = tokens;
   p1.h_scale_stride = cap;
+  p1.error = w.counts + MAX_LOCAL;
   p1.n_local = n_local;
   GemmParams p2 = p1;
   p2.a = w.hq;
@@ -671,7 +697,12 @@ extern "C" int ako4x_moe_fp8_block_scale_staged(
   mark(1);
   int rc;
   // average rows per local expert ~ tokens * 8 / 256
-  if (tokens >= 1024) rc = launch_gemms<2>(p1, p2, sms, st, mark);
+  static const bool legacy_mma = [] {
+    const char* v = getenv("AKO4X_MOE_LEGACY_MMA");  // development A/B switch only
+    return v && v[0] == '1';
+  }();
+  if (!legacy_mma) rc = launch_gemms_tc(p1, p2, sms, st, mark);
+  else if (tokens >= 1024) rc = launch_gemms<2>(p1, p2, sms, st, mark);
   else rc = launch_gemms<1>(p1, p2, sms, st, mark);
   if (rc != AKO4X_OK) return rc;
   mark(3);

@@ -23,7 +23,7 @@ def _scalar(v):
 @torch.no_grad()
 def run(routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights,
         gemm1_weights_scale, gemm2_weights, gemm2_weights_scale, local_expert_offset,
-        routed_scaling_factor):
+        routed_scaling_factor, _check_status=False):
     tokens = hidden_states.shape[0]
     n_local = gemm1_weights.shape[0]
     if routing_logits.shape != (tokens, NUM_EXPERTS) or routing_logits.dtype != torch.float32:
@@ -56,7 +56,17 @@ def run(routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_
         float(_scalar(routed_scaling_factor)), _cabi.ptr(out), tokens, n_local, _cabi.ptr(ws),
         ws_bytes, _cabi.stream())
     _cabi.check(st, "ako4x_moe_fp8_block_scale")
+    if _check_status:
+        off = L.ako4x_moe_fp8_block_scale_status_offset(tokens)
+        code = int(ws[off:off + 4].view(torch.int32).item())   # synchronises: tests only
+        if code != 0:
+            raise _cabi.Ako4xError(f"moe: a bounded device wait gave up (status {code})")
     return out
+
+
+def run_checked(*args):
+    """``run`` followed by a read of the device status word (synchronises the stream)."""
+    return run(*args, _check_status=True)
 
 
 @torch.no_grad()

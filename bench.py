@@ -379,7 +379,7 @@ def run_reference(args):
 # ---------------------------------------------------------------------------------------------
 def run_moe(args, rank, world, dist_on, peaks):
     from ako4x_b200 import moe
-    T = MOE_TOKENS
+    T = args.tokens
     a = moe_inputs(T, rank, "cuda")
     if world > 1:
         from ako4x_b200 import moe_ep
@@ -516,6 +516,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--op", default="moe", choices=["moe", "gqa_decode", "mla_decode"])
+    ap.add_argument("--tokens", type=int, default=MOE_TOKENS,
+                    help="MoE tokens per GPU (default: the benchmark configuration, 8192)")
     ap.add_argument("--no-ops-table", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()

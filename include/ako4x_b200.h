@@ -164,6 +164,11 @@ int ako4x_moe_fp8_block_scale(const float* routing_logits, const void* routing_b
                               float routed_scaling_factor, void* out, int64_t tokens,
                               int64_t num_local_experts, void* workspace, size_t workspace_bytes,
                               void* stream);
+/* Byte offset, inside a workspace for `tokens`, of a 32-bit status word that the call leaves at
+ * 0 on success. The tensor-core GEMM kernels bound every wait on an mbarrier; a wait that runs out
+ * of its cycle budget stores a non-zero code there (1 producer, 2/3 MMA issuer, 4 epilogue) and the
+ * kernel unwinds instead of hanging. A caller may read the word after synchronising the stream. */
+size_t ako4x_moe_fp8_block_scale_status_offset(int64_t tokens);
 /* The same call with measurement hooks: `stage_events` is NULL or an array of 5 cudaEvent_t
  * (as void*, entries may be NULL) recorded on `stream` before routing [0], before GEMM1 [1],
  * between GEMM1 and GEMM2 [2], after GEMM2 [3] and after the combine [4]. */

@@ -89,7 +89,7 @@ def test_routing_ties_bit_exact(built_lib):
 @pytest.mark.parametrize("tokens,offset", [(1, 0), (7, 0), (128, 0), (128, 96), (1024, 32)])
 def test_against_oracle(built_lib, weights, tokens, offset):
     a = _case(weights, tokens, shape_id=tokens % 67 + offset, offset=offset)
-    out = moe.run(*[a[k] for k in KEYS])
+    out = moe.run_checked(*[a[k] for k in KEYS])
     ref = _oracle(a)
     assert out.shape == ref.shape and out.dtype == torch.bfloat16
     if float(ref.float().abs().max()) == 0.0:   # no token routed to a local expert
@@ -105,18 +105,18 @@ def test_against_oracle(built_lib, weights, tokens, offset):
 def test_skewed_routing(built_lib, weights):
     """A skewed logit set loads a few experts with many rows (several m-tiles per expert)."""
     a = _case(weights, 512, shape_id=3, offset=0, skew=3.0)
-    out = moe.run(*[a[k] for k in KEYS])
+    out = moe.run_checked(*[a[k] for k in KEYS])
     fro, strict, harness = _report(out, _oracle(a))
     assert fro <= REL_FROBENIUS_MAX and harness >= HARNESS_MATCH_MIN
 
 
 def test_deterministic_and_no_stale_state(built_lib, weights):
     a = _case(weights, 256, shape_id=5)
-    o1 = moe.run(*[a[k] for k in KEYS]).clone()
-    o2 = moe.run(*[a[k] for k in KEYS])
+    o1 = moe.run_checked(*[a[k] for k in KEYS]).clone()
+    o2 = moe.run_checked(*[a[k] for k in KEYS])
     assert torch.equal(o1, o2), "same inputs must give identical bits (no atomics in the sums)"
     a["routing_logits"].copy_(a["routing_logits"].flip(0))
-    o3 = moe.run(*[a[k] for k in KEYS])
+    o3 = moe.run_checked(*[a[k] for k in KEYS])
     assert not torch.equal(o1, o3), "refilled buffers must be recomputed"
 
 
@@ -124,7 +124,7 @@ def test_expert_partition_linearity_full_size(built_lib, weights):
     """T = 8192 (full size, no oracle): a token row is zero exactly when none of its 8 experts is
     local, and the result is finite."""
     a = _case(weights, 8192, shape_id=8, offset=64)
-    out = moe.run(*[a[k] for k in KEYS])
+    out = moe.run_checked(*[a[k] for k in KEYS])
     assert torch.isfinite(out.float()).all()
     ids, _ = moe.ds_routing(a["routing_logits"], a["routing_bias"], 2.5)
     local = ((ids >= 64) & (ids < 96)).any(dim=1)
