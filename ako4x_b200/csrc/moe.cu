@@ -18,6 +18,8 @@
 // The grouped GEMM is persistent: each CTA walks a tile list (expert, n-tile, m-tile) derived from
 // the per-expert counts; tiles are 32*WM rows x 256 weight rows x 128 (one scale block) per step,
 // fed by a 4-stage cp.async ring with XOR-swizzled 128-byte rows and mma.sync.m16n8k32 e4m3.
+#include <cuda.h>  // CUtensorMap and its enums (types only; the encoder is fetched at run time)
+
 #include <cstdlib>
 
 #include "common.cuh"
@@ -43,6 +45,8 @@ struct Workspace {
   int32_t* offsets;       // [MAX_LOCAL+1]
   int32_t* sorted_token;  // [cap]
   float* h_scale;         // [16][cap]
+  uint8_t* xs;            // [cap][7168]  activations in expert-sorted row order
+  float* xs_scale;        // [56][cap]
   uint8_t* hq;            // [cap][4096]  (hi piece | lo piece)
   float* y;               // [cap][7168]
   size_t total;
@@ -64,6 +68,8 @@ Workspace carve(void* base, int64_t tokens) {
   w.offsets = (int32_t*)take((MAX_LOCAL + 1) * 4);
   w.sorted_token = (int32_t*)take(cap * 4);
   w.h_scale = (float*)take(16 * cap * 4);
+  w.xs = (uint8_t*)take(cap * (size_t)HID);
+  w.xs_scale = (float*)take((size_t)KB1 * cap * 4);
   w.hq = (uint8_t*)take(cap * 2 * INTER);
   w.y = (float*)take(cap * (size_t)HID * 4);
   w.total = p - (uintptr_t)base;
@@ -512,6 +518,57 @@ __global__ void __launch_bounds__(GemmCfg<WM>::THREADS, 1) moe_grouped_gemm_kern
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// 2b. permute: copy every (token, local expert) pair's activation row and its 56 scales into
+//     expert-sorted order, so that a GEMM tile's A operand is one contiguous TMA box.
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) moe_permute_kernel(
+    const uint8_t* __restrict__ x, const float* __restrict__ x_scale, const int32_t* __restrict__ pair_pos,
+    uint8_t* __restrict__ xs, float* __restrict__ xs_scale, int tokens, int64_t cap) {
+  const int lane = threadIdx.x & 31;
+  const int64_t slot = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);  // token*8 + k
+  if (slot >= (int64_t)tokens * TOPK) return;
+  const int pos = pair_pos[slot];
+  if (pos < 0) return;
+  const int64_t t = slot / TOPK;
+  const uint4* src = reinterpret_cast<const uint4*>(x + t * HID);
+  uint4* dst = reinterpret_cast<uint4*>(xs + (int64_t)pos * HID);
+#pragma unroll
+  for (int i = 0; i < HID / 16 / 32; ++i) dst[i * 32 + lane] = __ldg(src + i * 32 + lane);
+  for (int kb = lane; kb < KB1; kb += 32) xs_scale[(int64_t)kb * cap + pos] = x_scale[(int64_t)kb * tokens + t];
+}
+
+// ---- TMA descriptors (host) ---------------------------------------------------------------------
+typedef CUresult (*TensorMapEncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                           const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                           const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                           CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+TensorMapEncodeTiledFn tensor_map_encoder() {
+  static TensorMapEncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      return (TensorMapEncodeTiledFn) nullptr;
+    return (TensorMapEncodeTiledFn)p;
+  }();
+  return fn;
+}
+
+// Byte matrix [rows, row_bytes] (row-major), box = 128 bytes x box_rows, 128-byte swizzle.
+bool make_byte_matrix_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t row_bytes, uint32_t box_rows) {
+  TensorMapEncodeTiledFn enc = tensor_map_encoder();
+  if (!enc) return false;
+  const cuuint64_t dims[2] = {row_bytes, rows};
+  const cuuint64_t strides[1] = {row_bytes};
+  const cuuint32_t box[2] = {128u, box_rows};
+  const cuuint32_t estr[2] = {1u, 1u};
+  return enc(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 // The tcgen05 / TMEM form of the grouped GEMM (same GemmParams, same tile-list convention).
 #include "moe_gemm_tc.cuh"
 
@@ -585,14 +642,22 @@ int launch_gemms(const GemmParams& p1, const GemmParams& p2, int sms, cudaStream
   return AKO4X_OK;
 }
 
+// p1 / p2 are the GEMM1 / GEMM2 parameters with the expert-sorted activation copy as A.
 template <typename Mark>
-int launch_gemms_tc(const GemmParams& p1, const GemmParams& p2, int sms, cudaStream_t st, Mark mark) {
+int launch_gemms_tc(const GemmParams& p1, const GemmParams& p2, int64_t cap, int n_local, int sms,
+                    cudaStream_t st, Mark mark) {
   if (!ako::ensure_dynamic_smem<moe_gemm_tc_kernel<1>>(TC_SMEM)) return AKO4X_ELAUNCH;
   if (!ako::ensure_dynamic_smem<moe_gemm_tc_kernel<2>>(TC_SMEM)) return AKO4X_ELAUNCH;
-  moe_gemm_tc_kernel<1><<<sms, TC_THREADS, TC_SMEM, st>>>(p1);
+  CUtensorMap a1, b1, a2, b2;
+  if (!make_byte_matrix_map(&a1, p1.a, (uint64_t)cap, HID, TC_BM) ||
+      !make_byte_matrix_map(&b1, p1.w, (uint64_t)n_local * 2 * INTER, HID, 64) ||
+      !make_byte_matrix_map(&a2, p2.a, (uint64_t)cap, 2 * INTER, TC_BM) ||
+      !make_byte_matrix_map(&b2, p2.w, (uint64_t)n_local * HID, INTER, TC_BN))
+    return AKO4X_ELAUNCH;
+  moe_gemm_tc_kernel<1><<<sms, TC_THREADS, TC_SMEM, st>>>(p1, a1, b1);
   AKO_CHECK_LAUNCH();
   mark(2);
-  moe_gemm_tc_kernel<2><<<sms, TC_THREADS, TC_SMEM, st>>>(p2);
+  moe_gemm_tc_kernel<2><<<sms, TC_THREADS, TC_SMEM, st>>>(p2, a2, b2);
   AKO_CHECK_LAUNCH();
   return AKO4X_OK;
 }
@@ -701,8 +766,16 @@ extern "C" int ako4x_moe_fp8_block_scale_staged(
     const char* v = getenv("AKO4X_MOE_LEGACY_MMA");  // development A/B switch only
     return v && v[0] == '1';
   }();
-  if (!legacy_mma) rc = launch_gemms_tc(p1, p2, sms, st, mark);
-  else if (tokens >= 1024) rc = launch_gemms<2>(p1, p2, sms, st, mark);
+  if (!legacy_mma) {
+    moe_permute_kernel<<<(unsigned)ako::cdiv(tokens * TOPK, 8), 256, 0, st>>>(
+        (const uint8_t*)hidden_states, hidden_states_scale, w.pair_pos, w.xs, w.xs_scale, (int)tokens, cap);
+    AKO_CHECK_LAUNCH();
+    GemmParams t1 = p1;
+    t1.a = w.xs;
+    t1.a_scale = w.xs_scale;
+    t1.a_scale_stride = cap;
+    rc = launch_gemms_tc(t1, p2, cap, n_local, sms, st, mark);
+  } else if (tokens >= 1024) rc = launch_gemms<2>(p1, p2, sms, st, mark);
   else rc = launch_gemms<1>(p1, p2, sms, st, mark);
   if (rc != AKO4X_OK) return rc;
   mark(3);

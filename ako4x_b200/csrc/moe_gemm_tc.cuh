@@ -1,38 +1,40 @@
-// Grouped FP8 block-scale GEMM on the 5th-generation tensor cores (tcgen05 + TMEM), included by
-// moe.cu inside its anonymous namespace (it uses GemmParams and the size constants defined there).
+// Grouped FP8 block-scale GEMM on the 5th-generation tensor cores (tcgen05 + TMEM) fed by TMA,
+// included by moe.cu inside its anonymous namespace (it uses GemmParams and the size constants
+// defined there).
 //
 // One persistent CTA per SM walks the tile list (expert, n-tile, m-tile). A tile is 128 rows x 256
 // weight rows; every K step of 128 (one scale block) is four tcgen05.mma M128 N256 K32 e4m3
-// instructions into one of two 256-column TMEM accumulators. 9 warps, two roles:
-//   warp 8      one thread issues the MMAs; tcgen05.commit frees the shared-memory stage and
-//               publishes the TMEM accumulator of the K block;
-//   warps 0-7   256 worker threads. Each iteration g they (1) cp.async their share of K block g+3
-//               (A rows gathered by token in GEMM1, weight rows) into a 4-stage ring of
-//               128-byte-swizzled K-major tiles, (2) wait for their copies of K block g+1, fence them
-//               towards the async proxy and arrive on its `full` barrier, (3) pull the partial
-//               accumulator of K block g out of TMEM (tcgen05.ld), release the buffer, and promote
-//               it into fp32 registers with  a_scale[row, kb] * w_scale[block, kb]  -- the 128x128
-//               block-scale rule. The promotion of block g overlaps the MMAs of block g+1.
-//               Thread (warp w, lane l) owns accumulator row 32*(w%4)+l and columns 128*(w/4)...
+// instructions into one of two 256-column TMEM accumulators. 10 warps, three roles:
+//   warp 9      one thread issues TMA loads (cp.async.bulk.tensor, 128-byte swizzle) of the
+//               activation box (128 rows x 128 B) and the weight boxes (256 rows x 128 B) into a
+//               4-stage shared-memory ring; completion is counted in bytes on the stage's mbarrier;
+//   warp 8      one thread issues the MMAs; tcgen05.commit frees the stage and publishes the TMEM
+//               accumulator of the K block;
+//   warps 0-7   256 promotion threads: per K block they pull the partial accumulator out of TMEM
+//               (tcgen05.ld), release the buffer, and add it into fp32 registers scaled by
+//               a_scale[row, kb] * w_scale[block, kb] -- the 128x128 block-scale rule. Promotion of
+//               block g overlaps the MMAs of block g+1. Thread (warp w, lane l) owns accumulator
+//               row 32*(w%4)+l and columns 128*(w/4)...
+// Activations are read from an expert-sorted copy (rows of one expert contiguous), so a tile's A
+// operand is one TMA box; rows past the expert's count belong to the next expert (or are
+// out-of-bounds zero fill) and only produce accumulator rows that are never stored.
 // GEMM1 orders the weight rows of a tile as [g1 0-63 | g2 0-63 | g1 64-127 | g2 64-127] of one
-// 128-column block of h, so each worker owns matching linear/gate columns and applies SwiGLU, the
-// two-piece e4m3 quantisation and 64-byte row stores by itself. GEMM2 stores fp32 y.
-// No register re-balancing (setmaxnreg) is used: 288 threads leave 224 registers per thread.
-// Every mbarrier wait is bounded; a timeout sets p.error and both roles unwind to a common exit
-// that frees TMEM.
+// 128-column block of h (four 64-row boxes), so each promotion thread owns matching linear/gate
+// columns and applies SwiGLU, the two-piece e4m3 quantisation and 64-byte row stores by itself.
+// GEMM2 stores fp32 y. Every mbarrier wait is bounded; a timeout sets p.error and all roles unwind
+// to a common exit that frees TMEM.
 #pragma once
 // (tcgen05.cuh is included by moe.cu at file scope, before the anonymous namespace opens)
 
 constexpr int TC_BM = 128;
 constexpr int TC_BN = 256;
 constexpr int TC_STAGES = 4;
-constexpr int TC_LAG = 3;                       // K blocks issued ahead of the one being promoted
 constexpr int TC_A_BYTES = TC_BM * 128;
 constexpr int TC_B_BYTES = TC_BN * 128;
 constexpr int TC_STAGE_BYTES = TC_A_BYTES + TC_B_BYTES;
 constexpr int TC_SMEM = TC_STAGES * TC_STAGE_BYTES + 1024;  // + slack for 1024-byte alignment
 constexpr int TC_WORKERS = 256;
-constexpr int TC_THREADS = TC_WORKERS + 32;
+constexpr int TC_THREADS = TC_WORKERS + 64;
 constexpr int TC_TMEM_COLS = 512;
 
 enum : int { kErrLoad = 1, kErrMmaFull = 2, kErrMmaAcc = 3, kErrEpilogue = 4 };
@@ -57,11 +59,10 @@ __device__ __forceinline__ TileInfo tc_tile_info(const GemmParams& p, const int*
 }
 
 template <int WHICH>
-__global__ void __launch_bounds__(TC_THREADS, 1) moe_gemm_tc_kernel(GemmParams p) {
+__global__ void __launch_bounds__(TC_THREADS, 1)
+moe_gemm_tc_kernel(GemmParams p, const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b) {
   constexpr int NKB = (WHICH == 1) ? KB1 : KB2;
   constexpr int NT_TILES = (WHICH == 1) ? (INTER / 128) : (HID / TC_BN);
-  constexpr int64_t W_ROW = (WHICH == 1) ? HID : INTER;      // bytes per weight row
-  constexpr int64_t A_ROW = (WHICH == 1) ? HID : 2 * INTER;  // bytes per activation row
   constexpr uint32_t IDESC = ako::tc::idesc_e4m3_f32(TC_BM, TC_BN);
 
   extern __shared__ unsigned char smem_raw[];
@@ -85,7 +86,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) moe_gemm_tc_kernel(GemmParams p
     }
     s_cum[p.n_local] = acc;
     for (int s = 0; s < TC_STAGES; ++s) {
-      ako::tc::mbar_init(ako::smem_u32(&s_full[s]), TC_WORKERS);
+      ako::tc::mbar_init(ako::smem_u32(&s_full[s]), 1);
       ako::tc::mbar_init(ako::smem_u32(&s_empty[s]), 1);
     }
     for (int b = 0; b < 2; ++b) {
@@ -101,120 +102,76 @@ __global__ void __launch_bounds__(TC_THREADS, 1) moe_gemm_tc_kernel(GemmParams p
   ako::tc::fence_after_thread_sync();
   const uint32_t tmem_base = s_tmem_base;
   const int total_tiles = s_cum[p.n_local] * NT_TILES;
-  // K blocks this CTA runs in total (tiles blockIdx.x, +gridDim.x, ...)
-  const int my_tiles = (total_tiles > (int)blockIdx.x) ? (total_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
-  const int G = my_tiles * NKB;
 
-  if (warp == 8) {
+  if (warp == 9) {
+    // ================================ TMA producer =============================================
+    if (lane == 0) {
+      ako::tc::tma_prefetch_desc(&tm_a);
+      ako::tc::tma_prefetch_desc(&tm_b);
+      int g = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+        const TileInfo ti = tc_tile_info<NT_TILES>(p, s_cum, tile);
+        for (int kb = 0; kb < NKB; ++kb, ++g) {
+          const int stage = g % TC_STAGES;
+          const uint32_t ph = (g / TC_STAGES) & 1;
+          const uint32_t bar = ako::smem_u32(&s_full[stage]);
+          if (!ako::tc::mbar_wait(ako::smem_u32(&s_empty[stage]), ph ^ 1u, p.error, kErrLoad)) { ok = false; break; }
+          const uint32_t sa = smem_base + stage * TC_STAGE_BYTES;
+          const uint32_t sb = sa + TC_A_BYTES;
+          ako::tc::mbar_arrive_expect_tx(bar, TC_STAGE_BYTES);
+          ako::tc::tma_load_2d(sa, &tm_a, kb * 128, ti.row0, bar);
+          if (WHICH == 1) {
+            const int wr = ti.e * (2 * INTER) + ti.nt * 128;
+            ako::tc::tma_load_2d(sb, &tm_b, kb * 128, wr, bar);                         // g1, h cols 0-63
+            ako::tc::tma_load_2d(sb + 64 * 128, &tm_b, kb * 128, wr + INTER, bar);       // g2, h cols 0-63
+            ako::tc::tma_load_2d(sb + 128 * 128, &tm_b, kb * 128, wr + 64, bar);         // g1, 64-127
+            ako::tc::tma_load_2d(sb + 192 * 128, &tm_b, kb * 128, wr + INTER + 64, bar); // g2, 64-127
+          } else {
+            ako::tc::tma_load_2d(sb, &tm_b, (kb & 15) * 128, ti.e * HID + ti.nt * TC_BN, bar);
+          }
+        }
+      }
+    }
+  } else if (warp == 8) {
     // ================================ MMA issuer ===============================================
     if (lane == 0) {
-      for (int g = 0; g < G; ++g) {
-        const int stage = g % TC_STAGES;
-        const uint32_t ph = (g / TC_STAGES) & 1;
-        const int buf = g & 1;
-        const uint32_t aph = (g >> 1) & 1;
-        if (!ako::tc::mbar_wait(ako::smem_u32(&s_acc_empty[buf]), aph ^ 1u, p.error, kErrMmaAcc)) break;
-        if (!ako::tc::mbar_wait(ako::smem_u32(&s_full[stage]), ph, p.error, kErrMmaFull)) break;
-        ako::tc::fence_after_thread_sync();
-        const uint32_t sa = smem_base + stage * TC_STAGE_BYTES;
-        const uint32_t sb = sa + TC_A_BYTES;
-        const uint32_t d = tmem_base + buf * TC_BN;
+      int g = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+        for (int kb = 0; kb < NKB; ++kb, ++g) {
+          const int stage = g % TC_STAGES;
+          const uint32_t ph = (g / TC_STAGES) & 1;
+          const int buf = g & 1;
+          const uint32_t aph = (g >> 1) & 1;
+          if (!ako::tc::mbar_wait(ako::smem_u32(&s_acc_empty[buf]), aph ^ 1u, p.error, kErrMmaAcc)) { ok = false; break; }
+          if (!ako::tc::mbar_wait(ako::smem_u32(&s_full[stage]), ph, p.error, kErrMmaFull)) { ok = false; break; }
+          ako::tc::fence_after_thread_sync();
+          const uint32_t sa = smem_base + stage * TC_STAGE_BYTES;
+          const uint32_t sb = sa + TC_A_BYTES;
+          const uint32_t d = tmem_base + buf * TC_BN;
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks)
-          ako::tc::mma_f8(d, ako::tc::smem_desc_k_sw128(sa + ks * 32), ako::tc::smem_desc_k_sw128(sb + ks * 32),
-                          IDESC, ks > 0 ? 1u : 0u);
-        ako::tc::mma_commit(ako::smem_u32(&s_empty[stage]));
-        ako::tc::mma_commit(ako::smem_u32(&s_acc_full[buf]));
+          for (int ks = 0; ks < 4; ++ks)
+            ako::tc::mma_f8(d, ako::tc::smem_desc_k_sw128(sa + ks * 32), ako::tc::smem_desc_k_sw128(sb + ks * 32),
+                            IDESC, ks > 0 ? 1u : 0u);
+          ako::tc::mma_commit(ako::smem_u32(&s_empty[stage]));
+          ako::tc::mma_commit(ako::smem_u32(&s_acc_full[buf]));
+        }
       }
     }
   } else {
-    // ================================ workers: load + promote ==================================
+    // ================================ promotion threads =========================================
     const int half = warp >> 2;        // which 128 accumulator columns
     const int q = warp & 3;            // TMEM lane quarter
     const int r = 32 * q + lane;       // accumulator row of this thread
     bool ok = true;
-
-    // ---- load cursor ------------------------------------------------------------------------
-    int ld_g = 0;                      // next K block to issue
-    int ld_tile = blockIdx.x, ld_kb = 0;
-    int a_src[4] = {-1, -1, -1, -1};
-    const uint8_t* ld_wbase = p.w;
-    int ld_nt = 0;
-    auto load_setup = [&]() {
-      const TileInfo ti = tc_tile_info<NT_TILES>(p, s_cum, ld_tile);
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int rr = (tid >> 3) + 32 * j;
-        int src = -1;
-        if (rr < ti.rows) src = (WHICH == 1) ? p.sorted_token[ti.row0 + rr] : ti.row0 + rr;
-        a_src[j] = src;
-      }
-      ld_wbase = p.w + (int64_t)ti.e * ((WHICH == 1) ? (int64_t)2 * INTER * HID : (int64_t)HID * INTER);
-      ld_nt = ti.nt;
-    };
-    // Issues the copies of K block ld_g (one cp.async group, possibly empty) and advances.
-    auto load_issue = [&]() {
-      if (ok && ld_g < G) {
-        if (ld_kb == 0) load_setup();
-        const int stage = ld_g % TC_STAGES;
-        const uint32_t ph = (ld_g / TC_STAGES) & 1;
-        if (!ako::tc::mbar_wait(ako::smem_u32(&s_empty[stage]), ph ^ 1u, p.error, kErrLoad)) {
-          ok = false;
-        } else {
-          const uint32_t sa = smem_base + stage * TC_STAGE_BYTES;
-          const uint32_t sb = sa + TC_A_BYTES;
-          const int c = tid & 7;
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const int rr = (tid >> 3) + 32 * j;
-            const bool valid = a_src[j] >= 0;
-            ako::cp_async16(sa + rr * 128 + ((c ^ (rr & 7)) << 4),
-                            p.a + (int64_t)(valid ? a_src[j] : 0) * A_ROW + (int64_t)ld_kb * 128 + c * 16, valid);
-          }
-          const int wkb = (WHICH == 1) ? ld_kb : (ld_kb & 15);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const int rr = (tid >> 3) + 32 * j;
-            int64_t wrow;
-            if (WHICH == 1) {
-              // [g1 0-63 | g2 0-63 | g1 64-127 | g2 64-127] of h columns nt*128 ..
-              const int gate = (rr >> 6) & 1, blk = rr >> 7;
-              wrow = (int64_t)gate * INTER + ld_nt * 128 + blk * 64 + (rr & 63);
-            } else {
-              wrow = (int64_t)ld_nt * TC_BN + rr;
-            }
-            ako::cp_async16(sb + rr * 128 + ((c ^ (rr & 7)) << 4),
-                            ld_wbase + wrow * W_ROW + (int64_t)wkb * 128 + c * 16, true);
-          }
-          ++ld_g;
-          if (++ld_kb == NKB) { ld_kb = 0; ld_tile += gridDim.x; }
-        }
-      }
-      ako::cp_async_commit();
-    };
-    // Waits until this thread's copies of K block `g` have landed (at most `newer` younger groups
-    // may still be in flight), then publishes them.
-    auto publish = [&](int g) {
-      ako::tc::fence_proxy_async_smem();
-      ako::tc::mbar_arrive(ako::smem_u32(&s_full[g % TC_STAGES]));
-    };
-
-    // pipeline prologue: K blocks 0 .. LAG-1 in flight, block 0 published
-#pragma unroll
-    for (int i = 0; i < TC_LAG; ++i) load_issue();
-    if (G > 0 && ok) {
-      ako::cp_async_wait<TC_LAG - 1>();
-      publish(0);
-    }
-
     int g = 0;
     int tcount = 0;
     for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++tcount) {
       const TileInfo ti = tc_tile_info<NT_TILES>(p, s_cum, tile);
       const int tile_par = tcount & 1;
-      int src = -1;
-      if (r < ti.rows) src = (WHICH == 1) ? p.sorted_token[ti.row0 + r] : ti.row0 + r;
-      const float* asp = p.a_scale + (src >= 0 ? src : 0);
+      const bool live = r < ti.rows;
+      const float* asp = p.a_scale + (live ? ti.row0 + r : 0);
       const float* bsp0;
       const float* bsp1;
       if (WHICH == 1) {
@@ -227,24 +184,16 @@ __global__ void __launch_bounds__(TC_THREADS, 1) moe_gemm_tc_kernel(GemmParams p
       float acc[128];
 #pragma unroll
       for (int j = 0; j < 128; ++j) acc[j] = 0.f;
-      float sa_n = (src >= 0) ? __ldg(asp) : 0.f;
+      float sa_n = live ? __ldg(asp) : 0.f;
       float b0_n = __ldg(bsp0), b1_n = __ldg(bsp1);
 #pragma unroll 1
       for (int kb = 0; kb < NKB; ++kb, ++g) {
-        // (1) keep the ring full, (2) publish K block g+1
-        load_issue();
-        if (!ok) break;
-        if (g + 1 < G) {
-          ako::cp_async_wait<TC_LAG - 1>();
-          publish(g + 1);
-        }
-        // (3) promote K block g
         float sa = sa_n;
         if (WHICH == 2 && kb >= 16) sa *= 0.0625f;
         const float s0 = sa * b0_n, s1 = sa * b1_n;
         if (kb + 1 < NKB) {
           const int nk = (WHICH == 1) ? (kb + 1) : ((kb + 1) & 15);
-          sa_n = (src >= 0) ? __ldg(asp + (int64_t)nk * p.a_scale_stride) : 0.f;
+          sa_n = live ? __ldg(asp + (int64_t)nk * p.a_scale_stride) : 0.f;
           b0_n = __ldg(bsp0 + nk);
           b1_n = __ldg(bsp1 + nk);
         }
@@ -276,14 +225,15 @@ __global__ void __launch_bounds__(TC_THREADS, 1) moe_gemm_tc_kernel(GemmParams p
       if (!ok) break;
 
       if (WHICH == 2) {
-        if (r < ti.rows) {
+        if (live) {
           float* yp = p.y + (int64_t)(ti.row0 + r) * HID + ti.nt * TC_BN + half * 128;
 #pragma unroll
           for (int j = 0; j < 128; j += 4)
             *reinterpret_cast<float4*>(yp + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
         }
       } else {
-        // SwiGLU on this thread's 64 columns of h, row maximum across the two column halves
+        // SwiGLU on this thread's 64 columns of h, row maximum across the two column halves.
+        // Rows that are not live may hold garbage (another expert's rows): keep it out of smem.
         float mx = 0.f;
 #pragma unroll
         for (int j = 0; j < 64; ++j) {
@@ -292,13 +242,13 @@ __global__ void __launch_bounds__(TC_THREADS, 1) moe_gemm_tc_kernel(GemmParams p
           acc[j] = h;
           mx = fmaxf(mx, fabsf(h));
         }
-        s_amax[tile_par][half][r] = mx;
+        s_amax[tile_par][half][r] = live ? mx : 0.f;
         // exchange through a bounded mbarrier (256 arrivals), never an unbounded bar.sync
         ako::tc::mbar_arrive(ako::smem_u32(&s_xchg[tile_par]));
         if (!ako::tc::mbar_wait(ako::smem_u32(&s_xchg[tile_par]), (uint32_t)((tcount >> 1) & 1), p.error,
                                 kErrEpilogue)) { ok = false; break; }
         const float amax = fmaxf(s_amax[tile_par][0][r], s_amax[tile_par][1][r]);
-        if (r < ti.rows) {
+        if (live) {
           int ex = ((__float_as_int(amax) >> 23) & 0xff) - 127 - 7;  // amax / 2^ex < 256
           ex = max(ex, -100);
           const float sc = __int_as_float((ex + 127) << 23);
@@ -331,7 +281,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) moe_gemm_tc_kernel(GemmParams p
         }
       }
     }
-    ako::cp_async_wait<0>();  // no copy of this thread is left in flight at exit
   }
 
   // ================================ common exit ================================================

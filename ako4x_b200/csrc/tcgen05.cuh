@@ -49,6 +49,23 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* er
   }
 }
 
+// ---- TMA (bulk tensor copy global -> shared, completion counted in bytes on an mbarrier) ------
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+// 2-D tiled load of the box described by `tmap` at element coordinates (x = innermost, y = row)
+// into shared memory at `dst`; x * element size must be a multiple of 16 bytes.
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, int x, int y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n" ::
+          "r"(dst),
+      "l"(tmap), "r"(bar), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {
+  asm volatile("prefetch.tensormap [%0];\n" ::"l"(tmap) : "memory");
+}
+
 // ---- fences ----------------------------------------------------------------------------------
 // Generic-proxy writes to shared memory (st.shared, cp.async) -> visible to the async proxy
 // (tcgen05.mma operand reads).
