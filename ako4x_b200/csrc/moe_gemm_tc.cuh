@@ -91,8 +91,9 @@ moe_gemm_tc_kernel(GemmParams p, const __grid_constant__ CUtensorMap tm_a, const
     }
     for (int b = 0; b < 2; ++b) {
       ako::tc::mbar_init(ako::smem_u32(&s_acc_full[b]), 1);
-      ako::tc::mbar_init(ako::smem_u32(&s_acc_empty[b]), TC_WORKERS);
-      ako::tc::mbar_init(ako::smem_u32(&s_xchg[b]), TC_WORKERS);
+      // one elected arrival per worker warp: 256 same-address arrivals would serialise
+      ako::tc::mbar_init(ako::smem_u32(&s_acc_empty[b]), TC_WORKERS / 32);
+      ako::tc::mbar_init(ako::smem_u32(&s_xchg[b]), TC_WORKERS / 32);
     }
     ako::tc::mbar_init_fence();
   }
@@ -215,7 +216,8 @@ moe_gemm_tc_kernel(GemmParams p, const __grid_constant__ CUtensorMap tm_a, const
         ako::tc::tmem_ld32(taddr + 96, v1);
         ako::tc::tmem_ld_wait();
         ako::tc::fence_before_thread_sync();
-        ako::tc::mbar_arrive(ako::smem_u32(&s_acc_empty[buf]));
+        __syncwarp();
+        if (lane == 0) ako::tc::mbar_arrive(ako::smem_u32(&s_acc_empty[buf]));
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
           acc[64 + j] = fmaf(v0[j], s1, acc[64 + j]);
@@ -244,7 +246,8 @@ moe_gemm_tc_kernel(GemmParams p, const __grid_constant__ CUtensorMap tm_a, const
         }
         s_amax[tile_par][half][r] = live ? mx : 0.f;
         // exchange through a bounded mbarrier (256 arrivals), never an unbounded bar.sync
-        ako::tc::mbar_arrive(ako::smem_u32(&s_xchg[tile_par]));
+        __syncwarp();
+        if (lane == 0) ako::tc::mbar_arrive(ako::smem_u32(&s_xchg[tile_par]));
         if (!ako::tc::mbar_wait(ako::smem_u32(&s_xchg[tile_par]), (uint32_t)((tcount >> 1) & 1), p.error,
                                 kErrEpilogue)) { ok = false; break; }
         const float amax = fmaxf(s_amax[tile_par][0][r], s_amax[tile_par][1][r]);

@@ -141,6 +141,18 @@ __device__ __forceinline__ void tmem_ld_wait() {
   asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
 }
 
+// Two fp32 FMAs in one instruction (sm_100 packed fp32): a0 += v0*s, a1 += v1*s.
+__device__ __forceinline__ void fma2(float& a0, float& a1, float v0, float v1, float s) {
+  asm("{\n.reg .b64 ra, rv, rs;\n"
+      "mov.b64 ra, {%0, %1};\n"
+      "mov.b64 rv, {%2, %3};\n"
+      "mov.b64 rs, {%4, %4};\n"
+      "fma.rn.f32x2 ra, rv, rs, ra;\n"
+      "mov.b64 {%0, %1}, ra;\n}\n"
+      : "+f"(a0), "+f"(a1)
+      : "f"(v0), "f"(v1), "f"(s));
+}
+
 // ---- register re-balancing between warp groups ---------------------------------------------------
 template <int N>
 __device__ __forceinline__ void reg_dec() {
