@@ -65,6 +65,7 @@ _SIGNATURES = {
     "ako4x_rmsnorm_h128": (_INT, [_P, _P, _P, _I64, _P]),
     "ako4x_gqa_paged_decode_workspace_bytes": (_SZ, [_I64, _I64, _I64]),
     "ako4x_gqa_paged_decode": (_INT, [_P, _P, _P, _P, _P, _F32, _P, _P, _I64, _I64, _I64, _P, _SZ, _P]),
+    "ako4x_gqa_paged_decode_device_status": (_INT, []),
     "ako4x_gqa_paged_decode_noalloc_max_scratch_bytes": (_SZ, []),
     "ako4x_gqa_paged_decode_noalloc": (_INT, [_P, _P, _P, _P, _P, _F32, _P, _P, _I64, _I64, _I64, _P]),
     "ako4x_mla_paged_decode_workspace_bytes": (_SZ, [_I64, _I64, _I64]),

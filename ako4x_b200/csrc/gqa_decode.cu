@@ -3,12 +3,17 @@
 // HBM-bound: every KV token costs 4096 bytes (8 heads x 128 x bf16 for K and again for V) and
 // only 4 query rows reuse it. One CTA owns (sequence, KV split, half of the KV heads): its 4
 // warps each run flash-decoding for one KV head (the 4 query heads of that group padded to an
-// m16 tile of mma.sync) over a 3-stage cp.async ring of 16-token tiles. A token's four K heads
-// are 1 KB contiguous in the cache, so each gather touches 1 KB for K and 1 KB for V. Tiles are
-// stored per head as [token][128] with the 16-byte chunks XOR-swizzled by (token & 7) so that
-// ldmatrix is bank-conflict free. Partials (m, l, acc) go to the workspace in fp32 and a second
-// kernel merges them; with one split the CTA writes o and lse itself.
+// m16 tile of mma.sync) over a 3-stage ring of 16-token tiles. A token's four K heads are 1 KB
+// contiguous in the cache, so the gather is ONE 1 KB bulk copy (cp.async.bulk, completion counted
+// in bytes on the stage's mbarrier) per token per tensor, issued by 16 lanes of warp 0; 16-byte
+// cp.async copies run out of outstanding-request slots long before HBM is busy. Gather indices are
+// fetched one tile ahead of the copies that need them. Rows sit in shared memory with a 1040-byte
+// pitch, which keeps ldmatrix bank-conflict free without a swizzle. Partials (m, l, acc) go to the
+// workspace in fp32 and a second kernel merges them; with one split the CTA writes o and lse
+// itself. Waits on the mbarriers are bounded: a wait that runs out of budget records a code in
+// a device status word and the CTA stops consuming.
 #include "lse_merge.cuh"
+#include "tcgen05.cuh"
 
 namespace {
 
@@ -17,15 +22,19 @@ constexpr int HPC = 4;        // KV heads per CTA (one per warp)
 constexpr int TILE = 16;      // tokens per pipeline stage
 constexpr int STAGES = 3;
 constexpr int THREADS = HPC * 32;
-constexpr int TILE_ELEMS = HPC * TILE * D;                       // per K or V tile
-constexpr int STAGE_BYTES = 2 * TILE_ELEMS * 2;                  // K + V, bf16
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES;                 // 96 KB
+constexpr int ROW_BYTES = HPC * D * 2;            // 1024: the CTA's heads of one token, one tensor
+constexpr int PITCH = ROW_BYTES + 16;             // shared-memory row pitch
+constexpr int TENSOR_TILE_BYTES = TILE * PITCH;   // 16640
+constexpr int STAGE_BYTES = 2 * TENSOR_TILE_BYTES;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES;  // 99840 -> two CTAs per SM
 constexpr int MAX_SPLITS = 64;
+
+__device__ int g_gqa_status = 0;  // 0 = ok; set when a bounded wait gave up
 
 struct Params {
   const __nv_bfloat16* q;
-  const __nv_bfloat16* k;
-  const __nv_bfloat16* v;
+  const unsigned char* k;
+  const unsigned char* v;
   const int32_t* indptr;
   const int32_t* indices;
   __nv_bfloat16* o;
@@ -37,37 +46,16 @@ struct Params {
   int num_splits;
 };
 
-// Issues the cp.async copies of one 16-token tile (K and V, HPC heads) into `stage`.
-__device__ __forceinline__ void load_tile(const Params& p, __nv_bfloat16* stage, int64_t idx_base,
-                                          int tok0, int tok_end, int head0) {
-  const int tid = threadIdx.x;
-  // 64 chunks of 16 B per token per tensor (4 heads x 256 B); 128 threads cover 2 tokens a pass.
-  const int c = tid & 63;
-  const int h = c >> 4, chunk = c & 15;
-#pragma unroll
-  for (int pass = 0; pass < TILE / 2; ++pass) {
-    const int i = pass * 2 + (tid >> 6);
-    const int tok = tok0 + i;
-    const bool valid = tok < tok_end;
-    int64_t row = 0;
-    if (valid) {
-      if (p.page_size == 1) {
-        row = __ldg(p.indices + idx_base + tok);
-      } else {
-        const int pg = tok / p.page_size;
-        row = (int64_t)__ldg(p.indices + idx_base + pg) * p.page_size + (tok - pg * p.page_size);
-      }
-    }
-    const int64_t src = row * (HKV * D) + (int64_t)(head0 + h) * D + chunk * 8;
-    const int dst = (h * TILE + i) * D + ((chunk ^ (i & 7)) << 3);
-    ako::cp_async16(ako::smem_u32(stage + dst), p.k + src, valid);
-    ako::cp_async16(ako::smem_u32(stage + TILE_ELEMS + dst), p.v + src, valid);
-  }
+// Cache row of token `tok` of the sequence whose page list starts at `idx`.
+__device__ __forceinline__ int64_t token_row(const Params& p, const int32_t* idx, int tok) {
+  if (p.page_size == 1) return __ldg(idx + tok);
+  const int pg = tok / p.page_size;
+  return (int64_t)__ldg(idx + pg) * p.page_size + (tok - pg * p.page_size);
 }
 
 __global__ void __launch_bounds__(THREADS, 2) gqa_decode_kernel(Params p) {
-  extern __shared__ __align__(128) unsigned char smem_raw[];
-  __nv_bfloat16* smem = reinterpret_cast<__nv_bfloat16*>(smem_raw);
+  extern __shared__ __align__(128) unsigned char smem[];
+  __shared__ __align__(8) uint64_t s_full[STAGES];
 
   const int split = blockIdx.x % p.num_splits;
   const int half = (blockIdx.x / p.num_splits) & 1;
@@ -76,15 +64,57 @@ __global__ void __launch_bounds__(THREADS, 2) gqa_decode_kernel(Params p) {
   const int g = lane >> 2, t = lane & 3;
   const int head0 = half * HPC;
   const int kvh = head0 + warp;
+  const uint32_t smem_base = ako::smem_u32(smem);
 
   ako::pdl_trigger();  // the merge kernel may be scheduled early; it waits for this grid to finish
-  const int64_t idx_base = p.indptr[b];
-  const int len = (int)(p.indptr[b + 1] - idx_base) * p.page_size;
+  const int32_t* idx = p.indices + p.indptr[b];
+  const int len = (int)(p.indptr[b + 1] - p.indptr[b]) * p.page_size;
   int chunk = (int)ako::round_up(ako::cdiv(len, p.num_splits), TILE);
   if (chunk < TILE) chunk = TILE;
   const int tok_begin = min(len, split * chunk);
   const int tok_end = min(len, tok_begin + chunk);
   const int ntiles = (tok_end - tok_begin + TILE - 1) / TILE;
+
+  // Shared memory starts finite: rows of tokens past the end are never copied, and 0 * stale
+  // must not be NaN in the PV product.
+  for (int i = threadIdx.x; i < SMEM_BYTES / 16; i += THREADS) reinterpret_cast<uint4*>(smem)[i] = make_uint4(0, 0, 0, 0);
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) ako::tc::mbar_init(ako::smem_u32(&s_full[s]), 1);
+    ako::tc::mbar_init_fence();
+  }
+  ako::tc::fence_proxy_async_smem();  // the zero fill is ordered before the bulk copies
+  __syncthreads();
+
+  // ---- producer state (warp 0, lanes 0..15: one token of a tile each) ------------------------
+  const int64_t head_off = (int64_t)head0 * D * 2;
+  int64_t row_next = -1;  // cache row of this lane's token in the next tile to be issued
+  auto fetch_row = [&](int tile) {
+    const int tok = tok_begin + tile * TILE + lane;
+    row_next = (lane < TILE && tile < ntiles && tok < tok_end) ? token_row(p, idx, tok) : -1;
+  };
+  auto issue_tile = [&](int tile) {  // uses row_next fetched for `tile`
+    const int stage = tile % STAGES;
+    const uint32_t bar = ako::smem_u32(&s_full[stage]);
+    const bool valid = row_next >= 0;
+    const unsigned m = __ballot_sync(0xffffffffu, valid);
+    if (lane == 0) ako::tc::mbar_arrive_expect_tx(bar, (uint32_t)__popc(m) * 2 * ROW_BYTES);
+    __syncwarp();
+    if (valid) {
+      const uint32_t dst = smem_base + stage * STAGE_BYTES + lane * PITCH;
+      const int64_t src = row_next * (HKV * D * 2) + head_off;
+      ako::tc::bulk_load_1d(dst, p.k + src, ROW_BYTES, bar);
+      ako::tc::bulk_load_1d(dst + TENSOR_TILE_BYTES, p.v + src, ROW_BYTES, bar);
+    }
+  };
+  if (warp == 0) {
+    for (int s = 0; s < STAGES - 1; ++s) {
+      if (s < ntiles) {
+        fetch_row(s);
+        issue_tile(s);
+      }
+    }
+    fetch_row(STAGES - 1);
+  }
 
   // Q fragments of this warp's group (rows g<4 real, others zero).
   uint32_t qa[8][2];
@@ -104,24 +134,19 @@ __global__ void __launch_bounds__(THREADS, 2) gqa_decode_kernel(Params p) {
   for (int i = 0; i < 16; ++i) oacc[i][0] = oacc[i][1] = oacc[i][2] = oacc[i][3] = 0.f;
   float m_run = -INFINITY, l_run = 0.f;
 
-#pragma unroll
-  for (int s = 0; s < STAGES - 1; ++s) {
-    if (s < ntiles) load_tile(p, smem + s * (STAGE_BYTES / 2), idx_base, tok_begin + s * TILE, tok_end, head0);
-    ako::cp_async_commit();
-  }
-
   for (int it = 0; it < ntiles; ++it) {
-    ako::cp_async_wait<STAGES - 2>();
-    __syncthreads();
-    // prefetch tile it+STAGES-1 into the stage consumed at iteration it-1
-    {
-      const int nt = it + STAGES - 1;
-      if (nt < ntiles)
-        load_tile(p, smem + (nt % STAGES) * (STAGE_BYTES / 2), idx_base, tok_begin + nt * TILE, tok_end, head0);
-      ako::cp_async_commit();
+    const int stage = it % STAGES;
+    const bool landed = ako::tc::mbar_wait(ako::smem_u32(&s_full[stage]), (uint32_t)((it / STAGES) & 1),
+                                           &g_gqa_status, 1);
+    // every warp has finished tile it-1: its stage is free for tile it+STAGES-1
+    if (!__syncthreads_and(landed)) break;  // a wait gave up: the whole CTA stops consuming
+    if (warp == 0) {
+      ako::tc::fence_proxy_async_smem();  // generic reads of the freed stage before async writes
+      if (it + STAGES - 1 < ntiles) issue_tile(it + STAGES - 1);
+      fetch_row(it + STAGES);
     }
-    const __nv_bfloat16* Ks = smem + (it % STAGES) * (STAGE_BYTES / 2) + warp * TILE * D;
-    const __nv_bfloat16* Vs = Ks + TILE_ELEMS;
+    const uint32_t Ks = smem_base + stage * STAGE_BYTES + warp * (D * 2);
+    const uint32_t Vs = Ks + TENSOR_TILE_BYTES;
 
     // S = Q K^T : 2 n-tiles of 8 tokens
     float sacc[2][4];
@@ -133,8 +158,7 @@ __global__ void __launch_bounds__(THREADS, 2) gqa_decode_kernel(Params p) {
 #pragma unroll
       for (int ks = 0; ks < 8; ++ks) {
         uint32_t b00, b01, b10, b11;
-        const int chunk_id = (2 * ks + csel) ^ (tok & 7);
-        ako::ldmatrix_x4(b00, b01, b10, b11, ako::smem_u32(Ks + tok * D + (chunk_id << 3)));
+        ako::ldmatrix_x4(b00, b01, b10, b11, Ks + tok * PITCH + ((2 * ks + csel) << 4));
         const uint32_t a[4] = {qa[ks][0], 0u, qa[ks][1], 0u};
         ako::mma_bf16_16816(sacc[0], a, b00, b01);
         ako::mma_bf16_16816(sacc[1], a, b10, b11);
@@ -185,14 +209,12 @@ __global__ void __launch_bounds__(THREADS, 2) gqa_decode_kernel(Params p) {
 #pragma unroll
       for (int nd = 0; nd < 16; nd += 2) {
         uint32_t v00, v01, v10, v11;
-        const int chunk_id = (nd + csel) ^ (tok & 7);
-        ako::ldmatrix_x4_trans(v00, v01, v10, v11, ako::smem_u32(Vs + tok * D + (chunk_id << 3)));
+        ako::ldmatrix_x4_trans(v00, v01, v10, v11, Vs + tok * PITCH + ((nd + csel) << 4));
         ako::mma_bf16_16816(oacc[nd], pa, v00, v01);
         ako::mma_bf16_16816(oacc[nd + 1], pa, v10, v11);
       }
     }
   }
-  ako::cp_async_wait<0>();
 
   if (g < GROUP) {
     const int64_t rh = (int64_t)b * HQ + kvh * GROUP + g;
@@ -256,8 +278,8 @@ extern "C" int ako4x_gqa_paged_decode(const void* q, const void* k_cache, const 
 
   Params p;
   p.q = (const __nv_bfloat16*)q;
-  p.k = (const __nv_bfloat16*)k_cache;
-  p.v = (const __nv_bfloat16*)v_cache;
+  p.k = (const unsigned char*)k_cache;
+  p.v = (const unsigned char*)v_cache;
   p.indptr = kv_indptr;
   p.indices = kv_indices;
   p.o = (__nv_bfloat16*)o;
@@ -293,4 +315,12 @@ extern "C" int ako4x_gqa_paged_decode(const void* q, const void* k_cache, const 
       return AKO4X_ELAUNCH;
   }
   return AKO4X_OK;
+}
+
+// Status word of the decode kernel of this file: 0, or the code of a bounded wait that gave up.
+// Synchronises the device; meant for tests and post-mortems.
+extern "C" int ako4x_gqa_paged_decode_device_status(void) {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_gqa_status, sizeof(int)) != cudaSuccess) return AKO4X_ELAUNCH;
+  return v;
 }

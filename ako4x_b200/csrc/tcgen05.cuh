@@ -62,6 +62,12 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, int 
       "l"(tmap), "r"(bar), "r"(x), "r"(y)
       : "memory");
 }
+// 1-D bulk copy of `bytes` (multiple of 16, both addresses 16-byte aligned) global -> shared.
+__device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(dst),
+               "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
 __device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {
   asm volatile("prefetch.tensormap [%0];\n" ::"l"(tmap) : "memory");
 }

@@ -59,6 +59,11 @@ int ako4x_gqa_paged_decode(const void* q, const void* k_cache, const void* v_cac
                            int64_t page_size, void* workspace, size_t workspace_bytes,
                            void* stream);
 
+/* The gather pipeline waits on mbarriers with a cycle budget. A wait that gives up stores a
+ * non-zero code in a device status word and the CTA stops consuming; this call returns that word
+ * (0 = no wait ever gave up). It synchronises the device: for tests and post-mortems only. */
+int ako4x_gqa_paged_decode_device_status(void);
+
 /* The same operator for callers that have no scratch memory to pass and cannot allocate any (a
  * plug-in host that supplies only input and output tensors; a serving process whose HBM is fully
  * committed to its KV-cache pool). It has no counterpart in the reference. The split-KV partials
