@@ -25,8 +25,7 @@ constexpr int PAGE_BYTES = PS * HD + PS * 4;  // 8448
 // ---------------------------------------------------------------------------------------------
 constexpr int SC_WARPS = 4;
 constexpr int SC_THREADS = SC_WARPS * 32;
-constexpr int SC_PAGES_PER_WARP = 8;
-constexpr int SC_PAGES_PER_CTA = SC_WARPS * SC_PAGES_PER_WARP;
+constexpr int SC_MAX_PAGES_PER_WARP = 8;  // pages a warp walks; fewer when the grid would be small
 constexpr int SC_SMEM = SC_WARPS * 2 * PS * HD;  // 64 KB
 
 __device__ __forceinline__ void load_page(unsigned char* slot, const unsigned char* page, int lane) {
@@ -43,7 +42,7 @@ __global__ void __launch_bounds__(SC_THREADS) dsa_score_kernel(
     const unsigned char* __restrict__ q, const unsigned char* __restrict__ cache,
     const float* __restrict__ weights, const int32_t* __restrict__ seq_lens,
     const int32_t* __restrict__ block_table, float* __restrict__ scores, int max_pages,
-    int64_t num_cache_pages, int skip_short) {
+    int64_t num_cache_pages, int skip_short, int pages_per_warp) {
   extern __shared__ __align__(128) unsigned char smem[];
   const int r = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -51,7 +50,7 @@ __global__ void __launch_bounds__(SC_THREADS) dsa_score_kernel(
   ako::pdl_trigger();
   const int sl = seq_lens[r];
   float* out = scores + (int64_t)r * max_pages * PS;
-  const int page_lo = blockIdx.y * SC_PAGES_PER_CTA;
+  const int page_lo = blockIdx.y * SC_WARPS * pages_per_warp;
   if (sl <= 0 || (skip_short && sl <= TOPK)) return;
   const int npages = min(max_pages, (sl + PS - 1) / PS);
 
@@ -86,12 +85,12 @@ __global__ void __launch_bounds__(SC_THREADS) dsa_score_kernel(
   }
   ako::cp_async_commit();
 
-  for (int j = 0; j < SC_PAGES_PER_WARP; ++j) {
+  for (int j = 0; j < pages_per_warp; ++j) {
     const int pg = page_lo + warp + SC_WARPS * j;
     if (pg >= npages) break;
     phys_cur = phys_next;
     pg_next = pg + SC_WARPS;
-    if (j + 1 < SC_PAGES_PER_WARP && pg_next < npages) {
+    if (j + 1 < pages_per_warp && pg_next < npages) {
       phys_next = bt[pg_next];
       if (phys_next < 0 || phys_next >= num_cache_pages) phys_next = 0;
       load_page(slot0 + ((j + 1) & 1) * PS * HD, cache + phys_next * PAGE_BYTES, lane);
@@ -268,10 +267,14 @@ int launch_scores(const void* q, const void* cache, const float* weights, const 
                   const int32_t* block_table, float* scores, int64_t rows, int64_t max_pages,
                   int64_t num_cache_pages, int skip_short, cudaStream_t st) {
   if (!ako::ensure_dynamic_smem<dsa_score_kernel>(SC_SMEM)) return AKO4X_ELAUNCH;
-  dim3 grid((unsigned)rows, (unsigned)ako::cdiv(max_pages, SC_PAGES_PER_CTA));
+  // enough CTAs for ~4 waves of 148 SMs x 3 resident CTAs, at most 8 pages per warp
+  int64_t ppw = rows * max_pages / (SC_WARPS * 1776);
+  if (ppw < 1) ppw = 1;
+  if (ppw > SC_MAX_PAGES_PER_WARP) ppw = SC_MAX_PAGES_PER_WARP;
+  dim3 grid((unsigned)rows, (unsigned)ako::cdiv(max_pages, SC_WARPS * ppw));
   dsa_score_kernel<<<grid, SC_THREADS, SC_SMEM, st>>>(
       (const unsigned char*)q, (const unsigned char*)cache, weights, seq_lens, block_table, scores,
-      (int)max_pages, num_cache_pages, skip_short);
+      (int)max_pages, num_cache_pages, skip_short, (int)ppw);
   AKO_CHECK_LAUNCH();
   return AKO4X_OK;
 }

@@ -46,13 +46,6 @@ struct Params {
   int num_splits;
 };
 
-// Cache row of token `tok` of the sequence whose page list starts at `idx`.
-__device__ __forceinline__ int64_t token_row(const Params& p, const int32_t* idx, int tok) {
-  if (p.page_size == 1) return __ldg(idx + tok);
-  const int pg = tok / p.page_size;
-  return (int64_t)__ldg(idx + pg) * p.page_size + (tok - pg * p.page_size);
-}
-
 __global__ void __launch_bounds__(THREADS, 2) gqa_decode_kernel(Params p) {
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ __align__(8) uint64_t s_full[STAGES];
@@ -87,15 +80,22 @@ __global__ void __launch_bounds__(THREADS, 2) gqa_decode_kernel(Params p) {
 
   // ---- producer state (warp 0, lanes 0..15: one token of a tile each) ------------------------
   const int64_t head_off = (int64_t)head0 * D * 2;
-  int64_t row_next = -1;  // cache row of this lane's token in the next tile to be issued
+  // The page id of this lane's token in the next tile to be issued is loaded one iteration early
+  // and only LOADED there: nothing depends on it until issue_tile, so warp 0 never stalls on the
+  // index fetch in front of the barrier the other warps wait at.
+  int32_t page_next = 0;
   auto fetch_row = [&](int tile) {
-    const int tok = tok_begin + tile * TILE + lane;
-    row_next = (lane < TILE && tile < ntiles && tok < tok_end) ? token_row(p, idx, tok) : -1;
+    int tok = tok_begin + tile * TILE + lane;
+    tok = min(tok, max(tok_end - 1, 0));  // a valid address even when this lane has no token
+    if (len > 0) page_next = __ldg(idx + (p.page_size == 1 ? tok : tok / p.page_size));
   };
-  auto issue_tile = [&](int tile) {  // uses row_next fetched for `tile`
+  auto issue_tile = [&](int tile) {  // uses page_next fetched for `tile`
     const int stage = tile % STAGES;
     const uint32_t bar = ako::smem_u32(&s_full[stage]);
-    const bool valid = row_next >= 0;
+    const int tok = tok_begin + tile * TILE + lane;
+    const bool valid = lane < TILE && tok < tok_end;
+    const int64_t row_next = (p.page_size == 1) ? (int64_t)page_next
+                                                : (int64_t)page_next * p.page_size + tok % p.page_size;
     const unsigned m = __ballot_sync(0xffffffffu, valid);
     if (lane == 0) ako::tc::mbar_arrive_expect_tx(bar, (uint32_t)__popc(m) * 2 * ROW_BYTES);
     __syncwarp();
