@@ -70,6 +70,7 @@ _SIGNATURES = {
     "ako4x_gqa_paged_decode_noalloc": (_INT, [_P, _P, _P, _P, _P, _F32, _P, _P, _I64, _I64, _I64, _P]),
     "ako4x_mla_paged_decode_workspace_bytes": (_SZ, [_I64, _I64, _I64]),
     "ako4x_mla_paged_decode": (_INT, [_P, _P, _P, _P, _P, _P, _F32, _P, _P, _I64, _I64, _I64, _P, _SZ, _P]),
+    "ako4x_mla_attention_device_status": (_INT, []),
     "ako4x_mla_paged_prefill_workspace_bytes": (_SZ, [_I64, _I64, _I64, _I64]),
     "ako4x_mla_paged_prefill": (_INT, [_P, _P, _P, _P, _P, _P, _P, _F32, _P, _P, _I64, _I64, _I64, _I64, _P, _SZ, _P]),
     "ako4x_dsa_topk_indexer_workspace_bytes": (_SZ, [_I64, _I64]),

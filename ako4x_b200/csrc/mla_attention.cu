@@ -4,39 +4,50 @@
 // A "row" is one query token (16 heads = one m16 tile of mma.sync). Its keys are a list of cache
 // rows: the paged KV list of its sequence (decode), its sparse index list with -1 holes (DSA), or
 // the causally visible prefix of its sequence's KV list (prefill). One CTA of 8 warps owns
-// (row, KV split) and streams 64-token tiles (72 KB: 1024 B ckv + 128 B kpe per token) through a
-// 2-stage cp.async ring; the gather indices of tile i+2 travel in the same cp.async group as the
-// data of tile i+1, so no index load sits in front of a data load.
+// (row, KV split) and streams 64-token tiles through a 2-stage ring. A token is gathered with TWO
+// bulk copies (cp.async.bulk: 1024 B of ckv, 128 B of kpe; completion counted in bytes on the
+// stage's mbarrier) issued by the 64 lanes of warps 0-1, one token per lane; the lane loads its
+// gather index one tile earlier and nothing depends on that load until the copy is issued.
+// Rows sit in shared memory with 1040 / 144-byte pitches, which keeps ldmatrix bank-conflict free
+// without a swizzle.
 //   S phase : warp w computes logits of tokens 16*(w&3).. over one half of the 576-wide
 //             reduction (w>>2) with its Q fragments held in registers; halves meet in shared memory.
 //   PV phase: every warp rebuilds P (softmax is recomputed per warp, which removes two barriers)
 //             and accumulates its own 64 of the 512 output columns.
 // Each token costs 1152 bytes of HBM traffic and 34816 flop, so the kernel is gather-bandwidth
-// bound; shared-memory traffic per token (about 4.4 KB) is the second limit.
+// bound; shared-memory traffic per token (about 4.4 KB) is the second limit. Waits on the
+// mbarriers are bounded: a wait that runs out of budget records a code in a device status word
+// and the CTA stops consuming.
 #include "lse_merge.cuh"
+#include "tcgen05.cuh"
 
 namespace {
 
 constexpr int H = 16, DC = 512, DP = 64;
 constexpr int TILE = 64;
 constexpr int THREADS = 256;
-constexpr int CKV_TILE_ELEMS = TILE * DC;
-constexpr int KPE_TILE_ELEMS = TILE * DP;
-constexpr int STAGE_ELEMS = CKV_TILE_ELEMS + KPE_TILE_ELEMS;
+constexpr int CKV_ROW = DC * 2;                 // 1024 bytes
+constexpr int KPE_ROW = DP * 2;                 // 128 bytes
+constexpr int CKV_PITCH = CKV_ROW + 16;
+constexpr int KPE_PITCH = KPE_ROW + 16;
+constexpr int CKV_TILE_BYTES = TILE * CKV_PITCH;
+constexpr int KPE_TILE_BYTES = TILE * KPE_PITCH;
+constexpr int STAGE_BYTES = CKV_TILE_BYTES + KPE_TILE_BYTES;  // 75776
 constexpr int STAGES = 2;
 constexpr int SROW = 72;  // padded fp32 row stride of the logit exchange buffer
 constexpr int SBUF_FLOATS = 2 * H * SROW;
-constexpr int IDX_RING = 3;
-constexpr int SMEM_BYTES = STAGES * STAGE_ELEMS * 2 + SBUF_FLOATS * 4 + IDX_RING * TILE * 4;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + SBUF_FLOATS * 4;
 constexpr int MAX_SPLITS = 64;
+
+__device__ int g_mla_status = 0;  // 0 = ok; set when a bounded wait gave up
 
 enum Mode { kDecode = 0, kSparse = 1, kPrefill = 2 };
 
 struct Params {
   const __nv_bfloat16* q_nope;
   const __nv_bfloat16* q_pe;
-  const __nv_bfloat16* ckv;
-  const __nv_bfloat16* kpe;
+  const unsigned char* ckv;
+  const unsigned char* kpe;
   const int32_t* qo_indptr;   // prefill only
   const int32_t* kv_indptr;   // decode / prefill
   const int32_t* indices;     // kv_indices or sparse_indices
@@ -84,61 +95,13 @@ __device__ __forceinline__ RowDesc describe_row(const Params& p, int64_t row) {
   return d;
 }
 
-// cp.async of the gather indices of tile `tile` (positions tok0..tok0+63) into ring slot `slot`.
-// Entries past the end become -1.
-__device__ __forceinline__ void load_indices_async(const Params& p, const RowDesc& rd, int32_t* ring,
-                                                   int slot, int tok0, int tok_end) {
-  if (threadIdx.x < TILE) {
-    const int tok = tok0 + threadIdx.x;
-    const bool valid = tok < tok_end;
-    const int32_t* src = rd.idx + (valid ? (p.page_size == 1 ? tok : tok / p.page_size) : 0);
-    const uint32_t dst = ako::smem_u32(ring + slot * TILE + threadIdx.x);
-    const int sz = valid ? 4 : 0;
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;\n" ::"r"(dst), "l"(src), "r"(sz));
-  }
-}
-
-// cp.async of one 64-token tile. Ring entries: page id (or cache row), 0 after zero-fill means
-// "past the end" only when the position test says so; negative entries are holes.
-__device__ __forceinline__ void load_tile(const Params& p, __nv_bfloat16* stage, const int32_t* ring_slot,
-                                          int tok0, int tok_end) {
-  const int tid = threadIdx.x;
-  {
-    const int chunk = tid & 63;
-#pragma unroll
-    for (int pass = 0; pass < TILE / 4; ++pass) {
-      const int i = pass * 4 + (tid >> 6);
-      const int tok = tok0 + i;
-      const int32_t e = ring_slot[i];
-      const bool valid = (tok < tok_end) && (e >= 0);
-      int64_t row = 0;
-      if (valid) row = (p.page_size == 1) ? (int64_t)e : (int64_t)e * p.page_size + (tok % p.page_size);
-      const int dst = i * DC + ((chunk ^ (i & 7)) << 3);
-      ako::cp_async16(ako::smem_u32(stage + dst), p.ckv + row * DC + chunk * 8, valid);
-    }
-  }
-  {
-    const int chunk = tid & 7;
-#pragma unroll
-    for (int pass = 0; pass < 2; ++pass) {
-      const int i = pass * 32 + (tid >> 3);
-      const int tok = tok0 + i;
-      const int32_t e = ring_slot[i];
-      const bool valid = (tok < tok_end) && (e >= 0);
-      int64_t row = 0;
-      if (valid) row = (p.page_size == 1) ? (int64_t)e : (int64_t)e * p.page_size + (tok % p.page_size);
-      const int dst = CKV_TILE_ELEMS + i * DP + ((chunk ^ (i & 7)) << 3);
-      ako::cp_async16(ako::smem_u32(stage + dst), p.kpe + row * DP + chunk * 8, valid);
-    }
-  }
-}
-
 template <int MODE>
 __global__ void __launch_bounds__(THREADS, 1) mla_attention_kernel(Params p) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
-  __nv_bfloat16* tiles = reinterpret_cast<__nv_bfloat16*>(smem_raw);
-  float* sbuf = reinterpret_cast<float*>(smem_raw + STAGES * STAGE_ELEMS * 2);
-  int32_t* ring = reinterpret_cast<int32_t*>(sbuf + SBUF_FLOATS);
+  __shared__ __align__(8) uint64_t s_full[STAGES];
+  __shared__ uint32_t s_valid[STAGES][2];  // per stage: which of the 64 tokens were copied
+  float* sbuf = reinterpret_cast<float*>(smem_raw + STAGES * STAGE_BYTES);
+  const uint32_t smem_base = ako::smem_u32(smem_raw);
 
   const int split = blockIdx.x % p.num_splits;
   const int64_t row = blockIdx.x / p.num_splits;
@@ -154,6 +117,52 @@ __global__ void __launch_bounds__(THREADS, 1) mla_attention_kernel(Params p) {
   const int tok_begin = min(rd.count, split * chunk);
   const int tok_end = min(rd.count, tok_begin + chunk);
   const int ntiles = (tok_end - tok_begin + TILE - 1) / TILE;
+
+  // Shared memory starts finite: rows of holes / tokens past the end are never copied, and
+  // 0 * stale must not be NaN in the PV product.
+  for (int i = threadIdx.x; i < STAGES * STAGE_BYTES / 16; i += THREADS)
+    reinterpret_cast<uint4*>(smem_raw)[i] = make_uint4(0, 0, 0, 0);
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) ako::tc::mbar_init(ako::smem_u32(&s_full[s]), 2);  // warps 0 and 1
+    ako::tc::mbar_init_fence();
+  }
+  ako::tc::fence_proxy_async_smem();
+  __syncthreads();
+
+  // ---- producer state (warps 0-1: lane = one token of a tile) -----------------------------------
+  const int my_tok = warp * 32 + lane;  // meaningful for warps 0, 1
+  int32_t entry_next = 0;               // raw index entry for the next tile to be issued
+  auto fetch_entry = [&](int tile) {
+    int pos = tok_begin + tile * TILE + my_tok;
+    pos = min(pos, max(tok_end - 1, 0));
+    if (rd.count > 0) entry_next = __ldg(rd.idx + (p.page_size == 1 ? pos : pos / p.page_size));
+  };
+  auto issue_tile = [&](int tile) {  // uses entry_next fetched for `tile`
+    const int stage = tile % STAGES;
+    const uint32_t bar = ako::smem_u32(&s_full[stage]);
+    const int pos = tok_begin + tile * TILE + my_tok;
+    const bool valid = pos < tok_end && entry_next >= 0;
+    const int64_t crow = (p.page_size == 1) ? (int64_t)entry_next
+                                            : (int64_t)entry_next * p.page_size + pos % p.page_size;
+    const unsigned m = __ballot_sync(0xffffffffu, valid);
+    if (lane == 0) {
+      s_valid[stage][warp] = m;
+      ako::tc::mbar_arrive_expect_tx(bar, (uint32_t)__popc(m) * (CKV_ROW + KPE_ROW));
+    }
+    __syncwarp();
+    if (valid) {
+      const uint32_t dst = smem_base + stage * STAGE_BYTES;
+      ako::tc::bulk_load_1d(dst + my_tok * CKV_PITCH, p.ckv + crow * CKV_ROW, CKV_ROW, bar);
+      ako::tc::bulk_load_1d(dst + CKV_TILE_BYTES + my_tok * KPE_PITCH, p.kpe + crow * KPE_ROW, KPE_ROW, bar);
+    }
+  };
+  if (warp < 2) {
+    if (ntiles > 0) {
+      fetch_entry(0);
+      issue_tile(0);
+    }
+    fetch_entry(1);
+  }
 
   // Q fragments of this warp's reduction half: 18 k-steps of 16.
   uint32_t qa[18][4];
@@ -181,35 +190,19 @@ __global__ void __launch_bounds__(THREADS, 1) mla_attention_kernel(Params p) {
   for (int i = 0; i < 8; ++i) oacc[i][0] = oacc[i][1] = oacc[i][2] = oacc[i][3] = 0.f;
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
 
-  if (ntiles > 0) {
-    // prologue: indices of tile 0 (synchronous), then data of tile 0 + indices of tile 1 (async)
-    if (threadIdx.x < TILE) {
-      const int tok = tok_begin + threadIdx.x;
-      int32_t e = -1;
-      if (tok < tok_end) e = rd.idx[p.page_size == 1 ? tok : tok / p.page_size];
-      ring[threadIdx.x] = e;
-    }
-    __syncthreads();
-    load_tile(p, tiles, ring, tok_begin, tok_end);
-    if (ntiles > 1) load_indices_async(p, rd, ring, 1, tok_begin + TILE, tok_end);
-    ako::cp_async_commit();
-  }
-
   for (int it = 0; it < ntiles; ++it) {
-    ako::cp_async_wait<0>();
-    __syncthreads();
-    if (it + 1 < ntiles) {
-      load_tile(p, tiles + ((it + 1) & 1) * STAGE_ELEMS, ring + ((it + 1) % IDX_RING) * TILE,
-                tok_begin + (it + 1) * TILE, tok_end);
-      if (it + 2 < ntiles)
-        load_indices_async(p, rd, ring, (it + 2) % IDX_RING, tok_begin + (it + 2) * TILE, tok_end);
+    const int stage = it & 1;
+    const bool landed = ako::tc::mbar_wait(ako::smem_u32(&s_full[stage]), (uint32_t)((it >> 1) & 1),
+                                           &g_mla_status, 1);
+    // every warp has finished tile it-1: its stage (and s_valid entry) is free for tile it+1
+    if (!__syncthreads_and(landed)) break;
+    if (warp < 2) {
+      ako::tc::fence_proxy_async_smem();  // generic reads of the freed stage before async writes
+      if (it + 1 < ntiles) issue_tile(it + 1);
+      fetch_entry(it + 2);
     }
-    ako::cp_async_commit();
-
-    const __nv_bfloat16* Cs = tiles + (it & 1) * STAGE_ELEMS;
-    const __nv_bfloat16* Ps = Cs + CKV_TILE_ELEMS;
-    const int32_t* ring_cur = ring + (it % IDX_RING) * TILE;
-    const int tile_tok0 = tok_begin + it * TILE;
+    const uint32_t Cs = smem_base + stage * STAGE_BYTES;
+    const uint32_t Ps = Cs + CKV_TILE_BYTES;
 
     // ---- S phase: 16 tokens x half of the reduction --------------------------------------
     {
@@ -218,30 +211,30 @@ __global__ void __launch_bounds__(THREADS, 1) mla_attention_kernel(Params p) {
       for (int i = 0; i < 2; ++i) sacc[i][0] = sacc[i][1] = sacc[i][2] = sacc[i][3] = 0.f;
       const int tok = 16 * pw + ((lane >> 4) << 3) + (lane & 7);
       const int csel = (lane >> 3) & 1;
-      const int sw = tok & 7;
 #pragma unroll
       for (int ks = 0; ks < 18; ++ks) {
         uint32_t b00, b01, b10, b11;
         uint32_t addr;
         if (kh == 0 || ks < 14) {
           const int c = (kh == 0 ? 0 : 36) + 2 * ks + csel;  // 16-byte chunk of the 512-wide row
-          addr = ako::smem_u32(Cs + tok * DC + ((c ^ sw) << 3));
+          addr = Cs + tok * CKV_PITCH + (c << 4);
         } else {
           const int c = 2 * (ks - 14) + csel;
-          addr = ako::smem_u32(Ps + tok * DP + ((c ^ sw) << 3));
+          addr = Ps + tok * KPE_PITCH + (c << 4);
         }
         ako::ldmatrix_x4(b00, b01, b10, b11, addr);
         ako::mma_bf16_16816(sacc[0], qa[ks], b00, b01);
         ako::mma_bf16_16816(sacc[1], qa[ks], b10, b11);
       }
       float* sb = sbuf + kh * H * SROW;
+      const uint32_t vmask = s_valid[stage][pw >> 1];  // tokens 32*(pw>>1) ..
 #pragma unroll
       for (int nt = 0; nt < 2; ++nt) {
         const int c0 = 16 * pw + 8 * nt + 2 * t;
         float v0 = sacc[nt][0], v1 = sacc[nt][1], v2 = sacc[nt][2], v3 = sacc[nt][3];
         if (kh == 0) {  // the first half carries the validity mask
-          const bool ok0 = (tile_tok0 + c0 < tok_end) && (ring_cur[c0] >= 0);
-          const bool ok1 = (tile_tok0 + c0 + 1 < tok_end) && (ring_cur[c0 + 1] >= 0);
+          const bool ok0 = (vmask >> (c0 & 31)) & 1u;
+          const bool ok1 = (vmask >> ((c0 + 1) & 31)) & 1u;
           if (!ok0) { v0 = -INFINITY; v2 = -INFINITY; }
           if (!ok1) { v1 = -INFINITY; v3 = -INFINITY; }
         }
@@ -303,19 +296,17 @@ __global__ void __launch_bounds__(THREADS, 1) mla_attention_kernel(Params p) {
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const int tok = 16 * j + trow;
-        const int sw = tok & 7;
 #pragma unroll
         for (int nd = 0; nd < 8; nd += 2) {
           uint32_t v00, v01, v10, v11;
           const int c = 8 * warp + nd + csel;
-          ako::ldmatrix_x4_trans(v00, v01, v10, v11, ako::smem_u32(Cs + tok * DC + ((c ^ sw) << 3)));
+          ako::ldmatrix_x4_trans(v00, v01, v10, v11, Cs + tok * CKV_PITCH + (c << 4));
           ako::mma_bf16_16816(oacc[nd], pa[j], v00, v01);
           ako::mma_bf16_16816(oacc[nd + 1], pa[j], v10, v11);
         }
       }
     }
   }
-  ako::cp_async_wait<0>();
 
   // ---- epilogue ---------------------------------------------------------------------------------
 #pragma unroll
@@ -395,6 +386,17 @@ bool misaligned(const void* a, const void* b, const void* c, const void* d, cons
   return (((uintptr_t)a | (uintptr_t)b | (uintptr_t)c | (uintptr_t)d | (uintptr_t)e) & 15) != 0;
 }
 
+void fill_common(Params& p, const void* q_nope, const void* q_pe, const void* ckv_cache,
+                 const void* kpe_cache, void* o, float* lse, float sm_scale) {
+  p.q_nope = (const __nv_bfloat16*)q_nope;
+  p.q_pe = (const __nv_bfloat16*)q_pe;
+  p.ckv = (const unsigned char*)ckv_cache;
+  p.kpe = (const unsigned char*)kpe_cache;
+  p.o = (__nv_bfloat16*)o;
+  p.lse = lse;
+  p.scale_log2 = sm_scale * AKO_LOG2E;
+}
+
 }  // namespace
 
 // ---- paged MLA decode ----------------------------------------------------------------------------
@@ -418,15 +420,9 @@ extern "C" int ako4x_mla_paged_decode(const void* q_nope, const void* q_pe, cons
   const size_t need = workspace_for(batch, splits);
   if (need > 0 && (!workspace || workspace_bytes < need)) return AKO4X_EWORKSPACE;
   Params p = {};
-  p.q_nope = (const __nv_bfloat16*)q_nope;
-  p.q_pe = (const __nv_bfloat16*)q_pe;
-  p.ckv = (const __nv_bfloat16*)ckv_cache;
-  p.kpe = (const __nv_bfloat16*)kpe_cache;
+  fill_common(p, q_nope, q_pe, ckv_cache, kpe_cache, o, lse, sm_scale);
   p.kv_indptr = kv_indptr;
   p.indices = kv_indices;
-  p.o = (__nv_bfloat16*)o;
-  p.lse = lse;
-  p.scale_log2 = sm_scale * AKO_LOG2E;
   p.page_size = (int)page_size;
   return launch<kDecode>(p, batch, splits, workspace, (cudaStream_t)stream);
 }
@@ -452,14 +448,8 @@ extern "C" int ako4x_dsa_sparse_attention(const void* q_nope, const void* q_pe, 
   const size_t need = workspace_for(tokens, splits);
   if (need > 0 && (!workspace || workspace_bytes < need)) return AKO4X_EWORKSPACE;
   Params p = {};
-  p.q_nope = (const __nv_bfloat16*)q_nope;
-  p.q_pe = (const __nv_bfloat16*)q_pe;
-  p.ckv = (const __nv_bfloat16*)ckv_cache;
-  p.kpe = (const __nv_bfloat16*)kpe_cache;
+  fill_common(p, q_nope, q_pe, ckv_cache, kpe_cache, o, lse, sm_scale);
   p.indices = sparse_indices;
-  p.o = (__nv_bfloat16*)o;
-  p.lse = lse;
-  p.scale_log2 = sm_scale * AKO_LOG2E;
   p.page_size = 1;
   p.topk = (int)topk;
   return launch<kSparse>(p, tokens, splits, workspace, (cudaStream_t)stream);
@@ -487,17 +477,19 @@ extern "C" int ako4x_mla_paged_prefill(const void* q_nope, const void* q_pe, con
   if (num_kv_indices > 0 && !kv_indices) return AKO4X_EINVAL;
   if (misaligned(q_nope, q_pe, ckv_cache, kpe_cache, o)) return AKO4X_EINVAL;
   Params p = {};
-  p.q_nope = (const __nv_bfloat16*)q_nope;
-  p.q_pe = (const __nv_bfloat16*)q_pe;
-  p.ckv = (const __nv_bfloat16*)ckv_cache;
-  p.kpe = (const __nv_bfloat16*)kpe_cache;
+  fill_common(p, q_nope, q_pe, ckv_cache, kpe_cache, o, lse, sm_scale);
   p.qo_indptr = qo_indptr;
   p.kv_indptr = kv_indptr;
   p.indices = kv_indices;
-  p.o = (__nv_bfloat16*)o;
-  p.lse = lse;
-  p.scale_log2 = sm_scale * AKO_LOG2E;
   p.page_size = (int)page_size;
   p.batch = (int)batch;
   return launch<kPrefill>(p, total_q, 1, nullptr, (cudaStream_t)stream);
+}
+
+// Status word of the attention kernels of this file: 0, or the code of a bounded wait that gave
+// up. Synchronises the device; meant for tests and post-mortems.
+extern "C" int ako4x_mla_attention_device_status(void) {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_mla_status, sizeof(int)) != cudaSuccess) return AKO4X_ELAUNCH;
+  return v;
 }

@@ -94,6 +94,10 @@ int ako4x_mla_paged_decode(const void* q_nope, const void* q_pe, const void* ckv
                            int64_t batch, int64_t num_kv_indices, int64_t page_size,
                            void* workspace, size_t workspace_bytes, void* stream);
 
+/* Device status word shared by the MLA decode / prefill / DSA sparse attention kernels (same
+ * meaning as ako4x_gqa_paged_decode_device_status; synchronises the device). */
+int ako4x_mla_attention_device_status(void);
+
 /* ---- a4. Paged causal MLA prefill ----------------------------------------------------------
  * Replaces run(q_nope, q_pe, ckv_cache, kpe_cache, qo_indptr, kv_indptr, kv_indices, sm_scale):
  *   reference/mla-paged-prefill-causal-h16-ckv512-kpe64-ps1/variants/
