@@ -75,7 +75,7 @@ class ExpertParallelMoE:
     """Expert-parallel wrapper; ``routing_fn`` / ``expert_fn`` / ``combine_fn`` default to the CUDA
     operators and can be replaced by CPU stand-ins to test the exchange logic under gloo."""
 
-    kernels_per_step = 7  # routing + (routing, scatter, 2 GEMMs, combine) + EP combine
+    kernels_per_step = 8  # routing + (routing, scatter, permute, 2 GEMMs, combine) + EP combine
 
     def __init__(self, rank: int, world: int, group=None, routing_fn=None, expert_fn=None,
                  combine_fn=None):

@@ -335,7 +335,8 @@ def ops_table(peaks, calls=15):
 # CPU oracle timing (cpu_baseline and --impl reference)
 # ---------------------------------------------------------------------------------------------
 def cpu_moe_sample(sample_tokens, steps, warmup):
-    """Tokens/s of the CPU oracle on `sample_tokens` tokens of the T=8192 workload."""
+    """Full-token equivalents/s (local pairs / 8 / time) of the CPU oracle on `sample_tokens`
+    tokens of the T=8192 workload."""
     import oracle
     from ako4x_b200 import workloads as W
     cores = os.cpu_count() or 1
@@ -348,7 +349,10 @@ def cpu_moe_sample(sample_tokens, steps, warmup):
     for _ in range(steps):
         oracle.moe_fp8_block_scale(*args)
     dt = (time.perf_counter() - t0) / max(1, steps)
-    return sample_tokens / dt, dt, cores
+    ids, _ = oracle.ds_routing(a["routing_logits"], a["routing_bias"], a["routed_scaling_factor"])
+    lo = a["local_expert_offset"]
+    pairs = int(((ids >= lo) & (ids < lo + 32)).sum())
+    return pairs / 8.0 / dt, dt, cores
 
 
 def run_reference(args):
@@ -360,15 +364,17 @@ def run_reference(args):
     warmup = max(0, min(args.warmup, 1))
     tps, dt, cores = cpu_moe_sample(sample, steps, warmup)
     line = {
-        "impl": "reference", "metric": "moe_fp8_tokens_per_s", "value": tps, "unit": "tokens/s",
+        "impl": "reference", "metric": "moe_fp8_tokens_per_s", "value": tps,
+        "unit": "tokens/s (full-token equivalents: 8 expert applications = 1 token)",
         "n_gpus": args.gpus, "steps": steps, "warmup": warmup, "ms_per_step": dt * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp32",
         "data": "synthetic",
         "config": {"workload": f"moe_fp8_block_scale T={MOE_TOKENS} E_local=32 H=7168 I=2048 (DeepSeek-V3 routing)",
                    "sample_tokens": sample},
-        "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "port",
+        "cpu_baseline": {"value": tps, "unit": "tokens/s (full-token equivalents)", "cores": cores, "kind": "port",
                          "sample": f"{sample} of {MOE_TOKENS} tokens per step, all 32 local experts resident"},
-        "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "e2e": {"value": tps, "unit": "tokens/s (full-token equivalents)", "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
@@ -390,11 +396,25 @@ def run_moe(args, rank, world, dist_on, peaks):
         launches_per_step = ep.kernels_per_step
     else:
         step = lambda: moe.run(*[a[k] for k in MOE_KEYS])
-        launches_per_step = 5
+        launches_per_step = 6  # routing, scatter, permute, GEMM1, GEMM2, combine
     with ClockSampler(torch.cuda.current_device()) as cs:
         ms = time_steps(step, args.steps, args.warmup, dist_on)
     clocks = cs.summary()
-    value = world * T * args.steps / (ms * 1e-3)
+    # Work done per step: (token, expert) pairs whose expert is owned by a participating rank.
+    # A token is fully processed after 8 expert applications, so value = pairs / 8 / time
+    # ("full-token equivalents"): with N ranks covering 32*N of the 256 experts it grows with N,
+    # and at N = 8 it equals plain tokens/s. Plain tokens-in-flight/s is reported beside it.
+    ids, _ = moe.ds_routing(a["routing_logits"], a["routing_bias"], a["routed_scaling_factor"])
+    if world > 1:
+        pairs_t = (ids < 32 * world).sum().to(torch.int64)
+        import torch.distributed as dist
+        dist.all_reduce(pairs_t)
+    else:
+        lo = a["local_expert_offset"]
+        pairs_t = ((ids >= lo) & (ids < lo + 32)).sum().to(torch.int64)
+    total_pairs = int(pairs_t.item())
+    value = total_pairs / 8.0 * args.steps / (ms * 1e-3)
+    tokens_in_flight = world * T * args.steps / (ms * 1e-3)
 
     # end to end: pinned host inputs -> device, run, result -> pinned host
     h_in = {k: pinned(a[k]) for k in ("routing_logits", "hidden_states", "hidden_states_scale")}
@@ -417,10 +437,12 @@ def run_moe(args, rank, world, dist_on, peaks):
     e2e_ms = time_steps(e2e_step, args.steps, min(args.warmup, 3), dist_on)
     h2d = sum(v.numel() * v.element_size() for v in h_in.values())
     d2h = h_out.numel() * h_out.element_size()
-    e2e_value = world * T * args.steps / (e2e_ms * 1e-3)
+    e2e_value = total_pairs / 8.0 * args.steps / (e2e_ms * 1e-3)
 
     line = {
-        "metric": "moe_fp8_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
+        "metric": "moe_fp8_tokens_per_s", "value": value,
+        "unit": "tokens/s (full-token equivalents: 8 expert applications = 1 token)", "n_gpus": world,
+        "tokens_in_flight_per_s": tokens_in_flight, "pairs_per_step": total_pairs,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3",
         "data": "synthetic",
@@ -429,12 +451,12 @@ def run_moe(args, rank, world, dist_on, peaks):
                    "parallelism": f"ep{world}" if world > 1 else "single",
                    "l2": "inputs larger than L2 (1.4 GB of expert weights per step)"},
         "clocks": clocks,
-        "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d,
+        "e2e": {"value": e2e_value, "unit": "tokens/s (full-token equivalents)", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h},
         "gpu_launches": launches_per_step * args.steps,
     }
     if rank == 0 and world == 1:
-        pairs, _ = moe_local_pairs(a)
+        pairs = total_pairs
         st = moe_stage_times(a, calls=5)
         fp8_peak = 2 * peaks["bf16_tflops"]
         achieved = pairs * FLOP_PER_PAIR_GEMM1 / (st[1] * 1e-3) / 1e12
@@ -554,7 +576,7 @@ def main():
             line["ops"] = ops_table(peaks)
         if not args.no_cpu_baseline:
             tps, dt, cores = cpu_moe_sample(64, 1, 0)
-            line["cpu_baseline"] = {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "port",
+            line["cpu_baseline"] = {"value": tps, "unit": "tokens/s (full-token equivalents)", "cores": cores, "kind": "port",
                                     "sample": "64 of 8192 tokens, one pass of the CPU oracle "
                                               f"({dt:.1f} s), all 32 local experts resident"}
     if dist_on:
