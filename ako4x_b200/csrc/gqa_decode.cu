@@ -18,7 +18,9 @@
 namespace {
 
 constexpr int HQ = 32, HKV = 8, D = 128, GROUP = HQ / HKV;
-constexpr int HPC = 4;        // KV heads per CTA (one per warp)
+constexpr int HPC = 4;        // KV heads per CTA (one per warp); 8 (2 KB rows, one CTA per SM) measured the same
+constexpr int HEAD_GROUPS = HKV / HPC;  // CTAs that share one (sequence, split)
+constexpr int CTAS_PER_SM = (HPC == 4) ? 2 : 1;
 constexpr int TILE = 16;      // tokens per pipeline stage
 constexpr int STAGES = 3;
 constexpr int THREADS = HPC * 32;
@@ -46,13 +48,13 @@ struct Params {
   int num_splits;
 };
 
-__global__ void __launch_bounds__(THREADS, 2) gqa_decode_kernel(Params p) {
+__global__ void __launch_bounds__(THREADS, CTAS_PER_SM) gqa_decode_kernel(Params p) {
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ __align__(8) uint64_t s_full[STAGES];
 
   const int split = blockIdx.x % p.num_splits;
-  const int half = (blockIdx.x / p.num_splits) & 1;
-  const int b = blockIdx.x / (p.num_splits * 2);
+  const int half = (blockIdx.x / p.num_splits) % HEAD_GROUPS;
+  const int b = blockIdx.x / (p.num_splits * HEAD_GROUPS);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   const int head0 = half * HPC;
@@ -243,7 +245,7 @@ __global__ void __launch_bounds__(THREADS, 2) gqa_decode_kernel(Params p) {
 int pick_splits(int64_t batch, int64_t num_kv_indices, int64_t page_size) {
   if (batch <= 0) return 1;
   const int64_t avg_len = num_kv_indices * page_size / batch;
-  int64_t want = ako::cdiv(1184, 2 * batch);          // ~4 resident waves of 148 SMs x 2 CTAs
+  int64_t want = ako::cdiv(148 * 4 * CTAS_PER_SM, HEAD_GROUPS * batch);  // ~4 resident waves
   int64_t cap = avg_len / 128;                         // keep chunks >= 128 tokens on average
   if (cap < 1) cap = 1;
   int64_t s = want < cap ? want : cap;
@@ -291,7 +293,7 @@ extern "C" int ako4x_gqa_paged_decode(const void* q, const void* k_cache, const 
   p.num_splits = splits;
 
   if (!ako::ensure_dynamic_smem<gqa_decode_kernel>(SMEM_BYTES)) return AKO4X_ELAUNCH;
-  const int64_t grid = batch * 2 * splits;
+  const int64_t grid = batch * HEAD_GROUPS * splits;
   if (grid > 0x7fffffffLL) return AKO4X_EINVAL;
   gqa_decode_kernel<<<(unsigned)grid, THREADS, SMEM_BYTES, st>>>(p);
   AKO_CHECK_LAUNCH();
