@@ -123,7 +123,9 @@ __global__ void __launch_bounds__(THREADS, 1) mla_attention_kernel(Params p) {
   for (int i = threadIdx.x; i < STAGES * STAGE_BYTES / 16; i += THREADS)
     reinterpret_cast<uint4*>(smem_raw)[i] = make_uint4(0, 0, 0, 0);
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) ako::tc::mbar_init(ako::smem_u32(&s_full[s]), 2);  // warps 0 and 1
+    // arrivals per phase: warps 0 and 1 (bulk copies, with byte counts) + one deferred arrival per
+    // thread that fires when its kpe cp.async copies have landed
+    for (int s = 0; s < STAGES; ++s) ako::tc::mbar_init(ako::smem_u32(&s_full[s]), 2 + THREADS);
     ako::tc::mbar_init_fence();
   }
   ako::tc::fence_proxy_async_smem();
@@ -132,10 +134,39 @@ __global__ void __launch_bounds__(THREADS, 1) mla_attention_kernel(Params p) {
   // ---- producer state (warps 0-1: lane = one token of a tile) -----------------------------------
   const int my_tok = warp * 32 + lane;  // meaningful for warps 0, 1
   int32_t entry_next = 0;               // raw index entry for the next tile to be issued
+  // kpe rows (128 B) go through 16-byte cp.async instead: a bulk copy costs the copy engine the
+  // same whatever its size, and one per token (the 1 KB ckv row) is what it sustains. Thread t
+  // copies chunk t&7 of tokens t>>3 and (t>>3)+32 of the tile.
+  int32_t kentry_next[2] = {0, 0};
   auto fetch_entry = [&](int tile) {
-    int pos = tok_begin + tile * TILE + my_tok;
-    pos = min(pos, max(tok_end - 1, 0));
-    if (rd.count > 0) entry_next = __ldg(rd.idx + (p.page_size == 1 ? pos : pos / p.page_size));
+    if (rd.count <= 0) return;
+    const int last = max(tok_end - 1, 0);
+    if (warp < 2) {
+      const int pos = min(tok_begin + tile * TILE + my_tok, last);
+      entry_next = __ldg(rd.idx + (p.page_size == 1 ? pos : pos / p.page_size));
+    }
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const int pos = min(tok_begin + tile * TILE + (int)(threadIdx.x >> 3) + 32 * j, last);
+      kentry_next[j] = __ldg(rd.idx + (p.page_size == 1 ? pos : pos / p.page_size));
+    }
+  };
+  auto issue_kpe = [&](int tile) {  // every thread; uses kentry_next fetched for `tile`
+    const int stage = tile % STAGES;
+    const int c = threadIdx.x & 7;
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const int tk = (int)(threadIdx.x >> 3) + 32 * j;
+      const int pos = tok_begin + tile * TILE + tk;
+      const bool valid = pos < tok_end && kentry_next[j] >= 0;
+      const int64_t crow = !valid ? 0
+                           : (p.page_size == 1) ? (int64_t)kentry_next[j]
+                                                : (int64_t)kentry_next[j] * p.page_size + pos % p.page_size;
+      ako::cp_async16(smem_base + stage * STAGE_BYTES + CKV_TILE_BYTES + tk * KPE_PITCH + c * 16,
+                      p.kpe + crow * KPE_ROW + c * 16, valid);
+    }
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];\n" ::"r"(ako::smem_u32(&s_full[stage]))
+                 : "memory");
   };
   auto issue_tile = [&](int tile) {  // uses entry_next fetched for `tile`
     const int stage = tile % STAGES;
@@ -147,22 +178,20 @@ __global__ void __launch_bounds__(THREADS, 1) mla_attention_kernel(Params p) {
     const unsigned m = __ballot_sync(0xffffffffu, valid);
     if (lane == 0) {
       s_valid[stage][warp] = m;
-      ako::tc::mbar_arrive_expect_tx(bar, (uint32_t)__popc(m) * (CKV_ROW + KPE_ROW));
+      ako::tc::mbar_arrive_expect_tx(bar, (uint32_t)__popc(m) * CKV_ROW);
     }
     __syncwarp();
     if (valid) {
       const uint32_t dst = smem_base + stage * STAGE_BYTES;
       ako::tc::bulk_load_1d(dst + my_tok * CKV_PITCH, p.ckv + crow * CKV_ROW, CKV_ROW, bar);
-      ako::tc::bulk_load_1d(dst + CKV_TILE_BYTES + my_tok * KPE_PITCH, p.kpe + crow * KPE_ROW, KPE_ROW, bar);
     }
   };
-  if (warp < 2) {
-    if (ntiles > 0) {
-      fetch_entry(0);
-      issue_tile(0);
-    }
-    fetch_entry(1);
+  if (ntiles > 0) {
+    fetch_entry(0);
+    if (warp < 2) issue_tile(0);
+    issue_kpe(0);
   }
+  fetch_entry(1);
 
   // Q fragments of this warp's reduction half: 18 k-steps of 16.
   uint32_t qa[18][4];
@@ -196,11 +225,14 @@ __global__ void __launch_bounds__(THREADS, 1) mla_attention_kernel(Params p) {
                                            &g_mla_status, 1);
     // every warp has finished tile it-1: its stage (and s_valid entry) is free for tile it+1
     if (!__syncthreads_and(landed)) break;
-    if (warp < 2) {
-      ako::tc::fence_proxy_async_smem();  // generic reads of the freed stage before async writes
-      if (it + 1 < ntiles) issue_tile(it + 1);
-      fetch_entry(it + 2);
+    if (it + 1 < ntiles) {
+      if (warp < 2) {
+        ako::tc::fence_proxy_async_smem();  // generic reads of the freed stage before async writes
+        issue_tile(it + 1);
+      }
+      issue_kpe(it + 1);
     }
+    fetch_entry(it + 2);
     const uint32_t Cs = smem_base + stage * STAGE_BYTES;
     const uint32_t Ps = Cs + CKV_TILE_BYTES;
 
