@@ -77,6 +77,7 @@ _SIGNATURES = {
     "ako4x_dsa_topk_indexer": (_INT, [_P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _P, _SZ, _P]),
     "ako4x_dsa_index_scores": (_INT, [_P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _P]),
     "ako4x_dsa_topk_select": (_INT, [_P, _P, _P, _P, _I64, _I64, _P]),
+    "ako4x_dsa_indexer_device_status": (_INT, []),
     "ako4x_dsa_sparse_attention_workspace_bytes": (_SZ, [_I64, _I64]),
     "ako4x_dsa_sparse_attention": (_INT, [_P, _P, _P, _P, _P, _F32, _P, _P, _I64, _I64, _I64, _P, _SZ, _P]),
     "ako4x_moe_fp8_block_scale_workspace_bytes": (_SZ, [_I64, _I64]),

@@ -1,12 +1,9 @@
 // DSA top-k indexer: FP8 index scores + exact top-2048 selection.
 //
-// Score kernel: for query row r and token t, score = (sum_h w[r,h] * relu(q[r,h,:] . k[t,:])) *
-// kscale[t]. Tokens are the M dimension of mma.sync.m16n8k32 (e4m3 x e4m3 -> fp32), the 64 index
-// heads the N dimension, so relu, the head weights and the head reduction all happen in the
-// accumulator registers of the thread that owns the token (two shuffles finish the sum). A warp
-// owns one 64-token cache page at a time: the 8 KB of e4m3 values are copied with cp.async into a
-// private double-buffered shared-memory slot (16-byte chunks XOR-swizzled by token) and read back
-// with ldmatrix; Q fragments and head weights stay in registers. Scores are written as fp32.
+// Score kernel: score = (sum_h w[r,h] * relu(q[r,h,:] . k[t,:])) * kscale[t] on the tcgen05 tensor
+// cores (dsa_score_tc.cuh): tokens on the M dimension / TMEM lanes, heads of up to four query rows
+// on the N dimension, TMA-fed, relu + head weights + head sum as per-thread arithmetic on the
+// accumulator. Scores are written as fp32.
 //
 // Select kernel: one CTA per row. Keys are the order-preserving unsigned image of the fp32 scores;
 // a 4 x 8-bit most-significant-digit radix select (warp-aggregated shared-memory histograms)
@@ -14,6 +11,8 @@
 // the threshold plus the first tokens equal to it (ties: lower position wins), translated to
 // global cache slots through the block table.
 #include "common.cuh"
+#include "tcgen05.cuh"
+#include "tma_host.cuh"
 
 namespace {
 
@@ -21,124 +20,9 @@ constexpr int NH = 64, HD = 128, PS = 64, TOPK = 2048;
 constexpr int PAGE_BYTES = PS * HD + PS * 4;  // 8448
 
 // ---------------------------------------------------------------------------------------------
-// score kernel
+// score kernel (tensor cores)
 // ---------------------------------------------------------------------------------------------
-constexpr int SC_WARPS = 4;
-constexpr int SC_THREADS = SC_WARPS * 32;
-constexpr int SC_MAX_PAGES_PER_WARP = 8;  // pages a warp walks; fewer when the grid would be small
-constexpr int SC_SMEM = SC_WARPS * 2 * PS * HD;  // 64 KB
-
-__device__ __forceinline__ void load_page(unsigned char* slot, const unsigned char* page, int lane) {
-  // 64 rows x 8 chunks of 16 B; a warp pass covers 4 rows.
-#pragma unroll
-  for (int pass = 0; pass < 16; ++pass) {
-    const int row = pass * 4 + (lane >> 3);
-    const int c = lane & 7;
-    ako::cp_async16(ako::smem_u32(slot + row * HD + ((c ^ (row & 7)) << 4)), page + row * HD + c * 16);
-  }
-}
-
-__global__ void __launch_bounds__(SC_THREADS) dsa_score_kernel(
-    const unsigned char* __restrict__ q, const unsigned char* __restrict__ cache,
-    const float* __restrict__ weights, const int32_t* __restrict__ seq_lens,
-    const int32_t* __restrict__ block_table, float* __restrict__ scores, int max_pages,
-    int64_t num_cache_pages, int skip_short, int pages_per_warp) {
-  extern __shared__ __align__(128) unsigned char smem[];
-  const int r = blockIdx.x;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int g = lane >> 2, t = lane & 3;
-  ako::pdl_trigger();
-  const int sl = seq_lens[r];
-  float* out = scores + (int64_t)r * max_pages * PS;
-  const int page_lo = blockIdx.y * SC_WARPS * pages_per_warp;
-  if (sl <= 0 || (skip_short && sl <= TOPK)) return;
-  const int npages = min(max_pages, (sl + PS - 1) / PS);
-
-  // B fragments: Q[head][k] for 8 n-tiles x 4 k-steps, and this thread's head weights.
-  uint32_t qb[8][4][2];
-  float wv[8][2];
-  {
-    const unsigned char* qr = q + (int64_t)r * NH * HD;
-#pragma unroll
-    for (int nt = 0; nt < 8; ++nt) {
-      const unsigned char* qh = qr + (nt * 8 + g) * HD;
-#pragma unroll
-      for (int ks = 0; ks < 4; ++ks) {
-        qb[nt][ks][0] = *reinterpret_cast<const uint32_t*>(qh + ks * 32 + 4 * t);
-        qb[nt][ks][1] = *reinterpret_cast<const uint32_t*>(qh + ks * 32 + 16 + 4 * t);
-      }
-      const float2 w2 = *reinterpret_cast<const float2*>(weights + (int64_t)r * NH + nt * 8 + 2 * t);
-      wv[nt][0] = w2.x;
-      wv[nt][1] = w2.y;
-    }
-  }
-
-  unsigned char* slot0 = smem + warp * 2 * PS * HD;
-  const int32_t* bt = block_table + (int64_t)r * max_pages;
-  // pages of this warp: page_lo + warp + SC_WARPS * j
-  int pg_next = page_lo + warp;
-  int64_t phys_cur = -1, phys_next = -1;
-  if (pg_next < npages) {
-    phys_next = bt[pg_next];
-    if (phys_next < 0 || phys_next >= num_cache_pages) phys_next = 0;  // out-of-range id: stay in bounds
-    load_page(slot0, cache + phys_next * PAGE_BYTES, lane);
-  }
-  ako::cp_async_commit();
-
-  for (int j = 0; j < pages_per_warp; ++j) {
-    const int pg = page_lo + warp + SC_WARPS * j;
-    if (pg >= npages) break;
-    phys_cur = phys_next;
-    pg_next = pg + SC_WARPS;
-    if (j + 1 < pages_per_warp && pg_next < npages) {
-      phys_next = bt[pg_next];
-      if (phys_next < 0 || phys_next >= num_cache_pages) phys_next = 0;
-      load_page(slot0 + ((j + 1) & 1) * PS * HD, cache + phys_next * PAGE_BYTES, lane);
-    }
-    ako::cp_async_commit();
-    ako::cp_async_wait<1>();
-    __syncwarp();
-    const unsigned char* ks_smem = slot0 + (j & 1) * PS * HD;
-    const float* kscale = reinterpret_cast<const float*>(cache + phys_cur * PAGE_BYTES + PS * HD);
-
-#pragma unroll 1
-    for (int mt = 0; mt < 4; ++mt) {  // 16 tokens per m-tile
-      uint32_t a[4][4];
-      {
-        const int row = mt * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
-#pragma unroll
-        for (int ks = 0; ks < 4; ++ks) {
-          const int c = 2 * ks + (lane >> 4);
-          ako::ldmatrix_x4(a[ks][0], a[ks][1], a[ks][2], a[ks][3],
-                           ako::smem_u32(ks_smem + row * HD + ((c ^ (row & 7)) << 4)));
-        }
-      }
-      float s0 = 0.f, s1 = 0.f;  // tokens g and g+8 of the m-tile
-#pragma unroll
-      for (int nt = 0; nt < 8; ++nt) {
-        float c[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-        for (int ks = 0; ks < 4; ++ks) ako::mma_e4m3_16832(c, a[ks], qb[nt][ks][0], qb[nt][ks][1]);
-        s0 = fmaf(fmaxf(c[0], 0.f), wv[nt][0], s0);
-        s0 = fmaf(fmaxf(c[1], 0.f), wv[nt][1], s0);
-        s1 = fmaf(fmaxf(c[2], 0.f), wv[nt][0], s1);
-        s1 = fmaf(fmaxf(c[3], 0.f), wv[nt][1], s1);
-      }
-      s0 += __shfl_xor_sync(0xffffffffu, s0, 1);
-      s0 += __shfl_xor_sync(0xffffffffu, s0, 2);
-      s1 += __shfl_xor_sync(0xffffffffu, s1, 1);
-      s1 += __shfl_xor_sync(0xffffffffu, s1, 2);
-      if (t < 2) {
-        const int tok_in_page = mt * 16 + g + 8 * t;
-        const int tok = pg * PS + tok_in_page;
-        const float v = (t == 0 ? s0 : s1) * __ldg(kscale + tok_in_page);
-        out[tok] = (tok < sl) ? v : -INFINITY;
-      }
-    }
-    __syncwarp();  // the slot is overwritten two iterations later; keep the warp together
-  }
-  ako::cp_async_wait<0>();
-}
+#include "dsa_score_tc.cuh"
 
 // ---------------------------------------------------------------------------------------------
 // select kernel
@@ -263,18 +147,40 @@ __global__ void __launch_bounds__(SEL_THREADS) dsa_select_kernel(
   }
 }
 
+int sm_count() {
+  static int cached[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
 int launch_scores(const void* q, const void* cache, const float* weights, const int32_t* seq_lens,
                   const int32_t* block_table, float* scores, int64_t rows, int64_t max_pages,
                   int64_t num_cache_pages, int skip_short, cudaStream_t st) {
-  if (!ako::ensure_dynamic_smem<dsa_score_kernel>(SC_SMEM)) return AKO4X_ELAUNCH;
-  // enough CTAs for ~4 waves of 148 SMs x 3 resident CTAs, at most 8 pages per warp
-  int64_t ppw = rows * max_pages / (SC_WARPS * 1776);
-  if (ppw < 1) ppw = 1;
-  if (ppw > SC_MAX_PAGES_PER_WARP) ppw = SC_MAX_PAGES_PER_WARP;
-  dim3 grid((unsigned)rows, (unsigned)ako::cdiv(max_pages, SC_WARPS * ppw));
-  dsa_score_kernel<<<grid, SC_THREADS, SC_SMEM, st>>>(
-      (const unsigned char*)q, (const unsigned char*)cache, weights, seq_lens, block_table, scores,
-      (int)max_pages, num_cache_pages, skip_short, (int)ppw);
+  if (num_cache_pages < 1) return AKO4X_EINVAL;
+  if (!ako::ensure_dynamic_smem<dsa_score_tc_kernel>(TS_SMEM)) return AKO4X_ELAUNCH;
+  CUtensorMap tm_q, tm_k;
+  if (!ako::tma::byte_matrix_map(&tm_q, q, (uint64_t)rows * NH, HD, NH) ||
+      !ako::tma::paged_byte_matrix_map(&tm_k, cache, (uint64_t)num_cache_pages, PAGE_BYTES, PS))
+    return AKO4X_ELAUNCH;
+  ScoreParams p;
+  p.weights = weights;
+  p.seq_lens = seq_lens;
+  p.block_table = block_table;
+  p.cache = (const unsigned char*)cache;
+  p.scores = scores;
+  p.rows = (int)rows;
+  p.max_pages = (int)max_pages;
+  p.num_cache_pages = num_cache_pages;
+  p.skip_short = skip_short;
+  const int64_t units = ako::cdiv(rows, TS_ROWS) * ako::cdiv(max_pages, 2);
+  const int grid = (int)(units < sm_count() ? units : sm_count());
+  dsa_score_tc_kernel<<<grid, TS_THREADS, TS_SMEM, st>>>(p, tm_q, tm_k);
   AKO_CHECK_LAUNCH();
   return AKO4X_OK;
 }
@@ -353,4 +259,12 @@ extern "C" int ako4x_dsa_topk_indexer(const void* q_index_fp8, const void* k_ind
     pdl = true;
   }
   return launch_select(scores, seq_lens, block_table, topk_indices, rows, max_pages, pdl, st);
+}
+
+// Status word of the score kernel: 0, or the code of a bounded wait that gave up. Synchronises
+// the device; meant for tests and post-mortems.
+extern "C" int ako4x_dsa_indexer_device_status(void) {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_dsa_status, sizeof(int)) != cudaSuccess) return AKO4X_ELAUNCH;
+  return v;
 }

@@ -62,6 +62,14 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, int 
       "l"(tmap), "r"(bar), "r"(x), "r"(y)
       : "memory");
 }
+// 3-D tiled load (x innermost); the same alignment rule for x.
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const void* tmap, int x, int y, int z, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];\n" ::
+          "r"(dst),
+      "l"(tmap), "r"(bar), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
 // 1-D bulk copy of `bytes` (multiple of 16, both addresses 16-byte aligned) global -> shared.
 __device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(dst),

@@ -138,6 +138,10 @@ int ako4x_dsa_index_scores(const void* q_index_fp8, const void* k_index_cache, c
 int ako4x_dsa_topk_select(const float* scores, const int32_t* seq_lens, const int32_t* block_table,
                           int32_t* topk_indices, int64_t rows, int64_t max_pages, void* stream);
 
+/* Device status word of the tensor-core score kernel (same meaning as
+ * ako4x_gqa_paged_decode_device_status; synchronises the device). */
+int ako4x_dsa_indexer_device_status(void);
+
 /* ---- a6. DSA sparse MLA attention ----------------------------------------------------------
  * Replaces run(q_nope, q_pe, ckv_cache, kpe_cache, sparse_indices, sm_scale):
  *   reference/dsa-sparse-attention/variants/hybrid_pdl_v2/kernel.py:557-626
