@@ -28,20 +28,98 @@ constexpr int PAGE_BYTES = PS * HD + PS * 4;  // 8448
 // select kernel
 // ---------------------------------------------------------------------------------------------
 constexpr int SEL_THREADS = 1024;
+constexpr int SEL_PER = 32;                          // tokens per thread and chunk
+constexpr int SEL_CHUNK = SEL_THREADS * SEL_PER;     // 32768 tokens: one shared-memory resident chunk
+constexpr int SEL_BINS = 2048;                       // widest digit: 11 bits
+constexpr int SEL_SMEM = SEL_CHUNK * 4;              // 128 KB of keys
 
 __device__ __forceinline__ uint32_t order_key(float s) {
   const uint32_t b = __float_as_uint(s + 0.0f);  // -0 -> +0
   return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
 }
 
-__global__ void __launch_bounds__(SEL_THREADS) dsa_select_kernel(
+// Keys live in shared memory as 16-byte slots of four consecutive tokens. Slot f is stored at
+// f ^ ((f >> 3) & 7): conflict-free both for the coalesced fill (lane = slot) and for the
+// compaction, where a thread reads its own eight consecutive slots.
+__device__ __forceinline__ int sel_slot(int f) { return f ^ ((f >> 3) & 7); }
+
+// Fills the chunk's keys; tokens at or past `sl` get key 0 (below every finite score).
+__device__ __forceinline__ void sel_fill(uint4* skeys, const float* __restrict__ s, int chunk, int sl, int tid) {
+#pragma unroll
+  for (int it = 0; it < SEL_PER / 4; ++it) {
+    const int f = it * SEL_THREADS + tid;
+    const int i = chunk * SEL_CHUNK + 4 * f;  // a row is a whole number of 64-token pages: no overrun
+    uint4 k = make_uint4(0u, 0u, 0u, 0u);
+    if (i < sl) {
+      const float4 v = __ldg(reinterpret_cast<const float4*>(s + i));
+      k.x = order_key(v.x);
+      k.y = (i + 1 < sl) ? order_key(v.y) : 0u;
+      k.z = (i + 2 < sl) ? order_key(v.z) : 0u;
+      k.w = (i + 3 < sl) ? order_key(v.w) : 0u;
+    }
+    skeys[sel_slot(f)] = k;
+  }
+}
+
+// Inclusive suffix sum over the block of one int per thread (thread 0 gets the block total).
+// `buf` holds one int per warp. Two barriers.
+__device__ __forceinline__ int block_suffix_sum(int x, int* buf, int lane, int warp) {
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) {
+    const int y = __shfl_down_sync(0xffffffffu, x, off);
+    if (lane + off < 32) x += y;
+  }
+  if (lane == 0) buf[warp] = x;
+  __syncthreads();
+  int w = buf[lane];  // SEL_THREADS / 32 == 32 warps
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) {
+    const int y = __shfl_down_sync(0xffffffffu, w, off);
+    if (lane + off < 32) w += y;
+  }
+  const int after = __shfl_sync(0xffffffffu, w, (warp + 1) & 31);
+  __syncthreads();
+  return x + ((warp < 31) ? after : 0);
+}
+
+template <int PASS>
+__device__ __forceinline__ void sel_count(int* hist, uint32_t key, uint32_t prefix, int lane) {
+  constexpr int shift = (PASS == 0) ? 21 : (PASS == 1) ? 10 : 0;
+  constexpr uint32_t dmask = (PASS == 2) ? 0x3ffu : 0x7ffu;
+  constexpr uint32_t hi_mask = (PASS == 0) ? 0u : (PASS == 1) ? 0xffe00000u : 0xfffffc00u;
+  if (PASS == 0) {
+    // the leading digit (sign, exponent, two mantissa bits) repeats heavily: one atomic per
+    // distinct digit per warp
+    const uint32_t digit = key >> shift;
+    const unsigned peers = __match_any_sync(0xffffffffu, digit);
+    if (lane == (__ffs(peers) - 1)) atomicAdd(&hist[digit], __popc(peers));
+  } else if ((key & hi_mask) == prefix) {
+    atomicAdd(&hist[(key >> shift) & dmask], 1);
+  }
+}
+
+template <int PASS>
+__device__ __forceinline__ void sel_pass(int* hist, const uint4* skeys, uint32_t prefix, int tid, int lane) {
+#pragma unroll
+  for (int it = 0; it < SEL_PER / 4; ++it) {
+    const uint4 k = skeys[it * SEL_THREADS + tid];  // histogram: any order will do
+    sel_count<PASS>(hist, k.x, prefix, lane);
+    sel_count<PASS>(hist, k.y, prefix, lane);
+    sel_count<PASS>(hist, k.z, prefix, lane);
+    sel_count<PASS>(hist, k.w, prefix, lane);
+  }
+}
+
+__global__ void __launch_bounds__(SEL_THREADS, 1) dsa_select_kernel(
     const float* __restrict__ scores, const int32_t* __restrict__ seq_lens,
     const int32_t* __restrict__ block_table, int32_t* __restrict__ out, int max_pages) {
-  __shared__ int hist[256];
+  extern __shared__ __align__(16) unsigned char sel_smem[];
+  __shared__ int hist[SEL_BINS];
   __shared__ int scan_buf[SEL_THREADS / 32];
+  __shared__ int scan_buf2[SEL_THREADS / 32];
   __shared__ uint32_t s_prefix;
   __shared__ int s_krem;
-  __shared__ int s_gt_base, s_eq_base;
+  uint4* skeys = reinterpret_cast<uint4*>(sel_smem);
 
   const int r = blockIdx.x;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -57,92 +135,100 @@ __global__ void __launch_bounds__(SEL_THREADS) dsa_select_kernel(
   }
   ako::pdl_wait();
   const float* s = scores + (int64_t)r * max_pages * PS;
+  // Up to 32768 tokens the keys are read from global memory once and stay in shared memory;
+  // longer rows are swept chunk by chunk in every pass.
+  const int chunks = (sl + SEL_CHUNK - 1) / SEL_CHUNK;
+  sel_fill(skeys, s, 0, sl, tid);
 
-  if (tid == 0) { s_prefix = 0u; s_krem = TOPK; }
-  const int n_iter = (sl + SEL_THREADS - 1) / SEL_THREADS;
-
-  for (int d = 3; d >= 0; --d) {
-    if (tid < 256) hist[tid] = 0;
-    __syncthreads();
-    const uint32_t prefix = s_prefix;
-    const int krem_in = s_krem;  // read before anyone updates it at the end of this pass
-    const int shift = 8 * d;
-    const uint32_t hi_mask = (d == 3) ? 0u : (0xffffffffu << (shift + 8));
-    for (int it = 0; it < n_iter; ++it) {
-      const int i = it * SEL_THREADS + tid;
-      uint32_t digit = 0x100u | lane;  // sentinel: groups with nobody
-      if (i < sl) {
-        const uint32_t key = order_key(s[i]);
-        if ((key & hi_mask) == prefix) digit = (key >> shift) & 0xffu;
+  // ---- threshold: most-significant-digit radix select, digits of 11, 11 and 10 bits ------------
+  // Padding keys (0) only ever land in the lowest bin, below the 2048-th largest real key.
+  uint32_t prefix = 0u;
+  int krem = TOPK;
+#pragma unroll 1
+  for (int pass = 0; pass < 3; ++pass) {
+    const int shift = (pass == 0) ? 21 : (pass == 1) ? 10 : 0;
+    hist[tid] = 0;
+    hist[tid + SEL_THREADS] = 0;
+    __syncthreads();  // also: the keys are in place
+#pragma unroll 1
+    for (int c = 0; c < chunks; ++c) {
+      if (chunks > 1) {
+        __syncthreads();
+        sel_fill(skeys, s, c, sl, tid);
+        __syncthreads();
       }
-      const unsigned peers = __match_any_sync(0xffffffffu, digit);
-      if (digit < 0x100u && lane == (__ffs(peers) - 1)) atomicAdd(&hist[digit], __popc(peers));
+      if (pass == 0) sel_pass<0>(hist, skeys, prefix, tid, lane);
+      else if (pass == 1) sel_pass<1>(hist, skeys, prefix, tid, lane);
+      else sel_pass<2>(hist, skeys, prefix, tid, lane);
     }
     __syncthreads();
-    // inclusive suffix sums over the 256 bins (Hillis-Steele, 8 steps)
-    int v = (tid < 256) ? hist[tid] : 0;
-    const int own = v;
-    for (int off = 1; off < 256; off <<= 1) {
-      int add = 0;
-      if (tid < 256 && tid + off < 256) add = hist[tid + off];
-      __syncthreads();
-      if (tid < 256) { v += add; hist[tid] = v; }
-      __syncthreads();
-    }
-    // v = count(digit >= tid); pick the bin where the k-th largest lives
-    if (tid < 256) {
-      const int gt = v - own;
-      if (gt < krem_in && krem_in <= v) {
-        s_prefix = prefix | ((uint32_t)tid << shift);
-        s_krem = krem_in - gt;
-      }
+    // thread t owns bins 2t and 2t+1; suffix sums give count(digit >= bin)
+    const int h0 = hist[2 * tid], h1 = hist[2 * tid + 1];
+    const int incl = block_suffix_sum(h0 + h1, scan_buf, lane, warp);
+    const int gt1 = incl - (h0 + h1);  // keys with a larger digit than bin 2t+1
+    const int gt0 = gt1 + h1;
+    if (gt1 < krem && krem <= gt1 + h1) {
+      s_prefix = prefix | ((uint32_t)(2 * tid + 1) << shift);
+      s_krem = krem - gt1;
+    } else if (gt0 < krem && krem <= gt0 + h0) {
+      s_prefix = prefix | ((uint32_t)(2 * tid) << shift);
+      s_krem = krem - gt0;
     }
     __syncthreads();
+    prefix = s_prefix;
+    krem = s_krem;  // how many keys of the chosen bin are still to be taken
   }
-  const uint32_t thr = s_prefix;
-  const int krem = s_krem;  // how many keys equal to thr are taken (lowest positions first)
-  if (tid == 0) { s_gt_base = 0; s_eq_base = 0; }
-  __syncthreads();
+  const uint32_t thr = prefix;
 
-  for (int it = 0; it < n_iter; ++it) {
-    const int i = it * SEL_THREADS + tid;
-    uint32_t key = 0u;
-    const bool in = i < sl;
-    if (in) key = order_key(s[i]);
-    const bool is_gt = in && key > thr;
-    const bool is_eq = in && key == thr;
-    // block-wide exclusive scan of (gt, eq) packed as eq<<16 | gt
-    const unsigned bg = __ballot_sync(0xffffffffu, is_gt);
-    const unsigned be = __ballot_sync(0xffffffffu, is_eq);
-    const unsigned lt_mask = (1u << lane) - 1u;
-    int my = __popc(bg & lt_mask) | (__popc(be & lt_mask) << 16);
-    if (lane == 0) scan_buf[warp] = __popc(bg) | (__popc(be) << 16);
-    __syncthreads();
-    if (warp == 0) {
-      int x = scan_buf[lane];
-      int incl = x;
+  // ---- stable compaction in token order: keys above thr, plus the first `krem` equal to it ----
+  // Thread t owns the 32 consecutive tokens of its eight slots.
+  int g_base = 0, e_base = 0;
+#pragma unroll 1
+  for (int c = 0; c < chunks; ++c) {
+    if (chunks > 1) {
+      __syncthreads();
+      sel_fill(skeys, s, c, sl, tid);
+      __syncthreads();
+    }
+    const int tok0 = c * SEL_CHUNK + tid * SEL_PER;
+    const int nvalid = max(0, min(SEL_PER, sl - tok0));
+    uint32_t gmask = 0u, emask = 0u;  // bit j: token tok0 + j is above / equal to the threshold
 #pragma unroll
-      for (int off = 1; off < 32; off <<= 1) {
-        const int y = __shfl_up_sync(0xffffffffu, incl, off);
-        if (lane >= off) incl += y;
+    for (int q = 0; q < SEL_PER / 4; ++q) {
+      const uint4 k = skeys[sel_slot(tid * (SEL_PER / 4) + q)];
+      gmask |= ((k.x > thr) ? 1u : 0u) << (4 * q) | ((k.y > thr) ? 2u : 0u) << (4 * q) |
+               ((k.z > thr) ? 4u : 0u) << (4 * q) | ((k.w > thr) ? 8u : 0u) << (4 * q);
+      emask |= ((k.x == thr) ? 1u : 0u) << (4 * q) | ((k.y == thr) ? 2u : 0u) << (4 * q) |
+               ((k.z == thr) ? 4u : 0u) << (4 * q) | ((k.w == thr) ? 8u : 0u) << (4 * q);
+    }
+    const uint32_t vmask = (nvalid >= 32) ? 0xffffffffu : ((1u << nvalid) - 1u);
+    gmask &= vmask;
+    emask &= vmask;
+    const int ng = __popc(gmask), ne = __popc(emask);
+    const int sg = block_suffix_sum(ng, scan_buf, lane, warp);
+    const int se = block_suffix_sum(ne, scan_buf2, lane, warp);
+    if (tid == 0) { scan_buf[0] = sg; scan_buf2[0] = se; }  // thread 0's suffix sum is the total
+    __syncthreads();
+    const int block_g = scan_buf[0], block_e = scan_buf2[0];
+    int G = g_base + block_g - sg;  // above-threshold tokens before this thread's
+    int E = e_base + block_e - se;  // threshold-valued tokens before this thread's
+    uint32_t m = gmask | emask;
+    while (m) {
+      const int j = __ffs(m) - 1;
+      m &= m - 1;
+      const int i = tok0 + j;
+      int pos;
+      if (gmask >> j & 1u) {
+        pos = G + min(E, krem);
+        ++G;
+      } else {
+        pos = (E < krem) ? G + E : TOPK;
+        ++E;
       }
-      scan_buf[lane] = incl - x;  // exclusive
-      if (lane == 31) hist[0] = incl;  // chunk total (hist is free now)
+      if (pos < TOPK) o[pos] = bt[i >> 6] * PS + (i & 63);
     }
-    __syncthreads();
-    my += scan_buf[warp];
-    const int G = s_gt_base + (my & 0xffff);
-    const int E = s_eq_base + (my >> 16);
-    if (is_gt || (is_eq && E < krem)) {
-      const int pos = G + min(E, krem);
-      o[pos] = bt[i >> 6] * PS + (i & 63);
-    }
-    __syncthreads();
-    if (tid == 0) {
-      const int tot = hist[0];
-      s_gt_base += tot & 0xffff;
-      s_eq_base += tot >> 16;
-    }
+    g_base += block_g;
+    e_base += block_e;
     __syncthreads();
   }
 }
@@ -196,6 +282,8 @@ int launch_select(const float* scores, const int32_t* seq_lens, const int32_t* b
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = pdl ? 1 : 0;
+  cfg.dynamicSmemBytes = SEL_SMEM;
+  if (!ako::ensure_dynamic_smem<dsa_select_kernel>(SEL_SMEM)) return AKO4X_ELAUNCH;
   int mp = (int)max_pages;
   if (cudaLaunchKernelEx(&cfg, dsa_select_kernel, scores, seq_lens, block_table, out, mp) != cudaSuccess)
     return AKO4X_ELAUNCH;
