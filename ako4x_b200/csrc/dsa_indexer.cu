@@ -309,7 +309,7 @@ extern "C" int ako4x_dsa_index_scores(const void* q_index_fp8, const void* k_ind
   if (rows == 0 || max_pages == 0) return AKO4X_OK;
   if (!q_index_fp8 || !k_index_cache || !weights || !seq_lens || !block_table || !scores)
     return AKO4X_EINVAL;
-  if (((uintptr_t)q_index_fp8 | (uintptr_t)k_index_cache) & 15) return AKO4X_EINVAL;
+  if (((uintptr_t)q_index_fp8 | (uintptr_t)k_index_cache | (uintptr_t)weights) & 15) return AKO4X_EINVAL;
   return launch_scores(q_index_fp8, k_index_cache, weights, seq_lens, block_table, scores, rows,
                        max_pages, num_cache_pages, 0, (cudaStream_t)stream);
 }
@@ -333,7 +333,7 @@ extern "C" int ako4x_dsa_topk_indexer(const void* q_index_fp8, const void* k_ind
   if (rows == 0) return AKO4X_OK;
   if (!q_index_fp8 || !k_index_cache || !weights || !seq_lens || !block_table || !topk_indices)
     return AKO4X_EINVAL;
-  if (((uintptr_t)q_index_fp8 | (uintptr_t)k_index_cache) & 15) return AKO4X_EINVAL;
+  if (((uintptr_t)q_index_fp8 | (uintptr_t)k_index_cache | (uintptr_t)weights) & 15) return AKO4X_EINVAL;
   const size_t need = ako4x_dsa_topk_indexer_workspace_bytes(rows, max_pages);
   if (need > 0 && (!workspace || workspace_bytes < need)) return AKO4X_EWORKSPACE;
   cudaStream_t st = (cudaStream_t)stream;

@@ -59,6 +59,39 @@ def test_select_quantised_scores_many_ties(built_lib):
     assert torch.equal(out.cpu(), ref)
 
 
+def test_select_rows_longer_than_one_resident_chunk(built_lib):
+    """Rows above 32768 tokens are swept in chunks; ties straddle the chunk boundary."""
+    g = torch.Generator().manual_seed(11)
+    pages = 1100  # 70400 tokens
+    bt = torch.stack([torch.randperm(pages, generator=g) for _ in range(3)]).to(torch.int32)
+    sl = torch.tensor([70400, 32769, 50001], dtype=torch.int32)
+    scores = torch.randn((3, pages * 64), generator=g)
+    scores[1] = torch.randint(0, 40, (pages * 64,), generator=g).float()
+    scores[2, 32000:34000] = 9.0  # 2000 equal winners across the boundary, then a tie for the rest
+    ref = oracle.dsa_topk_select(scores, sl, bt)
+    out = dsa_indexer.topk_select(scores.cuda(), sl.cuda(), bt.cuda())
+    assert torch.equal(out.cpu(), ref)
+
+
+def test_scores_rows_with_their_own_pages(built_lib):
+    """Rows of different sequences (distinct page lists, ragged lengths) take the per-row MMA path."""
+    g = torch.Generator().manual_seed(5)
+    rows, pages_seq, npages = 7, 40, 400
+    a = W.make_dsa_indexer(rows, pages_seq * 64, shape_id=3, extra_pages=npages - pages_seq)
+    bt = torch.stack([torch.randperm(npages, generator=g)[:pages_seq] for _ in range(rows)]).to(torch.int32)
+    bt[1] = bt[0]                      # two rows share their pages, the others do not
+    a["block_table"] = bt.contiguous()
+    a["seq_lens"] = torch.tensor([2560, 2500, 2049, 64, 0, 2111, 2305], dtype=torch.int32)
+    d = _gpu(a)
+    s = dsa_indexer.index_scores(*[d[k] for k in KEYS]).cpu()
+    ref = oracle.dsa_index_scores(*[a[k] for k in KEYS])
+    for r in range(rows):
+        sl = int(a["seq_lens"][r])
+        assert torch.allclose(s[r, :sl], ref[r, :sl], rtol=1e-5, atol=1e-4)
+    (out,) = dsa_indexer.run(*[d[k] for k in KEYS])
+    _tier2(out.cpu(), a)
+
+
 def test_golden_regression(built_lib):
     g = load_golden("dsa_indexer_t3")
     d = _gpu(g["inputs"])
