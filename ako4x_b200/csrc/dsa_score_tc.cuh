@@ -5,7 +5,8 @@
 // the MMA (128 tokens = two 64-token cache pages), the 64 heads of up to FOUR query rows the N
 // dimension (N = 256), K = 128 e4m3 values (four tcgen05.mma K32 steps). With tokens on the TMEM
 // lanes, relu, the head weights and the head reduction are plain per-thread arithmetic on the
-// accumulator columns: no shuffles.
+// accumulator columns: no shuffles. That arithmetic (two CUDA-core instructions per accumulator
+// element) costs about as much as the MMA, so it gets sixteen warps.
 //
 // A unit of work is (group of 4 consecutive query rows, pair of logical pages). When the four rows
 // map that page pair to the same physical pages (consecutive tokens of one sequence, the prefill
@@ -13,14 +14,19 @@
 // the unit runs as four N = 64 sequences, one key tile each, into the four column blocks of the
 // same accumulator. A persistent CTA takes a contiguous range of units, so the 32 KB query tile of
 // a row group stays in shared memory while the CTA sweeps pages.
-//   warp 9      producer: lanes 0-3 read the block table of the group's four rows; lane 0 issues
-//               the TMA loads (query tile + head weights per group: 2 buffers; key tile: 6-stage
-//               ring, a page is a [64 x 128 B] box of a 3-D tensor map over the 8448-byte pages)
-//               and, per key tile, a slot of a 16-deep ring that carries the tile's 128 key scales
-//               and the unit's descriptor, so that no other warp touches the block table;
-//   warp 8      one thread: MMAs into one of two 256-column TMEM accumulators; commits free the
+//   warp 17     producer. Describe step: each lane reads the block table and sequence lengths of
+//               one of the next 32 units and writes one record per key tile into shared memory.
+//               Issue step: up to six lanes at a time take one record each and issue its copies
+//               (key tile: 6-stage ring, a page is a [64 x 128 B] box of a 3-D tensor map over the
+//               8448-byte pages; per unit a slot of a 16-deep ring that carries the key scales and
+//               the unit's descriptor, so that no other warp touches the block table; query tile
+//               + head weights per row group: 2 buffers). A record that starts a row group always
+//               opens an issue step, so every wait of a step depends only on earlier steps;
+//   warp 16     one thread: MMAs into one of two 256-column TMEM accumulators; commits free the
 //               key stage, the query buffer and publish the accumulator;
-//   warps 0-7   epilogue: thread (w, l) owns token 32*(w%4)+l and the two rows (w/4)*2, +1.
+//   warps 0-15  epilogue, two teams of eight warps: team k owns accumulator k and every second
+//               unit, so one team's barrier waits, TMEM loads and stores overlap the other's
+//               arithmetic. In a team thread (w, l) owns token 32*(w%4)+l and rows (w/4)*2, +1.
 // Every reader of TMA-written shared memory waits on the mbarrier the copy completes on. Every
 // wait is bounded; a timeout sets the status word and all roles unwind.
 
@@ -30,11 +36,18 @@ constexpr int TS_A_BYTES = 2 * PS * HD;         // 16 KB: two pages of e4m3 keys
 constexpr int TS_Q_BYTES = TS_N * HD;           // 32 KB: four rows of e4m3 queries
 constexpr int TS_W_BYTES = TS_N * 4;            // 1 KB: their head weights
 constexpr int TS_A_STAGES = 6;
-constexpr int TS_SLOTS = 16;                    // descriptor + key-scale ring
-constexpr int TS_SLOT_BYTES = 2 * PS * 4 + 64;  // 128 scales, then the descriptor
-constexpr int TS_SMEM = 2 * TS_Q_BYTES + TS_A_STAGES * TS_A_BYTES + 2 * TS_W_BYTES + TS_SLOTS * TS_SLOT_BYTES + 1024;
-constexpr int TS_EPI_THREADS = 256;
-constexpr int TS_THREADS = TS_EPI_THREADS + 64;
+constexpr int TS_SLOTS = 16;                    // per-unit ring: key scales + descriptor
+constexpr int TS_SCALE_BYTES = 2 * PS * 4;      // 128 key scales of one key tile
+constexpr int TS_SLOT_BYTES = TS_ROWS * TS_SCALE_BYTES + 64;
+constexpr int TS_DESCRIBE = 32;                 // units described per producer round (one per lane)
+constexpr int TS_RECS = TS_DESCRIBE * TS_ROWS + 2;
+constexpr int TS_REC_BYTES = 48;
+constexpr int TS_SMEM = 2 * TS_Q_BYTES + TS_A_STAGES * TS_A_BYTES + 2 * TS_W_BYTES + TS_SLOTS * TS_SLOT_BYTES +
+                        TS_RECS * TS_REC_BYTES + 1024;
+constexpr int TS_TEAM_WARPS = 8;
+constexpr int TS_EPI_WARPS = 2 * TS_TEAM_WARPS;
+constexpr int TS_MMA_WARP = TS_EPI_WARPS, TS_PRODUCER_WARP = TS_EPI_WARPS + 1;
+constexpr int TS_THREADS = (TS_EPI_WARPS + 2) * 32;
 
 __device__ int g_dsa_status = 0;  // 0 = ok; set when a bounded wait gave up
 
@@ -49,15 +62,24 @@ struct ScoreParams {
   int skip_short;
 };
 
-// Unit descriptor, written by the producer into the unit's first ring slot.
+// Unit descriptor, written by the producer into the unit's ring slot.
 struct ScoreDesc {
   int row0;           // first query row of the group
   int pp;             // page pair: logical pages 2*pp, 2*pp+1
   int flags;          // TS_F_*
+  int qc;             // ordinal of the row group inside this CTA (query buffer = qc & 1)
   int sl[TS_ROWS];    // row's sequence length, or -1 when the row takes nothing from this unit
-  int pad;
 };
 constexpr int TS_F_SHARED = 1, TS_F_NEWGROUP = 2, TS_F_END = 4;
+
+// One key tile to load: the producer's describe step writes these, its issue step reads them.
+struct ScoreRec {
+  int pa, pb;         // physical pages
+  int uo;             // ordinal of the unit inside this CTA (ring slot = uo % TS_SLOTS)
+  int sub;            // which key tile of the unit (0 for a shared one, else the row)
+  ScoreDesc d;
+};
+static_assert(sizeof(ScoreRec) == TS_REC_BYTES, "record size");
 
 __device__ __forceinline__ int phys_page(const ScoreParams& p, int r, int lp) {
   r = min(r, p.rows - 1);
@@ -95,17 +117,17 @@ dsa_score_tc_kernel(ScoreParams p, const __grid_constant__ CUtensorMap tm_q, con
     }
     for (int b = 0; b < 2; ++b) {
       ako::tc::mbar_init(ako::smem_u32(&s_q_full[b]), 1);
-      ako::tc::mbar_init(ako::smem_u32(&s_q_empty[b]), 1 + TS_EPI_THREADS / 32);
+      ako::tc::mbar_init(ako::smem_u32(&s_q_empty[b]), 1 + TS_EPI_WARPS);   // MMA commit + every epilogue warp
       ako::tc::mbar_init(ako::smem_u32(&s_acc_full[b]), 1);
-      ako::tc::mbar_init(ako::smem_u32(&s_acc_empty[b]), TS_EPI_THREADS / 32);
+      ako::tc::mbar_init(ako::smem_u32(&s_acc_empty[b]), TS_TEAM_WARPS);
     }
     for (int s = 0; s < TS_SLOTS; ++s) {
       ako::tc::mbar_init(ako::smem_u32(&s_slot_full[s]), 1);
-      ako::tc::mbar_init(ako::smem_u32(&s_slot_empty[s]), TS_EPI_THREADS / 32);
+      ako::tc::mbar_init(ako::smem_u32(&s_slot_empty[s]), 1 + TS_TEAM_WARPS);  // MMA thread + the owning team
     }
     ako::tc::mbar_init_fence();
   }
-  if (warp == 8) ako::tc::tmem_alloc(ako::smem_u32(&s_tmem_base), 512);
+  if (warp == TS_MMA_WARP) ako::tc::tmem_alloc(ako::smem_u32(&s_tmem_base), 512);
   ako::tc::fence_before_thread_sync();
   __syncthreads();
   ako::tc::fence_after_thread_sync();
@@ -117,121 +139,163 @@ dsa_score_tc_kernel(ScoreParams p, const __grid_constant__ CUtensorMap tm_q, con
   const int u_begin = (int)(total * blockIdx.x / gridDim.x);
   const int u_end = (int)(total * (blockIdx.x + 1) / gridDim.x);
 
-  if (warp == 9) {
+  if (warp == TS_PRODUCER_WARP) {
     // ================================ producer (whole warp) ====================================
     if (lane == 0) {
       ako::tc::tma_prefetch_desc(&tm_q);
       ako::tc::tma_prefetch_desc(&tm_k);
     }
-    int ac = 0, qc = 0, loaded_group = -1, issued_group = -1;
-    int my_sl = -1, my_lim = 0;  // lanes 0-3: this lane's row of the group
-    int ok = 1;
-    for (int unit = u_begin; ok && unit <= u_end; ++unit) {
-      const bool end = unit == u_end;
-      const int row0 = end ? 0 : (unit / pairs) * TS_ROWS;
-      const int pp = end ? 0 : unit % pairs;
-      int pa = 0, pb = 0;
-      bool shared = true;
-      if (!end) {
-        if (row0 != loaded_group) {
-          loaded_group = row0;
-          my_sl = -1;
-          my_lim = 0;
-          if (lane < TS_ROWS && row0 + lane < p.rows) {
-            const int sl = __ldg(p.seq_lens + row0 + lane);
-            if (sl > 0 && !(p.skip_short && sl <= TOPK)) {
-              my_sl = sl;
-              my_lim = min(sl, p.max_pages * PS);
-            }
+    ScoreRec* recs = reinterpret_cast<ScoreRec*>(slot_ptr + TS_SLOTS * TS_SLOT_BYTES);
+    const unsigned lt_mask = (1u << lane) - 1u;
+    int ac = 0, qc_base = 0, uo_base = 0;
+    bool done = false;
+    for (int ubase = u_begin; !done; ubase += TS_DESCRIBE) {
+      // ---- describe: lane l takes unit ubase + l. Two END records follow the last unit (one per
+      // epilogue team), in the first round that has two lanes to spare.
+      const int unit = ubase + lane;
+      int nsubs = 0, flags = 0, row0 = 0, pp = 0;
+      int pa[TS_ROWS], pb[TS_ROWS], sl[TS_ROWS];
+#pragma unroll
+      for (int i = 0; i < TS_ROWS; ++i) { pa[i] = 0; pb[i] = 0; sl[i] = -1; }
+      const int n_left = max(0, u_end - ubase);
+      const bool last_round = n_left <= TS_DESCRIBE - 2;
+      if (unit < u_end) {
+        row0 = (unit / pairs) * TS_ROWS;
+        pp = unit % pairs;
+        bool any = false, shared = true;
+        int fa = 0, fb = 0;
+#pragma unroll
+        for (int i = 0; i < TS_ROWS; ++i) {
+          const int r = row0 + i;
+          int s0 = (r < p.rows) ? __ldg(p.seq_lens + r) : 0;
+          if (s0 <= 0 || (p.skip_short && s0 <= TOPK)) s0 = 0;
+          const bool need = 2 * pp * PS < min(s0, p.max_pages * PS);
+          pa[i] = phys_page(p, r, 2 * pp);
+          pb[i] = phys_page(p, r, 2 * pp + 1);
+          if (need) {
+            sl[i] = s0;
+            if (!any) { fa = pa[i]; fb = pb[i]; }
+            else if (pa[i] != fa || pb[i] != fb) shared = false;
+            any = true;
           }
         }
-        const bool need = lane < TS_ROWS && 2 * pp * PS < my_lim;
-        if (lane < TS_ROWS) {
-          pa = phys_page(p, row0 + lane, 2 * pp);
-          pb = phys_page(p, row0 + lane, 2 * pp + 1);
-        }
-        const unsigned needmask = __ballot_sync(0xffffffffu, need);
-        if (needmask == 0u) continue;
-        const int first = __ffs(needmask) - 1;
-        const int fa = __shfl_sync(0xffffffffu, pa, first), fb = __shfl_sync(0xffffffffu, pb, first);
-        shared = __ballot_sync(0xffffffffu, need && (pa != fa || pb != fb)) == 0u;
-        if (shared) { pa = fa; pb = fb; }
-      }
-      const int sl_unit = (!end && lane < TS_ROWS && 2 * pp * PS < my_lim) ? my_sl : -1;
-      int sl4[TS_ROWS];
+        if (any) {
+          nsubs = shared ? 1 : TS_ROWS;
+          // a group's needed page pairs are a prefix, so its first unit in this CTA's range opens it
+          flags = (shared ? TS_F_SHARED : 0) | ((pp == 0 || unit == u_begin) ? TS_F_NEWGROUP : 0);
+          if (shared) {
 #pragma unroll
-      for (int i = 0; i < TS_ROWS; ++i) sl4[i] = __shfl_sync(0xffffffffu, sl_unit, i);
-      const bool newgroup = !end && row0 != issued_group;
-      if (newgroup) {
-        issued_group = row0;
-        if (lane == 0) {
-          const int qb = qc & 1;
-          if (ako::tc::mbar_wait(ako::smem_u32(&s_q_empty[qb]), (uint32_t)(((qc >> 1) & 1) ^ 1), &g_dsa_status, 1)) {
-            const uint32_t bar = ako::smem_u32(&s_q_full[qb]);
-            ako::tc::mbar_arrive_expect_tx(bar, TS_Q_BYTES + TS_W_BYTES);
-#pragma unroll
-            for (int i = 0; i < TS_ROWS; ++i) {
-              const int r = min(row0 + i, p.rows - 1);
-              ako::tc::tma_load_2d(q_base + qb * TS_Q_BYTES + i * NH * HD, &tm_q, 0, r * NH, bar);
-              ako::tc::bulk_load_1d(w_base + qb * TS_W_BYTES + i * NH * 4, p.weights + (int64_t)r * NH, NH * 4, bar);
-            }
-          } else {
-            ok = 0;
+            for (int i = 0; i < TS_ROWS; ++i) { pa[i] = fa; pb[i] = fb; }
           }
         }
-        ++qc;
+      } else if (last_round && (lane == n_left || lane == n_left + 1)) {
+        nsubs = 1;
+        flags = TS_F_END;
       }
-      const int subs = (end || shared) ? 1 : TS_ROWS;
-      for (int s = 0; s < subs; ++s, ++ac) {
-        const int pas = __shfl_sync(0xffffffffu, pa, shared ? 0 : s);
-        const int pbs = __shfl_sync(0xffffffffu, pb, shared ? 0 : s);
-        if (lane == 0 && ok) {
-          const int slot = ac % TS_SLOTS, stage = ac % TS_A_STAGES;
-          if (!ako::tc::mbar_wait(ako::smem_u32(&s_slot_empty[slot]), (uint32_t)(((ac / TS_SLOTS) & 1) ^ 1), &g_dsa_status, 2)) {
-            ok = 0;
-          } else {
-            unsigned char* sp = slot_ptr + slot * TS_SLOT_BYTES;
+      if (last_round) done = true;
+      int off = nsubs;  // exclusive prefix sum of nsubs over the warp
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int y = __shfl_up_sync(0xffffffffu, off, o);
+        if (lane >= o) off += y;
+      }
+      const int nrec = __shfl_sync(0xffffffffu, off, 31);
+      off -= nsubs;
+      const unsigned ngmask = __ballot_sync(0xffffffffu, (flags & TS_F_NEWGROUP) != 0);
+      // the group ordinal of a unit = groups opened before it or by it, minus one
+      const int qc = qc_base + __popc(ngmask & (lt_mask | (1u << lane))) - 1;
+      qc_base += __popc(ngmask);
+      const unsigned umask = __ballot_sync(0xffffffffu, nsubs > 0);
+      const int uo = uo_base + __popc(umask & lt_mask);
+      uo_base += __popc(umask);
+      for (int sidx = 0; sidx < nsubs; ++sidx) {
+        ScoreRec& rc = recs[off + sidx];
+        int a = pa[0], b = pb[0];
+#pragma unroll
+        for (int i = 1; i < TS_ROWS; ++i)
+          if (i == sidx) { a = pa[i]; b = pb[i]; }
+        rc.pa = a;
+        rc.pb = b;
+        rc.uo = uo;
+        rc.sub = sidx;
+        rc.d.row0 = row0;
+        rc.d.pp = pp;
+        rc.d.flags = (sidx == 0) ? flags : (flags & ~TS_F_NEWGROUP);
+        rc.d.qc = qc;
+#pragma unroll
+        for (int i = 0; i < TS_ROWS; ++i) rc.d.sl[i] = sl[i];
+      }
+      __syncwarp();
+
+      // ---- issue: up to TS_A_STAGES records per step, one per lane
+      int k = 0;
+      while (k < nrec) {
+        const bool have = lane < TS_A_STAGES && k + lane < nrec;
+        ScoreRec rc;
+        rc.d.flags = 0;
+        if (have) rc = recs[k + lane];
+        const unsigned cut = __ballot_sync(0xffffffffu, have && lane > 0 && (rc.d.flags & TS_F_NEWGROUP));
+        int nb = min(TS_A_STAGES, nrec - k);
+        if (cut) nb = min(nb, __ffs(cut) - 1);
+        bool ok = true;
+        if (lane < nb) {
+          const int a = ac + lane;
+          const int slot = rc.uo % TS_SLOTS, stage = a % TS_A_STAGES;
+          if (rc.d.flags & TS_F_NEWGROUP) {
+            const int qb = rc.d.qc & 1;
+            ok = ako::tc::mbar_wait(ako::smem_u32(&s_q_empty[qb]), (uint32_t)(((rc.d.qc >> 1) & 1) ^ 1), &g_dsa_status, 1);
+            if (ok) {
+              const uint32_t bar = ako::smem_u32(&s_q_full[qb]);
+              ako::tc::mbar_arrive_expect_tx(bar, TS_Q_BYTES + TS_W_BYTES);
+#pragma unroll
+              for (int i = 0; i < TS_ROWS; ++i) {
+                const int r = min(rc.d.row0 + i, p.rows - 1);
+                ako::tc::tma_load_2d(q_base + qb * TS_Q_BYTES + i * NH * HD, &tm_q, 0, r * NH, bar);
+                ako::tc::bulk_load_1d(w_base + qb * TS_W_BYTES + i * NH * 4, p.weights + (int64_t)r * NH, NH * 4, bar);
+              }
+            }
+          }
+          // every key tile of the unit waits for the slot: the tiles of one unit may be issued together
+          ok = ok && ako::tc::mbar_wait(ako::smem_u32(&s_slot_empty[slot]), (uint32_t)(((rc.uo / TS_SLOTS) & 1) ^ 1), &g_dsa_status, 2);
+          if (ok) {
             const uint32_t sbar = ako::smem_u32(&s_slot_full[slot]);
-            if (s == 0) {
-              ScoreDesc* d = reinterpret_cast<ScoreDesc*>(sp + 2 * PS * 4);
-              d->row0 = row0;
-              d->pp = pp;
-              d->flags = (shared ? TS_F_SHARED : 0) | (newgroup ? TS_F_NEWGROUP : 0) | (end ? TS_F_END : 0);
-#pragma unroll
-              for (int i = 0; i < TS_ROWS; ++i) d->sl[i] = sl4[i];
+            if (rc.sub == 0) {
+              *reinterpret_cast<ScoreDesc*>(slot_ptr + slot * TS_SLOT_BYTES + TS_ROWS * TS_SCALE_BYTES) = rc.d;
+              if (rc.d.flags & TS_F_END) ako::tc::mbar_arrive(sbar);
+              else ako::tc::mbar_arrive_expect_tx(sbar, ((rc.d.flags & TS_F_SHARED) ? 1 : TS_ROWS) * TS_SCALE_BYTES);
             }
-            if (end) {
-              ako::tc::mbar_arrive(sbar);
-            } else {
-              ako::tc::mbar_arrive_expect_tx(sbar, 2 * PS * 4);
-              const uint32_t sdst = slot_base + slot * TS_SLOT_BYTES;
-              ako::tc::bulk_load_1d(sdst, p.cache + (int64_t)pas * PAGE_BYTES + PS * HD, PS * 4, sbar);
-              ako::tc::bulk_load_1d(sdst + PS * 4, p.cache + (int64_t)pbs * PAGE_BYTES + PS * HD, PS * 4, sbar);
-              if (!ako::tc::mbar_wait(ako::smem_u32(&s_a_empty[stage]), (uint32_t)(((ac / TS_A_STAGES) & 1) ^ 1), &g_dsa_status, 3)) {
-                ok = 0;
-              } else {
+            if (!(rc.d.flags & TS_F_END)) {
+              const uint32_t sdst = slot_base + slot * TS_SLOT_BYTES + rc.sub * TS_SCALE_BYTES;
+              ako::tc::bulk_load_1d(sdst, p.cache + (int64_t)rc.pa * PAGE_BYTES + PS * HD, PS * 4, sbar);
+              ako::tc::bulk_load_1d(sdst + PS * 4, p.cache + (int64_t)rc.pb * PAGE_BYTES + PS * HD, PS * 4, sbar);
+              ok = ako::tc::mbar_wait(ako::smem_u32(&s_a_empty[stage]), (uint32_t)(((a / TS_A_STAGES) & 1) ^ 1), &g_dsa_status, 3);
+              if (ok) {
                 const uint32_t bar = ako::smem_u32(&s_a_full[stage]);
                 const uint32_t dst = a_base + stage * TS_A_BYTES;
                 ako::tc::mbar_arrive_expect_tx(bar, TS_A_BYTES);
-                ako::tc::tma_load_3d(dst, &tm_k, 0, 0, pas, bar);
-                ako::tc::tma_load_3d(dst + PS * HD, &tm_k, 0, 0, pbs, bar);
+                ako::tc::tma_load_3d(dst, &tm_k, 0, 0, rc.pa, bar);
+                ako::tc::tma_load_3d(dst + PS * HD, &tm_k, 0, 0, rc.pb, bar);
               }
             }
           }
         }
+        ac += nb;
+        k += nb;
+        if (__ballot_sync(0xffffffffu, !ok) != 0u) { done = true; break; }
       }
-      ok = __shfl_sync(0xffffffffu, ok, 0);
+      __syncwarp();  // the records are rewritten by the next describe step
     }
-  } else if (warp == 8) {
+  } else if (warp == TS_MMA_WARP) {
     // ================================ MMA issuer ===============================================
     if (lane == 0) {
       constexpr uint32_t IDESC_SHARED = ako::tc::idesc_e4m3_f32(128, TS_N);
       constexpr uint32_t IDESC_ROW = ako::tc::idesc_e4m3_f32(128, NH);
-      int ac = 0, qc = 0, uc = 0;
-      while (true) {
-        const int slot = ac % TS_SLOTS;
-        if (!ako::tc::mbar_wait(ako::smem_u32(&s_slot_full[slot]), (uint32_t)((ac / TS_SLOTS) & 1), &g_dsa_status, 4)) break;
-        const int flags = reinterpret_cast<const volatile ScoreDesc*>(slot_ptr + slot * TS_SLOT_BYTES + 2 * PS * 4)->flags;
+      int ac = 0, qc = 0;
+      for (int uo = 0;; ++uo) {
+        const int slot = uo % TS_SLOTS;
+        if (!ako::tc::mbar_wait(ako::smem_u32(&s_slot_full[slot]), (uint32_t)((uo / TS_SLOTS) & 1), &g_dsa_status, 4)) break;
+        const int flags = reinterpret_cast<const volatile ScoreDesc*>(slot_ptr + slot * TS_SLOT_BYTES + TS_ROWS * TS_SCALE_BYTES)->flags;
+        ako::tc::mbar_arrive(ako::smem_u32(&s_slot_empty[slot]));
         if (flags & TS_F_END) break;
         if (flags & TS_F_NEWGROUP) {
           if (qc > 0) ako::tc::mma_commit(ako::smem_u32(&s_q_empty[(qc - 1) & 1]));  // previous tile is done with
@@ -240,8 +304,8 @@ dsa_score_tc_kernel(ScoreParams p, const __grid_constant__ CUtensorMap tm_q, con
         }
         const bool shared = flags & TS_F_SHARED;
         const uint32_t qs = q_base + ((qc - 1) & 1) * TS_Q_BYTES;
-        const int buf = uc & 1;
-        if (!ako::tc::mbar_wait(ako::smem_u32(&s_acc_empty[buf]), (uint32_t)(((uc >> 1) & 1) ^ 1), &g_dsa_status, 6)) break;
+        const int buf = uo & 1;
+        if (!ako::tc::mbar_wait(ako::smem_u32(&s_acc_empty[buf]), (uint32_t)(((uo >> 1) & 1) ^ 1), &g_dsa_status, 6)) break;
         const int subs = shared ? 1 : TS_ROWS;
         bool ok = true;
         for (int s = 0; s < subs; ++s, ++ac) {
@@ -259,84 +323,71 @@ dsa_score_tc_kernel(ScoreParams p, const __grid_constant__ CUtensorMap tm_q, con
         }
         if (!ok) break;
         ako::tc::mma_commit(ako::smem_u32(&s_acc_full[buf]));
-        ++uc;
       }
     }
   } else {
-    // ================================ epilogue ====================================================
+    // ================================ epilogue (two teams) ========================================
+    const int team = warp / TS_TEAM_WARPS;
     const int q = warp & 3;             // TMEM lane quarter
-    const int rh = warp >> 2;           // which two rows of the group
+    const int rh = (warp >> 2) & 1;     // which two rows of the group
     const int t = 32 * q + lane;        // token inside the unit
-    int ac = 0, qc = 0, uc = 0;
-    while (true) {
-      const int slot0 = ac % TS_SLOTS;
-      if (!ako::tc::mbar_wait(ako::smem_u32(&s_slot_full[slot0]), (uint32_t)((ac / TS_SLOTS) & 1), &g_dsa_status, 8)) break;
-      const ScoreDesc d = *reinterpret_cast<const ScoreDesc*>(slot_ptr + slot0 * TS_SLOT_BYTES + 2 * PS * 4);
+    const uint32_t tmem_team = tmem_base + ((uint32_t)(32 * q) << 16) + team * TS_N + rh * 2 * NH;
+    int q_rel = 0;                      // query buffers released so far (group ordinals below this)
+    int q_cur = -1;
+    const float* wrow = nullptr;
+    float* orow[2] = {nullptr, nullptr};
+    for (int n = 0;; ++n) {
+      const int uo = 2 * n + team;
+      const int slot = uo % TS_SLOTS;
+      const unsigned char* sp = slot_ptr + slot * TS_SLOT_BYTES;
+      if (!ako::tc::mbar_wait(ako::smem_u32(&s_slot_full[slot]), (uint32_t)((uo / TS_SLOTS) & 1), &g_dsa_status, 8)) break;
+      const ScoreDesc d = *reinterpret_cast<const ScoreDesc*>(sp + TS_ROWS * TS_SCALE_BYTES);
       if (d.flags & TS_F_END) break;
-      const bool shared = d.flags & TS_F_SHARED;
-      const int subs = shared ? 1 : TS_ROWS;
-      if (d.flags & TS_F_NEWGROUP) {
-        if (qc > 0) {  // this warp has read the previous group's weights for the last time
-          __syncwarp();
-          if (lane == 0) ako::tc::mbar_arrive(ako::smem_u32(&s_q_empty[(qc - 1) & 1]));
-        }
-        if (!ako::tc::mbar_wait(ako::smem_u32(&s_q_full[qc & 1]), (uint32_t)((qc >> 1) & 1), &g_dsa_status, 9)) break;
-        ++qc;
+      if (d.qc != q_cur) {
+        // Groups below d.qc are finished for this warp (it may never have seen some of them).
+        __syncwarp();
+        if (lane == 0)
+          for (; q_rel < d.qc; ++q_rel) ako::tc::mbar_arrive(ako::smem_u32(&s_q_empty[q_rel & 1]));
+        q_rel = d.qc;
+        q_cur = d.qc;
+        if (!ako::tc::mbar_wait(ako::smem_u32(&s_q_full[q_cur & 1]), (uint32_t)((q_cur >> 1) & 1), &g_dsa_status, 9)) break;
+        wrow = reinterpret_cast<const float*>(w_ptr + (q_cur & 1) * TS_W_BYTES) + rh * 2 * NH;
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+          orow[i] = p.scores + (int64_t)min(d.row0 + rh * 2 + i, p.rows - 1) * p.max_pages * PS;
       }
-      const float* wrow = reinterpret_cast<const float*>(w_ptr + ((qc - 1) & 1) * TS_W_BYTES) + rh * 2 * NH;
       // key scales of this thread's token for its two rows
+      const bool shared = d.flags & TS_F_SHARED;
       float ksc[2];
-      bool ok = true;
 #pragma unroll
-      for (int i = 0; i < 2; ++i) {
-        const int a2 = ac + (shared ? 0 : rh * 2 + i);
-        const int sl2 = a2 % TS_SLOTS;
-        if (!shared && !ako::tc::mbar_wait(ako::smem_u32(&s_slot_full[sl2]), (uint32_t)((a2 / TS_SLOTS) & 1), &g_dsa_status, 10)) { ok = false; break; }
-        ksc[i] = reinterpret_cast<const float*>(slot_ptr + sl2 * TS_SLOT_BYTES)[t];
-      }
-      if (!ok) break;
-      if (!shared) {  // the other rows' slots are released by every warp as well: wait for them first
-#pragma unroll
-        for (int s = 0; s < TS_ROWS; ++s) {
-          const int a2 = ac + s;
-          if (!ako::tc::mbar_wait(ako::smem_u32(&s_slot_full[a2 % TS_SLOTS]), (uint32_t)((a2 / TS_SLOTS) & 1), &g_dsa_status, 11)) { ok = false; break; }
-        }
-        if (!ok) break;
-      }
+      for (int i = 0; i < 2; ++i)
+        ksc[i] = reinterpret_cast<const float*>(sp + (shared ? 0 : rh * 2 + i) * TS_SCALE_BYTES)[t];
       __syncwarp();
-      if (lane == 0) {
-        for (int s = 0; s < subs; ++s) ako::tc::mbar_arrive(ako::smem_u32(&s_slot_empty[(ac + s) % TS_SLOTS]));
-      }
-      ac += subs;
+      if (lane == 0) ako::tc::mbar_arrive(ako::smem_u32(&s_slot_empty[slot]));
 
-      const int buf = uc & 1;
-      if (!ako::tc::mbar_wait(ako::smem_u32(&s_acc_full[buf]), (uint32_t)((uc >> 1) & 1), &g_dsa_status, 12)) break;
+      if (!ako::tc::mbar_wait(ako::smem_u32(&s_acc_full[team]), (uint32_t)(n & 1), &g_dsa_status, 10)) break;
       ako::tc::fence_after_thread_sync();
-      const uint32_t taddr = tmem_base + ((uint32_t)(32 * q) << 16) + buf * TS_N + rh * 2 * NH;
-      float sum[2] = {0.f, 0.f};
+      // 32 accumulator columns per step: row (c>>1) of this thread's pair, heads 32*(c&1)...
+      float part[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {  // 32 columns each: row (c>>1) of this thread's pair, heads 32*(c&1)..
+      for (int c = 0; c < 4; ++c) {
         float v[32];
-        ako::tc::tmem_ld32(taddr + 32 * c, v);
-        const float4* wp = reinterpret_cast<const float4*>(wrow + 32 * c);
-        float4 w4[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) w4[j] = wp[j];
-        ako::tc::tmem_ld_wait();
+        ako::tc::tmem_ld32(tmem_team + 32 * c, v);
+        ako::tc::tmem_ld_wait_regs(v);
         if (c == 3) {  // the accumulator is in registers: release it
           ako::tc::fence_before_thread_sync();
           __syncwarp();
-          if (lane == 0) ako::tc::mbar_arrive(ako::smem_u32(&s_acc_empty[buf]));
+          if (lane == 0) ako::tc::mbar_arrive(ako::smem_u32(&s_acc_empty[team]));
         }
-        float s = sum[c >> 1];
+        const float4* wp = reinterpret_cast<const float4*>(wrow + 32 * c);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          s = fmaf(fmaxf(v[4 * j + 0], 0.f), w4[j].x, s);
-          s = fmaf(fmaxf(v[4 * j + 1], 0.f), w4[j].y, s);
-          s = fmaf(fmaxf(v[4 * j + 2], 0.f), w4[j].z, s);
-          s = fmaf(fmaxf(v[4 * j + 3], 0.f), w4[j].w, s);
+          const float4 w4 = wp[j];
+          part[c >> 1][0] = fmaf(fmaxf(v[4 * j + 0], 0.f), w4.x, part[c >> 1][0]);
+          part[c >> 1][1] = fmaf(fmaxf(v[4 * j + 1], 0.f), w4.y, part[c >> 1][1]);
+          part[c >> 1][2] = fmaf(fmaxf(v[4 * j + 2], 0.f), w4.z, part[c >> 1][2]);
+          part[c >> 1][3] = fmaf(fmaxf(v[4 * j + 3], 0.f), w4.w, part[c >> 1][3]);
         }
-        sum[c >> 1] = s;
       }
       const int tok = d.pp * 2 * PS + t;
       if (tok < p.max_pages * PS) {
@@ -344,16 +395,16 @@ dsa_score_tc_kernel(ScoreParams p, const __grid_constant__ CUtensorMap tm_q, con
         for (int i = 0; i < 2; ++i) {
           const int sl = d.sl[rh * 2 + i];
           if (sl < 0) continue;
-          p.scores[(int64_t)(d.row0 + rh * 2 + i) * p.max_pages * PS + tok] = (tok < sl) ? sum[i] * ksc[i] : -INFINITY;
+          const float sum = (part[i][0] + part[i][1]) + (part[i][2] + part[i][3]);
+          orow[i][tok] = (tok < sl) ? sum * ksc[i] : -INFINITY;
         }
       }
-      ++uc;
     }
   }
 
   ako::tc::fence_before_thread_sync();
   __syncthreads();
-  if (warp == 8) {
+  if (warp == TS_MMA_WARP) {
     ako::tc::fence_after_thread_sync();
     ako::tc::tmem_dealloc(tmem_base, 512);
   }
