@@ -14,7 +14,7 @@
 // the unit runs as four N = 64 sequences, one key tile each, into the four column blocks of the
 // same accumulator. A persistent CTA takes a contiguous range of units, so the 32 KB query tile of
 // a row group stays in shared memory while the CTA sweeps pages.
-//   warp 17     producer. Describe step: each lane reads the block table and sequence lengths of
+//   warp 18     producer. Describe step: each lane reads the block table and sequence lengths of
 //               one of the next 32 units and writes one record per key tile into shared memory.
 //               Issue step: up to six lanes at a time take one record each and issue its copies
 //               (key tile: 6-stage ring, a page is a [64 x 128 B] box of a 3-D tensor map over the
@@ -22,8 +22,11 @@
 //               the unit's descriptor, so that no other warp touches the block table; query tile
 //               + head weights per row group: 2 buffers). A record that starts a row group always
 //               opens an issue step, so every wait of a step depends only on earlier steps;
-//   warp 16     one thread: MMAs into one of two 256-column TMEM accumulators; commits free the
-//               key stage, the query buffer and publish the accumulator;
+//   warps 16,17 MMA issuers, one thread each: issuer k owns TMEM accumulator k (256 columns) and
+//               every second unit. An issuer is one dependent instruction stream in which every
+//               barrier test, descriptor read, MMA and commit costs 50-100 cycles, about twice the
+//               tensor pipe's time for a unit; two of them keep the pipe fed. Commits free the key
+//               stage, the query buffer and publish the accumulator;
 //   warps 0-15  epilogue, two teams of eight warps: team k owns accumulator k and every second
 //               unit, so one team's barrier waits, TMEM loads and stores overlap the other's
 //               arithmetic. In a team thread (w, l) owns token 32*(w%4)+l and rows (w/4)*2, +1.
@@ -41,13 +44,13 @@ constexpr int TS_SCALE_BYTES = 2 * PS * 4;      // 128 key scales of one key til
 constexpr int TS_SLOT_BYTES = TS_ROWS * TS_SCALE_BYTES + 64;
 constexpr int TS_DESCRIBE = 32;                 // units described per producer round (one per lane)
 constexpr int TS_RECS = TS_DESCRIBE * TS_ROWS + 2;
-constexpr int TS_REC_BYTES = 48;
+constexpr int TS_REC_BYTES = 64;
 constexpr int TS_SMEM = 2 * TS_Q_BYTES + TS_A_STAGES * TS_A_BYTES + 2 * TS_W_BYTES + TS_SLOTS * TS_SLOT_BYTES +
                         TS_RECS * TS_REC_BYTES + 1024;
 constexpr int TS_TEAM_WARPS = 8;
 constexpr int TS_EPI_WARPS = 2 * TS_TEAM_WARPS;
-constexpr int TS_MMA_WARP = TS_EPI_WARPS, TS_PRODUCER_WARP = TS_EPI_WARPS + 1;
-constexpr int TS_THREADS = (TS_EPI_WARPS + 2) * 32;
+constexpr int TS_MMA_WARP = TS_EPI_WARPS, TS_PRODUCER_WARP = TS_EPI_WARPS + 2;  // issuers: warps 16, 17
+constexpr int TS_THREADS = (TS_EPI_WARPS + 3) * 32;
 
 __device__ int g_dsa_status = 0;  // 0 = ok; set when a bounded wait gave up
 
@@ -69,6 +72,8 @@ struct ScoreDesc {
   int flags;          // TS_F_*
   int qc;             // ordinal of the row group inside this CTA (query buffer = qc & 1)
   int sl[TS_ROWS];    // row's sequence length, or -1 when the row takes nothing from this unit
+  int ac0;            // ordinal of the unit's first key tile inside this CTA (key stage = ordinal % stages)
+  int pad[3];
 };
 constexpr int TS_F_SHARED = 1, TS_F_NEWGROUP = 2, TS_F_END = 4;
 
@@ -117,13 +122,13 @@ dsa_score_tc_kernel(ScoreParams p, const __grid_constant__ CUtensorMap tm_q, con
     }
     for (int b = 0; b < 2; ++b) {
       ako::tc::mbar_init(ako::smem_u32(&s_q_full[b]), 1);
-      ako::tc::mbar_init(ako::smem_u32(&s_q_empty[b]), 1 + TS_EPI_WARPS);   // MMA commit + every epilogue warp
+      ako::tc::mbar_init(ako::smem_u32(&s_q_empty[b]), 2 + TS_EPI_WARPS);   // both issuers + every epilogue warp
       ako::tc::mbar_init(ako::smem_u32(&s_acc_full[b]), 1);
       ako::tc::mbar_init(ako::smem_u32(&s_acc_empty[b]), TS_TEAM_WARPS);
     }
     for (int s = 0; s < TS_SLOTS; ++s) {
       ako::tc::mbar_init(ako::smem_u32(&s_slot_full[s]), 1);
-      ako::tc::mbar_init(ako::smem_u32(&s_slot_empty[s]), 1 + TS_TEAM_WARPS);  // MMA thread + the owning team
+      ako::tc::mbar_init(ako::smem_u32(&s_slot_empty[s]), 1 + TS_TEAM_WARPS);  // the owning issuer + the owning team
     }
     ako::tc::mbar_init_fence();
   }
@@ -222,6 +227,7 @@ dsa_score_tc_kernel(ScoreParams p, const __grid_constant__ CUtensorMap tm_q, con
         rc.d.pp = pp;
         rc.d.flags = (sidx == 0) ? flags : (flags & ~TS_F_NEWGROUP);
         rc.d.qc = qc;
+        rc.d.ac0 = ac + off;  // every record of earlier rounds has been issued: ac counts them
 #pragma unroll
         for (int i = 0; i < TS_ROWS; ++i) rc.d.sl[i] = sl[i];
       }
@@ -285,44 +291,76 @@ dsa_score_tc_kernel(ScoreParams p, const __grid_constant__ CUtensorMap tm_q, con
       }
       __syncwarp();  // the records are rewritten by the next describe step
     }
-  } else if (warp == TS_MMA_WARP) {
-    // ================================ MMA issuer ===============================================
+  } else if (warp == TS_MMA_WARP || warp == TS_MMA_WARP + 1) {
+    // ================================ MMA issuers ==============================================
+    // The barrier waits and the descriptor read for the issuer's NEXT key tile are done between
+    // the second and third MMA of the current one.
     if (lane == 0) {
       constexpr uint32_t IDESC_SHARED = ako::tc::idesc_e4m3_f32(128, TS_N);
       constexpr uint32_t IDESC_ROW = ako::tc::idesc_e4m3_f32(128, NH);
-      int ac = 0, qc = 0;
-      for (int uo = 0;; ++uo) {
-        const int slot = uo % TS_SLOTS;
-        if (!ako::tc::mbar_wait(ako::smem_u32(&s_slot_full[slot]), (uint32_t)((uo / TS_SLOTS) & 1), &g_dsa_status, 4)) break;
-        const int flags = reinterpret_cast<const volatile ScoreDesc*>(slot_ptr + slot * TS_SLOT_BYTES + TS_ROWS * TS_SCALE_BYTES)->flags;
-        ako::tc::mbar_arrive(ako::smem_u32(&s_slot_empty[slot]));
-        if (flags & TS_F_END) break;
-        if (flags & TS_F_NEWGROUP) {
-          if (qc > 0) ako::tc::mma_commit(ako::smem_u32(&s_q_empty[(qc - 1) & 1]));  // previous tile is done with
-          if (!ako::tc::mbar_wait(ako::smem_u32(&s_q_full[qc & 1]), (uint32_t)((qc >> 1) & 1), &g_dsa_status, 5)) break;
-          ++qc;
+      struct Tile { uint32_t a_lo, b_lo, d, idesc; int stage, acc_wait; bool last; };  // descriptor low words
+      const int me = warp - TS_MMA_WARP;    // accumulator, and parity of the units taken
+      const uint32_t a_lo0 = ako::tc::smem_desc_lo(a_base), q_lo0 = ako::tc::smem_desc_lo(q_base);
+      const uint32_t acc = tmem_base + me * TS_N;
+      int n = 0;                            // units taken so far
+      int ac = 0, subs = 0, sub = 0;        // current unit: next key tile ordinal, tiles, tiles issued
+      bool shared = true;
+      uint32_t q_lo = q_lo0;
+      int q_cur = -1, q_rel = 0, q_rel_to = 0;  // group in use; groups released; groups to release
+      int acc_wait = 1;
+      // 1: tile ready, 0: END record, -1: a wait gave up
+      auto prepare = [&](Tile& t) -> int {
+        if (sub == subs) {  // next unit
+          const int uo = 2 * n + me;
+          const int slot = uo % TS_SLOTS;
+          if (!ako::tc::mbar_wait(ako::smem_u32(&s_slot_full[slot]), (uint32_t)((uo / TS_SLOTS) & 1), &g_dsa_status, 4)) return -1;
+          const volatile ScoreDesc* dp = reinterpret_cast<const volatile ScoreDesc*>(slot_ptr + slot * TS_SLOT_BYTES + TS_ROWS * TS_SCALE_BYTES);
+          const int flags = dp->flags, qc = dp->qc;
+          ac = dp->ac0;
+          ako::tc::mbar_arrive(ako::smem_u32(&s_slot_empty[slot]));
+          if (flags & TS_F_END) return 0;
+          if (qc != q_cur) {
+            q_rel_to = qc;  // handed back after the tile in flight, the last one that may read them
+            q_cur = qc;
+            if (!ako::tc::mbar_wait(ako::smem_u32(&s_q_full[qc & 1]), (uint32_t)((qc >> 1) & 1), &g_dsa_status, 5)) return -1;
+            q_lo = q_lo0 + (qc & 1) * (TS_Q_BYTES >> 4);
+          }
+          shared = flags & TS_F_SHARED;
+          subs = shared ? 1 : TS_ROWS;
+          sub = 0;
+          acc_wait = (n & 1) ^ 1;  // parity to wait for before the unit's first MMA
+          ++n;
         }
-        const bool shared = flags & TS_F_SHARED;
-        const uint32_t qs = q_base + ((qc - 1) & 1) * TS_Q_BYTES;
-        const int buf = uo & 1;
-        if (!ako::tc::mbar_wait(ako::smem_u32(&s_acc_empty[buf]), (uint32_t)(((uo >> 1) & 1) ^ 1), &g_dsa_status, 6)) break;
-        const int subs = shared ? 1 : TS_ROWS;
-        bool ok = true;
-        for (int s = 0; s < subs; ++s, ++ac) {
-          const int stage = ac % TS_A_STAGES;
-          if (!ako::tc::mbar_wait(ako::smem_u32(&s_a_full[stage]), (uint32_t)((ac / TS_A_STAGES) & 1), &g_dsa_status, 7)) { ok = false; break; }
-          ako::tc::fence_after_thread_sync();
-          const uint32_t sa = a_base + stage * TS_A_BYTES;
-          const uint32_t sb = qs + (shared ? 0 : s * NH * HD);
-          const uint32_t d = tmem_base + buf * TS_N + (shared ? 0 : s * NH);
-#pragma unroll
-          for (int ks = 0; ks < 4; ++ks)
-            ako::tc::mma_f8(d, ako::tc::smem_desc_k_sw128(sa + ks * 32), ako::tc::smem_desc_k_sw128(sb + ks * 32),
-                            shared ? IDESC_SHARED : IDESC_ROW, ks > 0 ? 1u : 0u);
-          ako::tc::mma_commit(ako::smem_u32(&s_a_empty[stage]));
-        }
-        if (!ok) break;
-        ako::tc::mma_commit(ako::smem_u32(&s_acc_full[buf]));
+        const int stage = ac % TS_A_STAGES;
+        if (!ako::tc::mbar_wait(ako::smem_u32(&s_a_full[stage]), (uint32_t)((ac / TS_A_STAGES) & 1), &g_dsa_status, 7)) return -1;
+        ako::tc::fence_after_thread_sync();
+        t.a_lo = a_lo0 + stage * (TS_A_BYTES >> 4);
+        t.b_lo = q_lo + (shared ? 0 : sub * ((NH * HD) >> 4));
+        t.d = acc + (shared ? 0 : sub * NH);
+        t.idesc = shared ? IDESC_SHARED : IDESC_ROW;
+        t.stage = stage;
+        t.acc_wait = (sub == 0) ? acc_wait : -1;
+        t.last = sub == subs - 1;
+        ++sub;
+        ++ac;
+        return 1;
+      };
+      Tile cur, nxt;
+      int r = prepare(cur);
+      while (r == 1) {
+        // This issuer's units share one accumulator: the team must have read the previous result.
+        if (cur.acc_wait >= 0 &&
+            !ako::tc::mbar_wait(ako::smem_u32(&s_acc_empty[me]), (uint32_t)cur.acc_wait, &g_dsa_status, 6)) break;
+        ako::tc::mma_f8_lohi<false>(cur.d, cur.a_lo, cur.b_lo, cur.idesc);  // K = 32 slices: +32 B = +2
+        ako::tc::mma_f8_lohi<true>(cur.d, cur.a_lo + 2, cur.b_lo + 2, cur.idesc);
+        r = prepare(nxt);
+        ako::tc::mma_f8_lohi<true>(cur.d, cur.a_lo + 4, cur.b_lo + 4, cur.idesc);
+        ako::tc::mma_f8_lohi<true>(cur.d, cur.a_lo + 6, cur.b_lo + 6, cur.idesc);
+        ako::tc::mma_commit(ako::smem_u32(&s_a_empty[cur.stage]));
+        if (cur.last) ako::tc::mma_commit(ako::smem_u32(&s_acc_full[me]));
+        for (; q_rel < q_rel_to; ++q_rel)  // groups this issuer is past (it may never have seen some)
+          ako::tc::mma_commit(ako::smem_u32(&s_q_empty[q_rel & 1]));
+        cur = nxt;
       }
     }
   } else {

@@ -30,6 +30,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// The same test, letting the hardware keep the thread suspended for up to `ns` nanoseconds while
+// the phase is incomplete: a waiting warp then leaves its scheduler's issue slots to the others.
+__device__ __forceinline__ bool mbar_try_wait_suspend(uint32_t bar, uint32_t parity, uint32_t ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n.reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+      "selp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(ns)
+      : "memory");
+  return ok != 0;
+}
 // Waits for the phase with the given parity. Returns false when `*err` is already set or when the
 // cycle budget runs out (then `*err` is set to `code`); the caller must unwind, not retry.
 constexpr long long kWaitBudgetCycles = 400000000LL;  // ~0.2 s at 1.9 GHz
@@ -38,8 +51,8 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* er
   const long long t0 = clock64();
   uint32_t spins = 0;
   while (true) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((++spins & 255u) == 0u) {
+    if (mbar_try_wait_suspend(bar, parity, 2000u)) return true;
+    if ((++spins & 15u) == 0u) {
       if (*reinterpret_cast<volatile int*>(err) != 0) return false;
       if (clock64() - t0 > kWaitBudgetCycles) {
         atomicCAS(err, 0, code);
@@ -130,6 +143,26 @@ __device__ __forceinline__ void mma_f8(uint32_t d_tmem, uint64_t adesc, uint64_t
       "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// The same MMA with the two descriptors given as halves: both K-major SW128 tiles share the high
+// word, and the low word (start address >> 4, LBO) advances by plain 32-bit adds -- 2 per K = 32
+// slice, bytes >> 4 per tile. The issuing thread is a single dependent instruction stream, so every
+// instruction saved between two MMAs shortens the gap in which the tensor pipe may drain.
+__device__ __forceinline__ uint32_t smem_desc_lo(uint32_t saddr) {
+  return ((saddr >> 4) & 0x3FFFu) | (1u << 16);
+}
+constexpr uint32_t kSmemDescHiSw128 = (1024u >> 4) | (1u << 14) | (2u << 29);
+template <bool ACCUMULATE>
+__device__ __forceinline__ void mma_f8_lohi(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc) {
+  asm volatile(
+      "{\n.reg .b64 da, db;\n.reg .pred p;\n"
+      "mov.b64 da, {%1, %4};\n"
+      "mov.b64 db, {%2, %4};\n"
+      "setp.ne.b32 p, %5, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], da, db, %3, p;\n}\n" ::"r"(d_tmem),
+      "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(kSmemDescHiSw128), "n"(ACCUMULATE ? 1 : 0)
+      : "memory");
+}
+
 // Arrives on `bar` once every tcgen05.mma issued so far by this thread has completed.
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar)

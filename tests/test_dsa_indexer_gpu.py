@@ -15,6 +15,15 @@ def _gpu(a):
     return W.to_device(a, "cuda")
 
 
+@pytest.fixture(autouse=True)
+def _status_clean(built_lib):
+    """No bounded wait of the score kernel may have given up, before or after a test."""
+    from ako4x_b200 import _cabi
+    assert _cabi.lib().ako4x_dsa_indexer_device_status() == 0
+    yield
+    assert _cabi.lib().ako4x_dsa_indexer_device_status() == 0
+
+
 def test_scores_match_oracle(built_lib):
     a = W.make_dsa_indexer(5, 2048 + 700, shape_id=1)
     d = _gpu(a)
