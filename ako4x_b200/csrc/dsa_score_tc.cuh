@@ -22,14 +22,15 @@
 //               the unit's descriptor, so that no other warp touches the block table; query tile
 //               + head weights per row group: 2 buffers). A record that starts a row group always
 //               opens an issue step, so every wait of a step depends only on earlier steps;
-//   warps 16,17 MMA issuers, one thread each: issuer k owns TMEM accumulator k (256 columns) and
-//               every second unit. An issuer is one dependent instruction stream in which every
-//               barrier test, descriptor read, MMA and commit costs 50-100 cycles, about twice the
-//               tensor pipe's time for a unit; two of them keep the pipe fed. Commits free the key
-//               stage, the query buffer and publish the accumulator;
-//   warps 0-15  epilogue, two teams of eight warps: team k owns accumulator k and every second
-//               unit, so one team's barrier waits, TMEM loads and stores overlap the other's
-//               arithmetic. In a team thread (w, l) owns token 32*(w%4)+l and rows (w/4)*2, +1.
+//   warps 16-19 MMA issuers, one thread each; warps 0-15 epilogue, four teams of four warps.
+//               TMEM holds four accumulators of 128 columns (two query rows each). Accumulator
+//               a = 2*(unit parity) + (row half) has its own issuer and its own team: the issuer
+//               runs the N = 128 MMAs of its row half for every second unit, the team reads the
+//               result (thread (w, l): token 32*(w%4)+l, both rows). The chain MMA -> commit ->
+//               team's TMEM loads -> release -> next MMA is a few thousand cycles of latency per
+//               accumulator, several times the tensor pipe's time for the tile, and every step an
+//               issuer takes (barrier test, descriptor read, MMA, commit) costs 50-100 cycles;
+//               four independent chains keep the pipe and the CUDA cores busy.
 // Every reader of TMA-written shared memory waits on the mbarrier the copy completes on. Every
 // wait is bounded; a timeout sets the status word and all roles unwind.
 
@@ -47,10 +48,12 @@ constexpr int TS_RECS = TS_DESCRIBE * TS_ROWS + 2;
 constexpr int TS_REC_BYTES = 64;
 constexpr int TS_SMEM = 2 * TS_Q_BYTES + TS_A_STAGES * TS_A_BYTES + 2 * TS_W_BYTES + TS_SLOTS * TS_SLOT_BYTES +
                         TS_RECS * TS_REC_BYTES + 1024;
-constexpr int TS_TEAM_WARPS = 8;
-constexpr int TS_EPI_WARPS = 2 * TS_TEAM_WARPS;
-constexpr int TS_MMA_WARP = TS_EPI_WARPS, TS_PRODUCER_WARP = TS_EPI_WARPS + 2;  // issuers: warps 16, 17
-constexpr int TS_THREADS = (TS_EPI_WARPS + 3) * 32;
+constexpr int TS_ACCS = 4;                      // accumulators = teams = issuers
+constexpr int TS_ACC_COLS = TS_N / 2;           // 128 columns: two query rows
+constexpr int TS_TEAM_WARPS = 4;
+constexpr int TS_EPI_WARPS = TS_ACCS * TS_TEAM_WARPS;
+constexpr int TS_MMA_WARP = TS_EPI_WARPS, TS_PRODUCER_WARP = TS_EPI_WARPS + TS_ACCS;  // issuers: warps 16-19
+constexpr int TS_THREADS = (TS_EPI_WARPS + TS_ACCS + 1) * 32;
 
 __device__ int g_dsa_status = 0;  // 0 = ok; set when a bounded wait gave up
 
@@ -100,8 +103,8 @@ dsa_score_tc_kernel(ScoreParams p, const __grid_constant__ CUtensorMap tm_q, con
   __shared__ __align__(8) uint64_t s_a_empty[TS_A_STAGES];
   __shared__ __align__(8) uint64_t s_q_full[2];
   __shared__ __align__(8) uint64_t s_q_empty[2];
-  __shared__ __align__(8) uint64_t s_acc_full[2];
-  __shared__ __align__(8) uint64_t s_acc_empty[2];
+  __shared__ __align__(8) uint64_t s_acc_full[TS_ACCS];
+  __shared__ __align__(8) uint64_t s_acc_empty[TS_ACCS];
   __shared__ __align__(8) uint64_t s_slot_full[TS_SLOTS];
   __shared__ __align__(8) uint64_t s_slot_empty[TS_SLOTS];
   __shared__ uint32_t s_tmem_base;
@@ -118,17 +121,19 @@ dsa_score_tc_kernel(ScoreParams p, const __grid_constant__ CUtensorMap tm_q, con
   if (tid == 0) {
     for (int s = 0; s < TS_A_STAGES; ++s) {
       ako::tc::mbar_init(ako::smem_u32(&s_a_full[s]), 1);
-      ako::tc::mbar_init(ako::smem_u32(&s_a_empty[s]), 1);
+      ako::tc::mbar_init(ako::smem_u32(&s_a_empty[s]), 2);  // the two issuers of the unit's parity
     }
     for (int b = 0; b < 2; ++b) {
       ako::tc::mbar_init(ako::smem_u32(&s_q_full[b]), 1);
-      ako::tc::mbar_init(ako::smem_u32(&s_q_empty[b]), 2 + TS_EPI_WARPS);   // both issuers + every epilogue warp
-      ako::tc::mbar_init(ako::smem_u32(&s_acc_full[b]), 1);
-      ako::tc::mbar_init(ako::smem_u32(&s_acc_empty[b]), TS_TEAM_WARPS);
+      ako::tc::mbar_init(ako::smem_u32(&s_q_empty[b]), TS_ACCS + TS_EPI_WARPS);   // every issuer + every epilogue warp
+    }
+    for (int a = 0; a < TS_ACCS; ++a) {
+      ako::tc::mbar_init(ako::smem_u32(&s_acc_full[a]), 1);
+      ako::tc::mbar_init(ako::smem_u32(&s_acc_empty[a]), TS_TEAM_WARPS);
     }
     for (int s = 0; s < TS_SLOTS; ++s) {
       ako::tc::mbar_init(ako::smem_u32(&s_slot_full[s]), 1);
-      ako::tc::mbar_init(ako::smem_u32(&s_slot_empty[s]), 1 + TS_TEAM_WARPS);  // the owning issuer + the owning team
+      ako::tc::mbar_init(ako::smem_u32(&s_slot_empty[s]), 2 + 2 * TS_TEAM_WARPS);  // the unit's two issuers and two teams
     }
     ako::tc::mbar_init_fence();
   }
@@ -291,17 +296,19 @@ dsa_score_tc_kernel(ScoreParams p, const __grid_constant__ CUtensorMap tm_q, con
       }
       __syncwarp();  // the records are rewritten by the next describe step
     }
-  } else if (warp == TS_MMA_WARP || warp == TS_MMA_WARP + 1) {
+  } else if (warp >= TS_MMA_WARP && warp < TS_MMA_WARP + TS_ACCS) {
     // ================================ MMA issuers ==============================================
     // The barrier waits and the descriptor read for the issuer's NEXT key tile are done between
     // the second and third MMA of the current one.
     if (lane == 0) {
-      constexpr uint32_t IDESC_SHARED = ako::tc::idesc_e4m3_f32(128, TS_N);
+      constexpr uint32_t IDESC_SHARED = ako::tc::idesc_e4m3_f32(128, TS_ACC_COLS);
       constexpr uint32_t IDESC_ROW = ako::tc::idesc_e4m3_f32(128, NH);
-      struct Tile { uint32_t a_lo, b_lo, d, idesc; int stage, acc_wait; bool last; };  // descriptor low words
-      const int me = warp - TS_MMA_WARP;    // accumulator, and parity of the units taken
+      // a_lo, b_lo: descriptor low words; mma: this issuer's row half takes part in the tile
+      struct Tile { uint32_t a_lo, b_lo, d, idesc; int stage, acc_wait; bool last, mma; };
+      const int me = warp - TS_MMA_WARP;    // accumulator
+      const int par = me >> 1, rh = me & 1; // parity of the units taken; row half
       const uint32_t a_lo0 = ako::tc::smem_desc_lo(a_base), q_lo0 = ako::tc::smem_desc_lo(q_base);
-      const uint32_t acc = tmem_base + me * TS_N;
+      const uint32_t acc = tmem_base + me * TS_ACC_COLS;
       int n = 0;                            // units taken so far
       int ac = 0, subs = 0, sub = 0;        // current unit: next key tile ordinal, tiles, tiles issued
       bool shared = true;
@@ -311,7 +318,7 @@ dsa_score_tc_kernel(ScoreParams p, const __grid_constant__ CUtensorMap tm_q, con
       // 1: tile ready, 0: END record, -1: a wait gave up
       auto prepare = [&](Tile& t) -> int {
         if (sub == subs) {  // next unit
-          const int uo = 2 * n + me;
+          const int uo = 2 * n + par;
           const int slot = uo % TS_SLOTS;
           if (!ako::tc::mbar_wait(ako::smem_u32(&s_slot_full[slot]), (uint32_t)((uo / TS_SLOTS) & 1), &g_dsa_status, 4)) return -1;
           const volatile ScoreDesc* dp = reinterpret_cast<const volatile ScoreDesc*>(slot_ptr + slot * TS_SLOT_BYTES + TS_ROWS * TS_SCALE_BYTES);
@@ -323,7 +330,7 @@ dsa_score_tc_kernel(ScoreParams p, const __grid_constant__ CUtensorMap tm_q, con
             q_rel_to = qc;  // handed back after the tile in flight, the last one that may read them
             q_cur = qc;
             if (!ako::tc::mbar_wait(ako::smem_u32(&s_q_full[qc & 1]), (uint32_t)((qc >> 1) & 1), &g_dsa_status, 5)) return -1;
-            q_lo = q_lo0 + (qc & 1) * (TS_Q_BYTES >> 4);
+            q_lo = q_lo0 + (qc & 1) * (TS_Q_BYTES >> 4) + rh * ((2 * NH * HD) >> 4);  // this half's two rows
           }
           shared = flags & TS_F_SHARED;
           subs = shared ? 1 : TS_ROWS;
@@ -331,16 +338,19 @@ dsa_score_tc_kernel(ScoreParams p, const __grid_constant__ CUtensorMap tm_q, con
           acc_wait = (n & 1) ^ 1;  // parity to wait for before the unit's first MMA
           ++n;
         }
+        // Tiles of the other row half are waited for as well: the stage's release counts both
+        // issuers, and this keeps an issuer from arriving for the stage's next use too early.
         const int stage = ac % TS_A_STAGES;
         if (!ako::tc::mbar_wait(ako::smem_u32(&s_a_full[stage]), (uint32_t)((ac / TS_A_STAGES) & 1), &g_dsa_status, 7)) return -1;
         ako::tc::fence_after_thread_sync();
+        t.mma = shared || (sub >> 1) == rh;
         t.a_lo = a_lo0 + stage * (TS_A_BYTES >> 4);
-        t.b_lo = q_lo + (shared ? 0 : sub * ((NH * HD) >> 4));
-        t.d = acc + (shared ? 0 : sub * NH);
+        t.b_lo = q_lo + (shared ? 0 : (sub & 1) * ((NH * HD) >> 4));
+        t.d = acc + (shared ? 0 : (sub & 1) * NH);
         t.idesc = shared ? IDESC_SHARED : IDESC_ROW;
         t.stage = stage;
-        t.acc_wait = (sub == 0) ? acc_wait : -1;
-        t.last = sub == subs - 1;
+        t.acc_wait = (shared || sub == 2 * rh) ? acc_wait : -1;  // first tile that writes the accumulator
+        t.last = shared || sub == 2 * rh + 1;                    // last tile that writes it
         ++sub;
         ++ac;
         return 1;
@@ -348,34 +358,40 @@ dsa_score_tc_kernel(ScoreParams p, const __grid_constant__ CUtensorMap tm_q, con
       Tile cur, nxt;
       int r = prepare(cur);
       while (r == 1) {
-        // This issuer's units share one accumulator: the team must have read the previous result.
-        if (cur.acc_wait >= 0 &&
-            !ako::tc::mbar_wait(ako::smem_u32(&s_acc_empty[me]), (uint32_t)cur.acc_wait, &g_dsa_status, 6)) break;
-        ako::tc::mma_f8_lohi<false>(cur.d, cur.a_lo, cur.b_lo, cur.idesc);  // K = 32 slices: +32 B = +2
-        ako::tc::mma_f8_lohi<true>(cur.d, cur.a_lo + 2, cur.b_lo + 2, cur.idesc);
-        r = prepare(nxt);
-        ako::tc::mma_f8_lohi<true>(cur.d, cur.a_lo + 4, cur.b_lo + 4, cur.idesc);
-        ako::tc::mma_f8_lohi<true>(cur.d, cur.a_lo + 6, cur.b_lo + 6, cur.idesc);
-        ako::tc::mma_commit(ako::smem_u32(&s_a_empty[cur.stage]));
-        if (cur.last) ako::tc::mma_commit(ako::smem_u32(&s_acc_full[me]));
+        if (cur.mma) {
+          // This issuer's units share one accumulator: the team must have read the previous result.
+          if (cur.acc_wait >= 0 &&
+              !ako::tc::mbar_wait(ako::smem_u32(&s_acc_empty[me]), (uint32_t)cur.acc_wait, &g_dsa_status, 6)) break;
+          ako::tc::mma_f8_lohi<false>(cur.d, cur.a_lo, cur.b_lo, cur.idesc);  // K = 32 slices: +32 B = +2
+          ako::tc::mma_f8_lohi<true>(cur.d, cur.a_lo + 2, cur.b_lo + 2, cur.idesc);
+          r = prepare(nxt);
+          ako::tc::mma_f8_lohi<true>(cur.d, cur.a_lo + 4, cur.b_lo + 4, cur.idesc);
+          ako::tc::mma_f8_lohi<true>(cur.d, cur.a_lo + 6, cur.b_lo + 6, cur.idesc);
+          ako::tc::mma_commit(ako::smem_u32(&s_a_empty[cur.stage]));
+          if (cur.last) ako::tc::mma_commit(ako::smem_u32(&s_acc_full[me]));
+        } else {
+          ako::tc::mbar_arrive(ako::smem_u32(&s_a_empty[cur.stage]));
+          r = prepare(nxt);
+        }
         for (; q_rel < q_rel_to; ++q_rel)  // groups this issuer is past (it may never have seen some)
           ako::tc::mma_commit(ako::smem_u32(&s_q_empty[q_rel & 1]));
         cur = nxt;
       }
     }
   } else {
-    // ================================ epilogue (two teams) ========================================
-    const int team = warp / TS_TEAM_WARPS;
+    // ================================ epilogue (four teams) =======================================
+    const int team = warp / TS_TEAM_WARPS;  // accumulator
+    const int par = team >> 1;          // parity of the units taken
+    const int rh = team & 1;            // which two rows of the group
     const int q = warp & 3;             // TMEM lane quarter
-    const int rh = (warp >> 2) & 1;     // which two rows of the group
     const int t = 32 * q + lane;        // token inside the unit
-    const uint32_t tmem_team = tmem_base + ((uint32_t)(32 * q) << 16) + team * TS_N + rh * 2 * NH;
+    const uint32_t tmem_team = tmem_base + ((uint32_t)(32 * q) << 16) + team * TS_ACC_COLS;
     int q_rel = 0;                      // query buffers released so far (group ordinals below this)
     int q_cur = -1;
     const float* wrow = nullptr;
     float* orow[2] = {nullptr, nullptr};
     for (int n = 0;; ++n) {
-      const int uo = 2 * n + team;
+      const int uo = 2 * n + par;
       const int slot = uo % TS_SLOTS;
       const unsigned char* sp = slot_ptr + slot * TS_SLOT_BYTES;
       if (!ako::tc::mbar_wait(ako::smem_u32(&s_slot_full[slot]), (uint32_t)((uo / TS_SLOTS) & 1), &g_dsa_status, 8)) break;
