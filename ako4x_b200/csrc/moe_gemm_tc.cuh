@@ -4,7 +4,11 @@
 //
 // One persistent CTA per SM walks the tile list (expert, n-tile, m-tile). A tile is 128 rows x 256
 // weight rows; every K step of 128 (one scale block) is four tcgen05.mma M128 N256 K32 e4m3
-// instructions into one of two 256-column TMEM accumulators. 10 warps, three roles:
+// instructions into one of two 256-column TMEM accumulators. 12 warps, three roles; the promotion
+// warps need more registers than a 12-warp CTA grants evenly (128 accumulators + 64 staging values
+// per thread), so each role begins by re-balancing: warps 8-11 drop to 56 registers per thread and
+// warps 0-7 rise to 224 (setmaxnreg; 2 x 224 + 56 = 3 x 168 per scheduler). Without it the
+// accumulators spill and the spill traffic sits in the MMA -> promotion -> MMA hand-over chain.
 //   warp 9      one thread issues TMA loads (cp.async.bulk.tensor, 128-byte swizzle) of the
 //               activation box (128 rows x 128 B) and the weight boxes (256 rows x 128 B) into a
 //               4-stage shared-memory ring; completion is counted in bytes on the stage's mbarrier;
@@ -21,6 +25,7 @@
 // GEMM1 orders the weight rows of a tile as [g1 0-63 | g2 0-63 | g1 64-127 | g2 64-127] of one
 // 128-column block of h (four 64-row boxes), so each promotion thread owns matching linear/gate
 // columns and applies SwiGLU, the two-piece e4m3 quantisation and 64-byte row stores by itself.
+//   warps 10,11 idle: they only donate their registers.
 // GEMM2 stores fp32 y. Every mbarrier wait is bounded; a timeout sets p.error and all roles unwind
 // to a common exit that frees TMEM.
 #pragma once
@@ -34,7 +39,8 @@ constexpr int TC_B_BYTES = TC_BN * 128;
 constexpr int TC_STAGE_BYTES = TC_A_BYTES + TC_B_BYTES;
 constexpr int TC_SMEM = TC_STAGES * TC_STAGE_BYTES + 1024;  // + slack for 1024-byte alignment
 constexpr int TC_WORKERS = 256;
-constexpr int TC_THREADS = TC_WORKERS + 64;
+constexpr int TC_THREADS = TC_WORKERS + 128;  // 3 warpgroups: setmaxnreg acts on whole warpgroups
+constexpr int TC_REGS_WORKER = 224, TC_REGS_OTHER = 56;
 constexpr int TC_TMEM_COLS = 512;
 
 enum : int { kErrLoad = 1, kErrMmaFull = 2, kErrMmaAcc = 3, kErrEpilogue = 4 };
@@ -104,8 +110,11 @@ moe_gemm_tc_kernel(GemmParams p, const __grid_constant__ CUtensorMap tm_a, const
   const uint32_t tmem_base = s_tmem_base;
   const int total_tiles = s_cum[p.n_local] * NT_TILES;
 
-  if (warp == 9) {
+  if (warp >= 10) {
+    ako::tc::reg_dec<TC_REGS_OTHER>();  // donor warps
+  } else if (warp == 9) {
     // ================================ TMA producer =============================================
+    ako::tc::reg_dec<TC_REGS_OTHER>();
     if (lane == 0) {
       ako::tc::tma_prefetch_desc(&tm_a);
       ako::tc::tma_prefetch_desc(&tm_b);
@@ -136,32 +145,37 @@ moe_gemm_tc_kernel(GemmParams p, const __grid_constant__ CUtensorMap tm_a, const
     }
   } else if (warp == 8) {
     // ================================ MMA issuer ===============================================
+    ako::tc::reg_dec<TC_REGS_OTHER>();
     if (lane == 0) {
-      int g = 0;
+      // descriptor low words: +2 per K = 32 slice, bytes >> 4 per stage
+      const uint32_t a_lo0 = ako::tc::smem_desc_lo(smem_base);
+      const uint32_t b_lo0 = ako::tc::smem_desc_lo(smem_base + TC_A_BYTES);
+      int g = 0, stage = 0;
+      uint32_t ph = 0;
       bool ok = true;
       for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
         for (int kb = 0; kb < NKB; ++kb, ++g) {
-          const int stage = g % TC_STAGES;
-          const uint32_t ph = (g / TC_STAGES) & 1;
           const int buf = g & 1;
           const uint32_t aph = (g >> 1) & 1;
           if (!ako::tc::mbar_wait(ako::smem_u32(&s_acc_empty[buf]), aph ^ 1u, p.error, kErrMmaAcc)) { ok = false; break; }
           if (!ako::tc::mbar_wait(ako::smem_u32(&s_full[stage]), ph, p.error, kErrMmaFull)) { ok = false; break; }
           ako::tc::fence_after_thread_sync();
-          const uint32_t sa = smem_base + stage * TC_STAGE_BYTES;
-          const uint32_t sb = sa + TC_A_BYTES;
+          const uint32_t a_lo = a_lo0 + stage * (TC_STAGE_BYTES >> 4);
+          const uint32_t b_lo = b_lo0 + stage * (TC_STAGE_BYTES >> 4);
           const uint32_t d = tmem_base + buf * TC_BN;
-#pragma unroll
-          for (int ks = 0; ks < 4; ++ks)
-            ako::tc::mma_f8(d, ako::tc::smem_desc_k_sw128(sa + ks * 32), ako::tc::smem_desc_k_sw128(sb + ks * 32),
-                            IDESC, ks > 0 ? 1u : 0u);
+          ako::tc::mma_f8_lohi<false>(d, a_lo, b_lo, IDESC);
+          ako::tc::mma_f8_lohi<true>(d, a_lo + 2, b_lo + 2, IDESC);
+          ako::tc::mma_f8_lohi<true>(d, a_lo + 4, b_lo + 4, IDESC);
+          ako::tc::mma_f8_lohi<true>(d, a_lo + 6, b_lo + 6, IDESC);
           ako::tc::mma_commit(ako::smem_u32(&s_empty[stage]));
           ako::tc::mma_commit(ako::smem_u32(&s_acc_full[buf]));
+          if (++stage == TC_STAGES) { stage = 0; ph ^= 1u; }
         }
       }
     }
   } else {
     // ================================ promotion threads =========================================
+    ako::tc::reg_inc<TC_REGS_WORKER>();
     const int half = warp >> 2;        // which 128 accumulator columns
     const int q = warp & 3;            // TMEM lane quarter
     const int r = 32 * q + lane;       // accumulator row of this thread
@@ -206,7 +220,8 @@ moe_gemm_tc_kernel(GemmParams p, const __grid_constant__ CUtensorMap tm_a, const
         float v0[32], v1[32];
         ako::tc::tmem_ld32(taddr, v0);
         ako::tc::tmem_ld32(taddr + 32, v1);
-        ako::tc::tmem_ld_wait();
+        ako::tc::tmem_ld_wait_regs(v0);
+        ako::tc::tmem_ld_wait_regs(v1);
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
           acc[j] = fmaf(v0[j], s0, acc[j]);
@@ -214,7 +229,8 @@ moe_gemm_tc_kernel(GemmParams p, const __grid_constant__ CUtensorMap tm_a, const
         }
         ako::tc::tmem_ld32(taddr + 64, v0);
         ako::tc::tmem_ld32(taddr + 96, v1);
-        ako::tc::tmem_ld_wait();
+        ako::tc::tmem_ld_wait_regs(v0);
+        ako::tc::tmem_ld_wait_regs(v1);
         ako::tc::fence_before_thread_sync();
         __syncwarp();
         if (lane == 0) ako::tc::mbar_arrive(ako::smem_u32(&s_acc_empty[buf]));

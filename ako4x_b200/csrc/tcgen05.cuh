@@ -30,6 +30,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// Non-blocking test of the phase: returns at once. A waiter polling with this wakes within a few
+// tens of cycles of the completion; try_wait may leave it suspended far longer.
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n.reg .pred p;\n"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
 // The same test, letting the hardware keep the thread suspended for up to `ns` nanoseconds while
 // the phase is incomplete: a waiting warp then leaves its scheduler's issue slots to the others.
 __device__ __forceinline__ bool mbar_try_wait_suspend(uint32_t bar, uint32_t parity, uint32_t ns) {
@@ -51,8 +64,8 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* er
   const long long t0 = clock64();
   uint32_t spins = 0;
   while (true) {
-    if (mbar_try_wait_suspend(bar, parity, 2000u)) return true;
-    if ((++spins & 15u) == 0u) {
+    if (mbar_test_wait(bar, parity)) return true;
+    if ((++spins & 1023u) == 0u) {
       if (*reinterpret_cast<volatile int*>(err) != 0) return false;
       if (clock64() - t0 > kWaitBudgetCycles) {
         atomicCAS(err, 0, code);
