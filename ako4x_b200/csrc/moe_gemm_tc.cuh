@@ -37,7 +37,8 @@ constexpr int TC_STAGES = 4;
 constexpr int TC_A_BYTES = TC_BM * 128;
 constexpr int TC_B_BYTES = TC_BN * 128;
 constexpr int TC_STAGE_BYTES = TC_A_BYTES + TC_B_BYTES;
-constexpr int TC_SMEM = TC_STAGES * TC_STAGE_BYTES + 1024;  // + slack for 1024-byte alignment
+constexpr int TC_EXTRA_BYTES = 32 * 1024;  // after the ring: GEMM1 row maxima / GEMM2 store staging (4 KB per warp)
+constexpr int TC_SMEM = TC_STAGES * TC_STAGE_BYTES + TC_EXTRA_BYTES + 1024;  // + slack for 1024-byte alignment
 constexpr int TC_WORKERS = 256;
 constexpr int TC_THREADS = TC_WORKERS + 128;  // 3 warpgroups: setmaxnreg acts on whole warpgroups
 constexpr int TC_REGS_WORKER = 224, TC_REGS_OTHER = 56;
@@ -79,10 +80,11 @@ moe_gemm_tc_kernel(GemmParams p, const __grid_constant__ CUtensorMap tm_a, const
   __shared__ __align__(8) uint64_t s_xchg[2];
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_cum[MAX_LOCAL + 1];
-  __shared__ float s_amax[2][2][TC_BM];  // [tile parity][column half][row]
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const uint32_t smem_base = (ako::smem_u32(smem_raw) + 1023u) & ~1023u;
+  unsigned char* extra = smem_raw + (smem_base - ako::smem_u32(smem_raw)) + TC_STAGES * TC_STAGE_BYTES;
+  float (*s_amax)[2][TC_BM] = reinterpret_cast<float (*)[2][TC_BM]>(extra);  // GEMM1: [tile parity][column half][row]
 
   if (tid == 0) {
     int acc = 0;
@@ -243,11 +245,28 @@ moe_gemm_tc_kernel(GemmParams p, const __grid_constant__ CUtensorMap tm_a, const
       if (!ok) break;
 
       if (WHICH == 2) {
-        if (live) {
-          float* yp = p.y + (int64_t)(ti.row0 + r) * HID + ti.nt * TC_BN + half * 128;
+        // A thread holds 128 columns of ONE row; stored directly, a warp's instruction would touch
+        // 32 rows with 16 bytes each. Each warp transposes 32-column chunks through its own 4 KB
+        // of shared memory (16-byte groups XOR-swizzled by row: conflict-free both ways) so that an
+        // instruction writes four rows of 128 contiguous bytes.
+        float4* stg = reinterpret_cast<float4*>(extra) + warp * 256;
+        float* ytile = p.y + (int64_t)ti.row0 * HID + ti.nt * TC_BN + half * 128;
 #pragma unroll
-          for (int j = 0; j < 128; j += 4)
-            *reinterpret_cast<float4*>(yp + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+        for (int c = 0; c < 4; ++c) {
+#pragma unroll
+          for (int g4 = 0; g4 < 8; ++g4)
+            stg[lane * 8 + (g4 ^ (lane & 7))] =
+                make_float4(acc[32 * c + 4 * g4], acc[32 * c + 4 * g4 + 1], acc[32 * c + 4 * g4 + 2], acc[32 * c + 4 * g4 + 3]);
+          __syncwarp();
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int rr = 4 * i + (lane >> 3), gg = lane & 7;
+            const float4 val = stg[rr * 8 + (gg ^ (rr & 7))];
+            const int trow = 32 * q + rr;
+            if (trow < ti.rows)
+              *reinterpret_cast<float4*>(ytile + (int64_t)trow * HID + 32 * c + 4 * gg) = val;
+          }
+          __syncwarp();
         }
       } else {
         // SwiGLU on this thread's 64 columns of h, row maximum across the two column halves.
@@ -256,7 +275,7 @@ moe_gemm_tc_kernel(GemmParams p, const __grid_constant__ CUtensorMap tm_a, const
 #pragma unroll
         for (int j = 0; j < 64; ++j) {
           const float x1 = acc[j], x2 = acc[64 + j];
-          const float h = (x2 / (1.0f + __expf(-x2))) * x1;
+          const float h = __fdividef(x2, 1.0f + __expf(-x2)) * x1;
           acc[j] = h;
           mx = fmaxf(mx, fabsf(h));
         }
