@@ -7,6 +7,8 @@
 //                   experts (ties: lower index), weights; counts tokens per local expert.
 //   2. scatter      one CTA per local expert: stable (token-ordered) positions inside the
 //                   expert's segment, so the row order and every later sum is deterministic.
+//   2b. permute     every (token, local expert) pair's activation row and scales copied into
+//                   expert-sorted order, so a GEMM tile's A operand is one TMA box.
 //   3. GEMM1        grouped FP8 GEMM  g = x W13^T  with 128x128 block-scale promotion in fp32
 //                   registers, fused SwiGLU  h = silu(g[2048:]) * g[:2048],  and h written as TWO
 //                   e4m3 pieces per element (h ~ s*(hi + lo/16), s a power of two per row and
@@ -15,9 +17,9 @@
 //   4. GEMM2        the same grouped FP8 GEMM over K = 2*2048 (hi piece, lo piece) against W2.
 //   5. combine      out[t] = bf16( sum over the token's local experts, in expert order, of
 //                   weight * y ): a gather-reduce, no atomics.
-// The grouped GEMM is persistent: each CTA walks a tile list (expert, n-tile, m-tile) derived from
-// the per-expert counts; tiles are 32*WM rows x 256 weight rows x 128 (one scale block) per step,
-// fed by a 4-stage cp.async ring with XOR-swizzled 128-byte rows and mma.sync.m16n8k32 e4m3.
+// The grouped GEMM (moe_gemm_tc.cuh) is persistent: each CTA walks a tile list (expert, n-tile,
+// m-tile) derived from the per-expert counts; tiles are 128 rows x 256 weight rows, K steps of 128
+// (one scale block) fed by TMA and multiplied by tcgen05.mma into TMEM accumulators.
 #include <cuda.h>  // CUtensorMap and its enums (types only; the encoder is fetched at run time)
 
 #include <cstdlib>
@@ -251,21 +253,6 @@ __global__ void __launch_bounds__(1024) moe_scatter_kernel(
 // ---------------------------------------------------------------------------------------------
 // 3/4. grouped FP8 block-scale GEMM (persistent)
 // ---------------------------------------------------------------------------------------------
-constexpr int WN = 4;            // warps along N; each warp owns 8 n-tiles of 8 weight rows
-constexpr int BROWS = 256;       // weight rows per CTA tile (two 128-row scale blocks)
-constexpr int G_STAGES = 4;
-
-template <int WM>
-struct GemmCfg {
-  static constexpr int BM = 32 * WM;
-  static constexpr int THREADS = 32 * WM * WN;
-  static constexpr int A_BYTES = BM * 128;
-  static constexpr int B_BYTES = BROWS * 128;
-  static constexpr int S_BYTES = BM * 4;  // activation scales of the stage
-  static constexpr int STAGE = A_BYTES + B_BYTES + S_BYTES;
-  static constexpr int SMEM = G_STAGES * STAGE;
-};
-
 struct GemmParams {
   const uint8_t* a;          // GEMM1: x [T,7168]; GEMM2: hq [cap,4096]
   const float* a_scale;      // GEMM1: [56,T]; GEMM2: h_scale [16,cap]
@@ -283,240 +270,6 @@ struct GemmParams {
   int n_local;
 };
 
-template <int WM, int WHICH>  // WHICH: 1 = GEMM1 (+SwiGLU, two-piece quantisation), 2 = GEMM2
-__global__ void __launch_bounds__(GemmCfg<WM>::THREADS, 1) moe_grouped_gemm_kernel(GemmParams p) {
-  using C = GemmCfg<WM>;
-  constexpr int BM = C::BM;
-  constexpr int NKB = (WHICH == 1) ? KB1 : KB2;
-  constexpr int NT_TILES = (WHICH == 1) ? (INTER / 128) : (HID / BROWS);  // 16 or 28 n-tiles
-  extern __shared__ __align__(128) unsigned char smem[];
-  __shared__ int s_cum[MAX_LOCAL + 1];   // cumulative m-tiles per expert
-  __shared__ int s_tok[BM];              // A row of each tile row (token or pair row), -1 = none
-  __shared__ float s_bs[2][NKB];         // weight scales of the tile's two 128-row blocks
-  __shared__ int s_amax[BM];             // GEMM1 epilogue: per-row max |h| (float bits)
-
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int wm = warp / WN, wn = warp % WN;
-  const int g = lane >> 2, t = lane & 3;
-
-  if (tid == 0) {
-    int acc = 0;
-    for (int e = 0; e < p.n_local; ++e) {
-      s_cum[e] = acc;
-      acc += (p.counts[e] + BM - 1) / BM;
-    }
-    s_cum[p.n_local] = acc;
-  }
-  __syncthreads();
-  const int total_tiles = s_cum[p.n_local] * NT_TILES;
-
-  for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
-    // tile -> (expert, n-tile, m-tile); m fastest so neighbouring CTAs share weight tiles
-    int e = 0;
-    while (s_cum[e + 1] * NT_TILES <= tile) ++e;
-    const int mt_e = s_cum[e + 1] - s_cum[e];
-    const int rem = tile - s_cum[e] * NT_TILES;
-    const int nt = rem / mt_e, mt = rem % mt_e;
-    const int cnt = p.counts[e];
-    const int row0 = p.offsets[e] + mt * BM;       // first pair row of the tile
-    const int rows = min(BM, cnt - mt * BM);
-
-    __syncthreads();  // previous tile's readers of s_tok / s_bs / smem are done
-    if (tid < BM) {
-      int src = -1;
-      if (tid < rows) src = (WHICH == 1) ? p.sorted_token[row0 + tid] : row0 + tid;
-      s_tok[tid] = src;
-      if (WHICH == 1) s_amax[tid] = 0;
-    }
-    for (int i = tid; i < 2 * NKB; i += C::THREADS) {
-      const int blk = i / NKB, kb = i % NKB;
-      float v;
-      if (WHICH == 1)
-        v = p.w_scale[((int64_t)e * (2 * INTER / 128) + blk * (INTER / 128) + nt) * KB1 + kb];
-      else
-        v = p.w_scale[((int64_t)e * (HID / 128) + nt * 2 + blk) * (INTER / 128) + (kb & 15)];
-      s_bs[blk][kb] = v;
-    }
-    __syncthreads();
-
-    const uint8_t* wbase = p.w + (int64_t)e * (WHICH == 1 ? (int64_t)2 * INTER * HID : (int64_t)HID * INTER);
-    constexpr int64_t W_ROW = (WHICH == 1) ? HID : INTER;   // bytes per weight row
-    constexpr int64_t A_ROW = (WHICH == 1) ? HID : 2 * INTER;
-
-    auto load_stage = [&](int kb, int stage) {
-      unsigned char* sa = smem + stage * C::STAGE;
-      unsigned char* sb = sa + C::A_BYTES;
-      float* ss = reinterpret_cast<float*>(sb + C::B_BYTES);
-      // A: BM rows x 8 chunks
-      for (int i = tid; i < BM * 8; i += C::THREADS) {
-        const int r = i >> 3, c = i & 7;
-        const int src = s_tok[r];
-        const uint8_t* gp = p.a + (int64_t)max(src, 0) * A_ROW + (int64_t)kb * 128 + c * 16;
-        ako::cp_async16(ako::smem_u32(sa + r * 128 + ((c ^ (r & 7)) << 4)), gp, src >= 0);
-      }
-      // B: 256 weight rows x 8 chunks
-      const int wkb = (WHICH == 1) ? kb : (kb & 15);
-      for (int i = tid; i < BROWS * 8; i += C::THREADS) {
-        const int r = i >> 3, c = i & 7;
-        int64_t wrow;
-        if (WHICH == 1) wrow = (r < 128) ? (nt * 128 + r) : (INTER + nt * 128 + (r - 128));
-        else wrow = (int64_t)nt * BROWS + r;
-        const uint8_t* gp = wbase + wrow * W_ROW + (int64_t)wkb * 128 + c * 16;
-        ako::cp_async16(ako::smem_u32(sb + r * 128 + ((c ^ (r & 7)) << 4)), gp, true);
-      }
-      // activation scales of the k-block
-      if (tid < BM) {
-        const int src = s_tok[tid];
-        const float* gp = p.a_scale + (int64_t)wkb * p.a_scale_stride + max(src, 0);
-        const int sz = (src >= 0) ? 4 : 0;
-        asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;\n" ::"r"(ako::smem_u32(ss + tid)),
-                     "l"(gp), "r"(sz));
-      }
-    };
-
-    float acc[2][8][4];
-#pragma unroll
-    for (int mi = 0; mi < 2; ++mi)
-#pragma unroll
-      for (int ni = 0; ni < 8; ++ni) acc[mi][ni][0] = acc[mi][ni][1] = acc[mi][ni][2] = acc[mi][ni][3] = 0.f;
-
-#pragma unroll
-    for (int s = 0; s < G_STAGES - 1; ++s) {
-      load_stage(s, s);
-      ako::cp_async_commit();
-    }
-
-#pragma unroll 1
-    for (int kb = 0; kb < NKB; ++kb) {
-      ako::cp_async_wait<G_STAGES - 2>();
-      __syncthreads();
-      if (kb + G_STAGES - 1 < NKB) load_stage(kb + G_STAGES - 1, (kb + G_STAGES - 1) % G_STAGES);
-      ako::cp_async_commit();
-
-      const unsigned char* sa = smem + (kb % G_STAGES) * C::STAGE;
-      const unsigned char* sb = sa + C::A_BYTES;
-      const float* ss = reinterpret_cast<const float*>(sb + C::B_BYTES);
-
-      float blk[2][8][4];
-#pragma unroll
-      for (int mi = 0; mi < 2; ++mi)
-#pragma unroll
-        for (int ni = 0; ni < 8; ++ni) blk[mi][ni][0] = blk[mi][ni][1] = blk[mi][ni][2] = blk[mi][ni][3] = 0.f;
-
-#pragma unroll
-      for (int ks = 0; ks < 4; ++ks) {
-        uint32_t af[2][4];
-#pragma unroll
-        for (int mi = 0; mi < 2; ++mi) {
-          const int r = 32 * wm + 16 * mi + (lane & 7) + (((lane >> 3) & 1) << 3);
-          const int c = 2 * ks + (lane >> 4);
-          ako::ldmatrix_x4(af[mi][0], af[mi][1], af[mi][2], af[mi][3],
-                           ako::smem_u32(sa + r * 128 + ((c ^ (r & 7)) << 4)));
-        }
-#pragma unroll
-        for (int np = 0; np < 4; ++np) {  // pairs of n-tiles
-          // n-tiles 0-3 sit in rows [0,128), 4-7 in rows [128,256) of the weight tile
-          const int ni0 = 2 * np;
-          const int rbase = ((ni0 < 4) ? 0 : 128) + 32 * wn + 8 * (ni0 & 3);
-          const int r = rbase + ((lane >> 4) << 3) + (lane & 7);
-          const int c = 2 * ks + ((lane >> 3) & 1);
-          uint32_t b00, b01, b10, b11;
-          ako::ldmatrix_x4(b00, b01, b10, b11, ako::smem_u32(sb + r * 128 + ((c ^ (r & 7)) << 4)));
-#pragma unroll
-          for (int mi = 0; mi < 2; ++mi) {
-            ako::mma_e4m3_16832(blk[mi][ni0], af[mi], b00, b01);
-            ako::mma_e4m3_16832(blk[mi][ni0 + 1], af[mi], b10, b11);
-          }
-        }
-      }
-      // promotion: acc += blk * a_scale[row] * w_scale[block]
-      const float bs0 = s_bs[0][kb], bs1 = s_bs[1][kb];
-      const float piece = (WHICH == 2 && kb >= 16) ? 0.0625f : 1.0f;
-#pragma unroll
-      for (int mi = 0; mi < 2; ++mi) {
-        const int r = 32 * wm + 16 * mi + g;
-        const float sa0 = ss[r] * piece, sa1 = ss[r + 8] * piece;
-#pragma unroll
-        for (int ni = 0; ni < 8; ++ni) {
-          const float bsv = (ni < 4) ? bs0 : bs1;
-          acc[mi][ni][0] = fmaf(blk[mi][ni][0], sa0 * bsv, acc[mi][ni][0]);
-          acc[mi][ni][1] = fmaf(blk[mi][ni][1], sa0 * bsv, acc[mi][ni][1]);
-          acc[mi][ni][2] = fmaf(blk[mi][ni][2], sa1 * bsv, acc[mi][ni][2]);
-          acc[mi][ni][3] = fmaf(blk[mi][ni][3], sa1 * bsv, acc[mi][ni][3]);
-        }
-      }
-    }
-    ako::cp_async_wait<0>();
-
-    if (WHICH == 2) {
-      // y[pair_row][n] fp32
-#pragma unroll
-      for (int mi = 0; mi < 2; ++mi)
-#pragma unroll
-        for (int hf = 0; hf < 2; ++hf) {
-          const int r = 32 * wm + 16 * mi + g + 8 * hf;
-          if (r < rows) {
-            float* yp = p.y + (int64_t)(row0 + r) * HID + nt * BROWS;
-#pragma unroll
-            for (int ni = 0; ni < 8; ++ni) {
-              const int col = ((ni < 4) ? 0 : 128) + 32 * wn + 8 * (ni & 3) + 2 * t;
-              *reinterpret_cast<float2*>(yp + col) = make_float2(acc[mi][ni][2 * hf], acc[mi][ni][2 * hf + 1]);
-            }
-          }
-        }
-    } else {
-      // SwiGLU: n-tiles 0-3 hold the linear half, 4-7 the gate half of the same 32 columns
-      float hv[2][2][4][2];
-#pragma unroll
-      for (int mi = 0; mi < 2; ++mi)
-#pragma unroll
-        for (int hf = 0; hf < 2; ++hf) {
-          float mx = 0.f;
-#pragma unroll
-          for (int ni = 0; ni < 4; ++ni)
-#pragma unroll
-            for (int j = 0; j < 2; ++j) {
-              const float x1 = acc[mi][ni][2 * hf + j];
-              const float x2 = acc[mi][ni + 4][2 * hf + j];
-              const float h = (x2 / (1.0f + __expf(-x2))) * x1;
-              hv[mi][hf][ni][j] = h;
-              mx = fmaxf(mx, fabsf(h));
-            }
-          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-          if (t == 0) atomicMax(&s_amax[32 * wm + 16 * mi + g + 8 * hf], __float_as_int(mx));
-        }
-      __syncthreads();
-#pragma unroll
-      for (int mi = 0; mi < 2; ++mi)
-#pragma unroll
-        for (int hf = 0; hf < 2; ++hf) {
-          const int r = 32 * wm + 16 * mi + g + 8 * hf;
-          if (r < rows) {
-            const float amax = __int_as_float(s_amax[r]);
-            // power-of-two scale with amax / scale < 256 (e4m3 holds up to 448)
-            int ex = ((__float_as_int(amax) >> 23) & 0xff) - 127 - 7;
-            ex = max(ex, -100);
-            const float sc = __int_as_float((ex + 127) << 23);
-            const float inv = __int_as_float((127 - ex) << 23);
-            uint8_t* hp = p.hq + (int64_t)(row0 + r) * (2 * INTER) + nt * 128 + 32 * wn + 2 * t;
-#pragma unroll
-            for (int ni = 0; ni < 4; ++ni) {
-              const float v0 = hv[mi][hf][ni][0] * inv, v1 = hv[mi][hf][ni][1] * inv;
-              const __nv_fp8x2_storage_t hi = __nv_cvt_float2_to_fp8x2(make_float2(v0, v1), __NV_SATFINITE, __NV_E4M3);
-              const __half2_raw hr = __nv_cvt_fp8x2_to_halfraw2(hi, __NV_E4M3);
-              const float2 hf2 = __half22float2(*reinterpret_cast<const __half2*>(&hr));
-              const __nv_fp8x2_storage_t lo = __nv_cvt_float2_to_fp8x2(
-                  make_float2((v0 - hf2.x) * 16.f, (v1 - hf2.y) * 16.f), __NV_SATFINITE, __NV_E4M3);
-              *reinterpret_cast<__nv_fp8x2_storage_t*>(hp + 8 * ni) = hi;
-              *reinterpret_cast<__nv_fp8x2_storage_t*>(hp + INTER + 8 * ni) = lo;
-            }
-            if (wn == 0 && t == 0) p.h_scale[(int64_t)nt * p.h_scale_stride + row0 + r] = sc;
-          }
-        }
-    }
-  }
-}
 
 // ---------------------------------------------------------------------------------------------
 // 2b. permute: copy every (token, local expert) pair's activation row and its 56 scales into
@@ -629,18 +382,6 @@ __global__ void __launch_bounds__(256) moe_ep_combine_kernel(
   }
 }
 
-template <int WM, typename Mark>
-int launch_gemms(const GemmParams& p1, const GemmParams& p2, int sms, cudaStream_t st, Mark mark) {
-  using C = GemmCfg<WM>;
-  if (!ako::ensure_dynamic_smem<moe_grouped_gemm_kernel<WM, 1>>(C::SMEM)) return AKO4X_ELAUNCH;
-  if (!ako::ensure_dynamic_smem<moe_grouped_gemm_kernel<WM, 2>>(C::SMEM)) return AKO4X_ELAUNCH;
-  moe_grouped_gemm_kernel<WM, 1><<<sms, C::THREADS, C::SMEM, st>>>(p1);
-  AKO_CHECK_LAUNCH();
-  mark(2);
-  moe_grouped_gemm_kernel<WM, 2><<<sms, C::THREADS, C::SMEM, st>>>(p2);
-  AKO_CHECK_LAUNCH();
-  return AKO4X_OK;
-}
 
 // p1 / p2 are the GEMM1 / GEMM2 parameters with the expert-sorted activation copy as A.
 template <typename Mark>
@@ -761,22 +502,14 @@ extern "C" int ako4x_moe_fp8_block_scale_staged(
   const int sms = sm_count();
   mark(1);
   int rc;
-  // average rows per local expert ~ tokens * 8 / 256
-  static const bool legacy_mma = [] {
-    const char* v = getenv("AKO4X_MOE_LEGACY_MMA");  // development A/B switch only
-    return v && v[0] == '1';
-  }();
-  if (!legacy_mma) {
-    moe_permute_kernel<<<(unsigned)ako::cdiv(tokens * TOPK, 8), 256, 0, st>>>(
-        (const uint8_t*)hidden_states, hidden_states_scale, w.pair_pos, w.xs, w.xs_scale, (int)tokens, cap);
-    AKO_CHECK_LAUNCH();
-    GemmParams t1 = p1;
-    t1.a = w.xs;
-    t1.a_scale = w.xs_scale;
-    t1.a_scale_stride = cap;
-    rc = launch_gemms_tc(t1, p2, cap, n_local, sms, st, mark);
-  } else if (tokens >= 1024) rc = launch_gemms<2>(p1, p2, sms, st, mark);
-  else rc = launch_gemms<1>(p1, p2, sms, st, mark);
+  moe_permute_kernel<<<(unsigned)ako::cdiv(tokens * TOPK, 8), 256, 0, st>>>(
+      (const uint8_t*)hidden_states, hidden_states_scale, w.pair_pos, w.xs, w.xs_scale, (int)tokens, cap);
+  AKO_CHECK_LAUNCH();
+  GemmParams t1 = p1;
+  t1.a = w.xs;
+  t1.a_scale = w.xs_scale;
+  t1.a_scale_stride = cap;
+  rc = launch_gemms_tc(t1, p2, cap, n_local, sms, st, mark);
   if (rc != AKO4X_OK) return rc;
   mark(3);
   moe_combine_kernel<<<(unsigned)tokens, 256, 0, st>>>(w.y, w.pair_pos, w.topk_w, (__nv_bfloat16*)out);

@@ -461,7 +461,7 @@ def run_moe(args, rank, world, dist_on, peaks):
         fp8_peak = 2 * peaks["bf16_tflops"]
         achieved = pairs * FLOP_PER_PAIR_GEMM1 / (st[1] * 1e-3) / 1e12
         line["roofline"] = {
-            "bound": "tensor", "kernel": "moe_grouped_gemm_kernel<2,1> (GEMM1 + SwiGLU)",
+            "bound": "tensor", "kernel": "moe_gemm_tc_kernel<1> (GEMM1 + SwiGLU + two-piece e4m3 h)",
             "achieved": achieved, "peak": fp8_peak, "unit": "TFLOP/s", "frac": achieved / fp8_peak,
             "traffic": None,
             "peak_source": f"2 x {peaks['source']} bf16 burst (no FP8 peak is recorded)",
