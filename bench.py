@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the B200 operator library.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--op moe|gqa_decode|mla_decode]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--op moe|gqa_decode|mla_decode] [--ops-only LIST]
                     [--impl ours|reference] [--no-ops-table]
 
 Headline (default ``--op moe``): FP8 block-scale MoE tokens/s at 8192 tokens per GPU, 32 local
@@ -225,7 +225,7 @@ def moe_stage_times(a, calls):
 # ---------------------------------------------------------------------------------------------
 # per-operator table (1 GPU)
 # ---------------------------------------------------------------------------------------------
-def ops_table(peaks, calls=15):
+def ops_table(peaks, calls=15, only=None):
     from ako4x_b200 import (dsa_attention, dsa_indexer, gqa_decode, mla_decode, mla_prefill, moe,
                             rmsnorm, workloads as W)
     hbm = peaks["hbm_gbs"] * 1e9
@@ -327,7 +327,8 @@ def ops_table(peaks, calls=15):
 
     for name, f in (("rmsnorm", _rms), ("gqa_decode", _gqa), ("mla_decode", _mla), ("mla_prefill", _prefill),
                     ("dsa", _dsa), ("moe_fp8", _moe)):
-        guarded(name, f)
+        if only is None or name in only:
+            guarded(name, f)
     return rows
 
 
@@ -541,6 +542,10 @@ def main():
     ap.add_argument("--tokens", type=int, default=MOE_TOKENS,
                     help="MoE tokens per GPU (default: the benchmark configuration, 8192)")
     ap.add_argument("--no-ops-table", action="store_true")
+    ap.add_argument("--ops-only", default=None,
+                    help="comma list of rmsnorm,gqa_decode,mla_decode,mla_prefill,dsa,moe_fp8: time only these "
+                         "operators (cold L2) and print their table; used for per-kernel profiles")
+    ap.add_argument("--calls", type=int, default=15, help="timed calls per operator row of the table")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
 
@@ -565,6 +570,11 @@ def main():
     from ako4x_b200 import _cabi
     _cabi.lib()  # fail loudly when the CUDA library is missing
 
+    if args.ops_only:
+        if world != 1:
+            raise SystemExit("--ops-only is a single-GPU mode")
+        print(json.dumps({"ops": ops_table(peaks, calls=args.calls, only=set(args.ops_only.split(",")))}), flush=True)
+        return
     if args.op == "moe":
         line = run_moe(args, rank, world, dist_on, peaks)
     else:
