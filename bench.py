@@ -111,11 +111,15 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
-def time_steps(fn, steps, warmup, dist_on):
-    """W warm-ups, then K steps between two CUDA events on the current stream; max over ranks."""
+def time_steps(fn, steps, warmup, dist_on, finish=None):
+    """W warm-ups, then K steps between two CUDA events on the current stream; max over ranks.
+    `finish` (optional) runs before the closing event: a step that uses side streams joins them to
+    the current stream there, so the event covers all of its work."""
     import torch.distributed as dist
     for _ in range(warmup):
         fn()
+    if finish:
+        finish()
     torch.cuda.synchronize()
     if dist_on:
         dist.barrier()
@@ -124,6 +128,8 @@ def time_steps(fn, steps, warmup, dist_on):
     e0.record()
     for _ in range(steps):
         fn()
+    if finish:
+        finish()
     e1.record()
     torch.cuda.synchronize()
     if dist_on:
@@ -417,27 +423,56 @@ def run_moe(args, rank, world, dist_on, peaks):
     value = total_pairs / 8.0 * args.steps / (ms * 1e-3)
     tokens_in_flight = world * T * args.steps / (ms * 1e-3)
 
-    # end to end: pinned host inputs -> device, run, result -> pinned host
+    # end to end: pinned host inputs -> device, run, result -> pinned host, EVERY step. On one GPU
+    # the three legs of consecutive steps overlap (copy-in stream, compute stream, copy-out stream,
+    # double-buffered device inputs and host outputs): the serving pattern for a stream of batches.
     h_in = {k: pinned(a[k]) for k in ("routing_logits", "hidden_states", "hidden_states_scale")}
-    d_in = {k: torch.empty_like(a[k]) for k in h_in}
-    h_out = torch.empty((T, 7168), dtype=torch.bfloat16, pin_memory=True)
+    d_in = [{k: torch.empty_like(a[k]) for k in h_in} for _ in range(2)]
+    h_out = [torch.empty((T, 7168), dtype=torch.bfloat16, pin_memory=True) for _ in range(2)]
+    s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+    ev_in = [torch.cuda.Event() for _ in range(2)]
+    ev_run = [torch.cuda.Event() for _ in range(2)]
+    ev_out = [torch.cuda.Event() for _ in range(2)]
+    counter = [0]
 
     def e2e_step():
-        for k in h_in:
-            d_in[k].copy_(h_in[k], non_blocking=True)
-        b = dict(a)
-        b.update(d_in)
-        if world > 1:
+        j = counter[0] & 1
+        counter[0] += 1
+        cur = torch.cuda.current_stream()
+        if world > 1:  # the expert-parallel step synchronises with the host: legs stay in order
+            for k in h_in:
+                d_in[j][k].copy_(h_in[k], non_blocking=True)
+            b = dict(a)
+            b.update(d_in[j])
             o = ep.run(b["routing_logits"], b["routing_bias"], b["hidden_states"], b["hidden_states_scale"],
                        b["gemm1_weights"], b["gemm1_weights_scale"], b["gemm2_weights"],
                        b["gemm2_weights_scale"], b["routed_scaling_factor"])
-        else:
-            o = moe.run(*[b[k] for k in MOE_KEYS])
-        h_out.copy_(o, non_blocking=True)
+            h_out[j].copy_(o, non_blocking=True)
+            return
+        s_in.wait_event(ev_run[j])          # the step two back has consumed this input buffer
+        with torch.cuda.stream(s_in):
+            for k in h_in:
+                d_in[j][k].copy_(h_in[k], non_blocking=True)
+            ev_in[j].record(s_in)
+        cur.wait_event(ev_in[j])
+        b = dict(a)
+        b.update(d_in[j])
+        o = moe.run(*[b[k] for k in MOE_KEYS])
+        ev_run[j].record(cur)
+        s_out.wait_event(ev_run[j])
+        s_out.wait_event(ev_out[j])         # (ordering on s_out already implies it)
+        with torch.cuda.stream(s_out):
+            h_out[j].copy_(o, non_blocking=True)
+            ev_out[j].record(s_out)
+        o.record_stream(s_out)
 
-    e2e_ms = time_steps(e2e_step, args.steps, min(args.warmup, 3), dist_on)
+    def e2e_finish():
+        torch.cuda.current_stream().wait_stream(s_in)
+        torch.cuda.current_stream().wait_stream(s_out)
+
+    e2e_ms = time_steps(e2e_step, args.steps, min(args.warmup, 3), dist_on, finish=e2e_finish)
     h2d = sum(v.numel() * v.element_size() for v in h_in.values())
-    d2h = h_out.numel() * h_out.element_size()
+    d2h = h_out[0].numel() * h_out[0].element_size()
     e2e_value = total_pairs / 8.0 * args.steps / (e2e_ms * 1e-3)
 
     line = {
@@ -464,7 +499,10 @@ def run_moe(args, rank, world, dist_on, peaks):
         line["roofline"] = {
             "bound": "tensor", "kernel": "moe_gemm_tc_kernel<1> (GEMM1 + SwiGLU + two-piece e4m3 h)",
             "achieved": achieved, "peak": fp8_peak, "unit": "TFLOP/s", "frac": achieved / fp8_peak,
-            "traffic": None,
+            # dram__bytes_read.sum + dram__bytes_write.sum of one GEMM1 launch at this workload, from
+            # the ncu capture summarised in profiles/moe_gemm_tc_T8192_launch_list_and_counters.md
+            "traffic": 1052370432 if T == MOE_TOKENS else None,
+            "traffic_unit": "bytes per launch (algorithmic: 939.5 MB of W13 + 58 MB activations + 66 MB h)",
             "peak_source": f"2 x {peaks['source']} bf16 burst (no FP8 peak is recorded)",
             "local_pairs": pairs,
             "stage_ms": {"route_scatter": st[0], "gemm1": st[1], "gemm2": st[2], "combine": st[3]},
