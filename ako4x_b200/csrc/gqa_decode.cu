@@ -248,6 +248,13 @@ int pick_splits(int64_t batch, int64_t num_kv_indices, int64_t page_size) {
   int64_t want = ako::cdiv(148 * 4 * CTAS_PER_SM, HEAD_GROUPS * batch);  // ~4 resident waves
   int64_t cap = avg_len / 128;                         // keep chunks >= 128 tokens on average
   if (cap < 1) cap = 1;
+  // A small batch leaves SMs idle at that grain and each CTA walks its chunk tile by tile, so the
+  // call's latency is the chunk length: go down to two 16-token tiles per CTA, up to one wave of CTAs.
+  if (HEAD_GROUPS * batch * cap < 148 * CTAS_PER_SM) {
+    const int64_t fine = avg_len / (2 * TILE) > 1 ? avg_len / (2 * TILE) : 1;
+    const int64_t one_wave = (148 * CTAS_PER_SM) / (HEAD_GROUPS * batch) > 1 ? (148 * CTAS_PER_SM) / (HEAD_GROUPS * batch) : 1;
+    cap = fine < one_wave ? fine : one_wave;
+  }
   int64_t s = want < cap ? want : cap;
   if (s < 1) s = 1;
   if (s > MAX_SPLITS) s = MAX_SPLITS;

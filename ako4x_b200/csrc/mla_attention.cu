@@ -372,6 +372,13 @@ int pick_splits(int64_t rows, int64_t avg_keys) {
   int64_t want = ako::cdiv(592, rows);       // ~4 waves of 148 single-CTA SMs
   int64_t cap = avg_keys / 128;               // at least two tiles per CTA on average
   if (cap < 1) cap = 1;
+  // Few rows leave SMs idle at that grain and the call's latency is the chunk length: one tile per CTA,
+  // up to one wave of CTAs.
+  if (rows * cap < 148) {
+    const int64_t fine = avg_keys / TILE > 1 ? avg_keys / TILE : 1;
+    const int64_t one_wave = 148 / rows > 1 ? 148 / rows : 1;
+    cap = fine < one_wave ? fine : one_wave;
+  }
   int64_t s = want < cap ? want : cap;
   if (s < 1) s = 1;
   if (s > MAX_SPLITS) s = MAX_SPLITS;
