@@ -45,8 +45,10 @@ __device__ __forceinline__ int sel_slot(int f) { return f ^ ((f >> 3) & 7); }
 
 // Fills the chunk's keys; tokens at or past `sl` get key 0 (below every finite score).
 __device__ __forceinline__ void sel_fill(uint4* skeys, const float* __restrict__ s, int chunk, int sl, int tid) {
+  const int nslots = (min(sl - chunk * SEL_CHUNK, SEL_CHUNK) + 3) >> 2;  // slots that hold a token
 #pragma unroll
   for (int it = 0; it < SEL_PER / 4; ++it) {
+    if (it * SEL_THREADS >= nslots) break;  // short rows: the passes below stop at the same slot
     const int f = it * SEL_THREADS + tid;
     const int i = chunk * SEL_CHUNK + 4 * f;  // a row is a whole number of 64-token pages: no overrun
     uint4 k = make_uint4(0u, 0u, 0u, 0u);
@@ -99,9 +101,10 @@ __device__ __forceinline__ void sel_count(int* hist, uint32_t key, uint32_t pref
 }
 
 template <int PASS>
-__device__ __forceinline__ void sel_pass(int* hist, const uint4* skeys, uint32_t prefix, int tid, int lane) {
+__device__ __forceinline__ void sel_pass(int* hist, const uint4* skeys, uint32_t prefix, int tid, int lane, int nslots) {
 #pragma unroll
   for (int it = 0; it < SEL_PER / 4; ++it) {
+    if (it * SEL_THREADS >= nslots) break;  // whole-block decision: the slots past the row were never filled
     const uint4 k = skeys[it * SEL_THREADS + tid];  // histogram: any order will do
     sel_count<PASS>(hist, k.x, prefix, lane);
     sel_count<PASS>(hist, k.y, prefix, lane);
@@ -157,9 +160,10 @@ __global__ void __launch_bounds__(SEL_THREADS, 1) dsa_select_kernel(
         sel_fill(skeys, s, c, sl, tid);
         __syncthreads();
       }
-      if (pass == 0) sel_pass<0>(hist, skeys, prefix, tid, lane);
-      else if (pass == 1) sel_pass<1>(hist, skeys, prefix, tid, lane);
-      else sel_pass<2>(hist, skeys, prefix, tid, lane);
+      const int nslots = (min(sl - c * SEL_CHUNK, SEL_CHUNK) + 3) >> 2;
+      if (pass == 0) sel_pass<0>(hist, skeys, prefix, tid, lane, nslots);
+      else if (pass == 1) sel_pass<1>(hist, skeys, prefix, tid, lane, nslots);
+      else sel_pass<2>(hist, skeys, prefix, tid, lane, nslots);
     }
     __syncthreads();
     // thread t owns bins 2t and 2t+1; suffix sums give count(digit >= bin)
