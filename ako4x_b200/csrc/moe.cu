@@ -20,12 +20,11 @@
 // The grouped GEMM (moe_gemm_tc.cuh) is persistent: each CTA walks a tile list (expert, n-tile,
 // m-tile) derived from the per-expert counts; tiles are 128 rows x 256 weight rows, K steps of 128
 // (one scale block) fed by TMA and multiplied by tcgen05.mma into TMEM accumulators.
-#include <cuda.h>  // CUtensorMap and its enums (types only; the encoder is fetched at run time)
-
 #include <cstdlib>
 
 #include "common.cuh"
 #include "tcgen05.cuh"
+#include "tma_host.cuh"
 
 namespace {
 
@@ -291,37 +290,6 @@ __global__ void __launch_bounds__(256) moe_permute_kernel(
   for (int kb = lane; kb < KB1; kb += 32) xs_scale[(int64_t)kb * cap + pos] = x_scale[(int64_t)kb * tokens + t];
 }
 
-// ---- TMA descriptors (host) ---------------------------------------------------------------------
-typedef CUresult (*TensorMapEncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
-                                           const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
-                                           const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                           CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-TensorMapEncodeTiledFn tensor_map_encoder() {
-  static TensorMapEncodeTiledFn fn = [] {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
-        q != cudaDriverEntryPointSuccess)
-      return (TensorMapEncodeTiledFn) nullptr;
-    return (TensorMapEncodeTiledFn)p;
-  }();
-  return fn;
-}
-
-// Byte matrix [rows, row_bytes] (row-major), box = 128 bytes x box_rows, 128-byte swizzle.
-bool make_byte_matrix_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t row_bytes, uint32_t box_rows) {
-  TensorMapEncodeTiledFn enc = tensor_map_encoder();
-  if (!enc) return false;
-  const cuuint64_t dims[2] = {row_bytes, rows};
-  const cuuint64_t strides[1] = {row_bytes};
-  const cuuint32_t box[2] = {128u, box_rows};
-  const cuuint32_t estr[2] = {1u, 1u};
-  return enc(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
-             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
 // The tcgen05 / TMEM form of the grouped GEMM (same GemmParams, same tile-list convention).
 #include "moe_gemm_tc.cuh"
 
@@ -390,10 +358,10 @@ int launch_gemms_tc(const GemmParams& p1, const GemmParams& p2, int64_t cap, int
   if (!ako::ensure_dynamic_smem<moe_gemm_tc_kernel<1>>(TC_SMEM)) return AKO4X_ELAUNCH;
   if (!ako::ensure_dynamic_smem<moe_gemm_tc_kernel<2>>(TC_SMEM)) return AKO4X_ELAUNCH;
   CUtensorMap a1, b1, a2, b2;
-  if (!make_byte_matrix_map(&a1, p1.a, (uint64_t)cap, HID, TC_BM) ||
-      !make_byte_matrix_map(&b1, p1.w, (uint64_t)n_local * 2 * INTER, HID, 64) ||
-      !make_byte_matrix_map(&a2, p2.a, (uint64_t)cap, 2 * INTER, TC_BM) ||
-      !make_byte_matrix_map(&b2, p2.w, (uint64_t)n_local * HID, INTER, TC_BN))
+  if (!ako::tma::byte_matrix_map(&a1, p1.a, (uint64_t)cap, HID, TC_BM) ||
+      !ako::tma::byte_matrix_map(&b1, p1.w, (uint64_t)n_local * 2 * INTER, HID, 64) ||
+      !ako::tma::byte_matrix_map(&a2, p2.a, (uint64_t)cap, 2 * INTER, TC_BM) ||
+      !ako::tma::byte_matrix_map(&b2, p2.w, (uint64_t)n_local * HID, INTER, TC_BN))
     return AKO4X_ELAUNCH;
   moe_gemm_tc_kernel<1><<<sms, TC_THREADS, TC_SMEM, st>>>(p1, a1, b1);
   AKO_CHECK_LAUNCH();

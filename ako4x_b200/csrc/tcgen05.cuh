@@ -19,17 +19,6 @@ __device__ __forceinline__ void mbar_init_fence() {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n.reg .pred p;\n"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-      "selp.u32 %0, 1, 0, p;\n}\n"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
 // Non-blocking test of the phase: returns at once. A waiter polling with this wakes within a few
 // tens of cycles of the completion; try_wait may leave it suspended far longer.
 __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
@@ -43,24 +32,11 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// The same test, letting the hardware keep the thread suspended for up to `ns` nanoseconds while
-// the phase is incomplete: a waiting warp then leaves its scheduler's issue slots to the others.
-__device__ __forceinline__ bool mbar_try_wait_suspend(uint32_t bar, uint32_t parity, uint32_t ns) {
-  uint32_t ok;
-  asm volatile(
-      "{\n.reg .pred p;\n"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
-      "selp.u32 %0, 1, 0, p;\n}\n"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity), "r"(ns)
-      : "memory");
-  return ok != 0;
-}
 // Waits for the phase with the given parity. Returns false when `*err` is already set or when the
 // cycle budget runs out (then `*err` is set to `code`); the caller must unwind, not retry.
 constexpr long long kWaitBudgetCycles = 400000000LL;  // ~0.2 s at 1.9 GHz
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* err, int code) {
-  if (mbar_try_wait(bar, parity)) return true;
+  if (mbar_test_wait(bar, parity)) return true;
   const long long t0 = clock64();
   uint32_t spins = 0;
   while (true) {
@@ -133,30 +109,17 @@ __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
 }
 
 // ---- descriptors -----------------------------------------------------------------------------
-// K-major operand tile in shared memory: rows of 128 bytes, 8-row groups contiguous (1024 B), the
-// 16-byte chunks of a row XOR-swizzled with (row & 7) -- the 128-byte swizzle. `saddr` is the
-// shared-memory byte address of the tile (1024-byte aligned) plus the byte offset of the K slice.
-__device__ __forceinline__ uint64_t smem_desc_k_sw128(uint32_t saddr) {
-  const uint32_t lo = ((saddr >> 4) & 0x3FFFu) | (1u << 16);          // start address, LBO = 1
-  const uint32_t hi = (1024u >> 4) | (1u << 14) | (2u << 29);          // SBO, version 1, SWIZZLE_128B
-  return (static_cast<uint64_t>(hi) << 32) | lo;
-}
 // Instruction descriptor: D fp32, A and B e4m3, both K-major, dense, M x N tile.
 __host__ __device__ constexpr uint32_t idesc_e4m3_f32(int m, int n) {
   return (1u << 4) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
 }
 
-// D[tmem] (+)= A[smem] * B[smem]^T, one K = 32 slice of e4m3. Issued by ONE thread.
-__device__ __forceinline__ void mma_f8(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
-                                       uint32_t accumulate) {
-  asm volatile(
-      "{\n.reg .pred p;\n"
-      "setp.ne.b32 p, %4, 0;\n"
-      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n}\n" ::"r"(d_tmem),
-      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// The same MMA with the two descriptors given as halves: both K-major SW128 tiles share the high
+// K-major operand tiles in shared memory: rows of 128 bytes, 8-row groups contiguous (1024 B), the
+// 16-byte chunks of a row XOR-swizzled with (row & 7) -- the 128-byte swizzle TMA writes. The
+// 64-bit descriptor = low word (start address >> 4 in bits 0-13, LBO = 1 in bits 16-29) and high
+// word (SBO = 1024 >> 4, version 1 at bit 14, SWIZZLE_128B = 2 at bits 29-31).
+// D[tmem] (+)= A[smem] * B[smem]^T, one K = 32 slice of e4m3, issued by ONE thread, with the two
+// descriptors given as halves: both tiles share the high
 // word, and the low word (start address >> 4, LBO) advances by plain 32-bit adds -- 2 per K = 32
 // slice, bytes >> 4 per tile. The issuing thread is a single dependent instruction stream, so every
 // instruction saved between two MMAs shortens the gap in which the tensor pipe may drain.
@@ -197,12 +160,8 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
         "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr));
 }
-__device__ __forceinline__ void tmem_ld_wait() {
-  asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-}
-
-// The same wait, naming the destination registers of the load it completes, so that the compiler
-// cannot schedule a use of them above it.
+// Waits for this thread's tcgen05.ld; it names the destination registers of the load it completes,
+// so that the compiler cannot schedule a use of them above it.
 __device__ __forceinline__ void tmem_ld_wait_regs(float (&v)[32]) {
   uint32_t* r = reinterpret_cast<uint32_t*>(v);
   asm volatile(
@@ -216,18 +175,6 @@ __device__ __forceinline__ void tmem_ld_wait_regs(float (&v)[32]) {
       : "memory");
 }
 
-// Two fp32 FMAs in one instruction (sm_100 packed fp32): a0 += v0*s, a1 += v1*s.
-__device__ __forceinline__ void fma2(float& a0, float& a1, float v0, float v1, float s) {
-  asm("{\n.reg .b64 ra, rv, rs;\n"
-      "mov.b64 ra, {%0, %1};\n"
-      "mov.b64 rv, {%2, %3};\n"
-      "mov.b64 rs, {%4, %4};\n"
-      "fma.rn.f32x2 ra, rv, rs, ra;\n"
-      "mov.b64 {%0, %1}, ra;\n}\n"
-      : "+f"(a0), "+f"(a1)
-      : "f"(v0), "f"(v1), "f"(s));
-}
-
 // ---- register re-balancing between warp groups ---------------------------------------------------
 template <int N>
 __device__ __forceinline__ void reg_dec() {
@@ -236,10 +183,6 @@ __device__ __forceinline__ void reg_dec() {
 template <int N>
 __device__ __forceinline__ void reg_inc() {
   asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;\n" ::"n"(N));
-}
-
-__device__ __forceinline__ void named_barrier(int id, int threads) {
-  asm volatile("bar.sync %0, %1;\n" ::"r"(id), "r"(threads) : "memory");
 }
 
 }  // namespace tc
