@@ -19,6 +19,7 @@
 // mbarriers are bounded: a wait that runs out of budget records a code in a device status word
 // and the CTA stops consuming.
 #include "lse_merge.cuh"
+#include "mla_prefill_tc.h"
 #include "tcgen05.cuh"
 
 namespace {
@@ -497,8 +498,8 @@ extern "C" int ako4x_dsa_sparse_attention(const void* q_nope, const void* q_pe, 
 // ---- causal paged MLA prefill --------------------------------------------------------------------
 extern "C" size_t ako4x_mla_paged_prefill_workspace_bytes(int64_t total_q, int64_t batch,
                                                           int64_t num_kv_indices, int64_t page_size) {
-  (void)total_q; (void)batch; (void)num_kv_indices; (void)page_size;
-  return 0;
+  (void)total_q;
+  return ako_mla_prefill_tc_workspace_bytes(batch, num_kv_indices, page_size);
 }
 
 extern "C" int ako4x_mla_paged_prefill(const void* q_nope, const void* q_pe, const void* ckv_cache,
@@ -507,7 +508,6 @@ extern "C" int ako4x_mla_paged_prefill(const void* q_nope, const void* q_pe, con
                                        float sm_scale, void* o, float* lse, int64_t total_q,
                                        int64_t batch, int64_t num_kv_indices, int64_t page_size,
                                        void* workspace, size_t workspace_bytes, void* stream) {
-  (void)workspace; (void)workspace_bytes;
   if (total_q < 0 || batch < 0 || num_kv_indices < 0 || page_size < 1) return AKO4X_EINVAL;
   if (total_q == 0) return AKO4X_OK;
   if (batch == 0) return AKO4X_EINVAL;
@@ -515,6 +515,10 @@ extern "C" int ako4x_mla_paged_prefill(const void* q_nope, const void* q_pe, con
     return AKO4X_EINVAL;
   if (num_kv_indices > 0 && !kv_indices) return AKO4X_EINVAL;
   if (misaligned(q_nope, q_pe, ckv_cache, kpe_cache, o)) return AKO4X_EINVAL;
+  if (num_kv_indices > 0)  // tensor-core path (mla_prefill_tc.cu); without keys the rows are empty
+    return ako_mla_prefill_tc_launch(q_nope, q_pe, ckv_cache, kpe_cache, qo_indptr, kv_indptr, kv_indices,
+                                     sm_scale, o, lse, total_q, batch, num_kv_indices, page_size, workspace,
+                                     workspace_bytes, (cudaStream_t)stream);
   Params p = {};
   fill_common(p, q_nope, q_pe, ckv_cache, kpe_cache, o, lse, sm_scale);
   p.qo_indptr = qo_indptr;
@@ -530,5 +534,6 @@ extern "C" int ako4x_mla_paged_prefill(const void* q_nope, const void* q_pe, con
 extern "C" int ako4x_mla_attention_device_status(void) {
   int v = 0;
   if (cudaMemcpyFromSymbol(&v, g_mla_status, sizeof(int)) != cudaSuccess) return AKO4X_ELAUNCH;
+  if (v == 0) v = ako_mla_prefill_tc_status();
   return v;
 }

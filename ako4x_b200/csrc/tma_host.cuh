@@ -39,6 +39,21 @@ inline bool byte_matrix_map(CUtensorMap* m, const void* base, uint64_t rows, uin
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// bf16 matrix [rows, cols] with a row stride in bytes; box = 64 columns (128 bytes) x box_rows;
+// 128-byte swizzle: the K-major operand layout of tcgen05.mma.
+inline bool bf16_matrix_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols,
+                            uint64_t row_stride_bytes, uint32_t box_rows) {
+  EncodeTiledFn enc = encoder();
+  if (!enc) return false;
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {row_stride_bytes};
+  const cuuint32_t box[2] = {64u, box_rows};
+  const cuuint32_t estr[2] = {1u, 1u};
+  return enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 // Paged byte matrices: `pages` pages of `page_stride` bytes, each starting with [rows, 128] bytes;
 // box = one page's 128 x rows block; 128-byte swizzle.
 inline bool paged_byte_matrix_map(CUtensorMap* m, const void* base, uint64_t pages, uint64_t page_stride,
