@@ -43,6 +43,7 @@ constexpr int MAX_SPLITS = 64;
 __device__ int g_mla_status = 0;  // 0 = ok; set when a bounded wait gave up
 
 enum Mode { kDecode = 0, kSparse = 1, kPrefill = 2 };
+constexpr int64_t kPrefillTcMinQueries = 48;
 
 struct Params {
   const __nv_bfloat16* q_nope;
@@ -498,7 +499,7 @@ extern "C" int ako4x_dsa_sparse_attention(const void* q_nope, const void* q_pe, 
 // ---- causal paged MLA prefill --------------------------------------------------------------------
 extern "C" size_t ako4x_mla_paged_prefill_workspace_bytes(int64_t total_q, int64_t batch,
                                                           int64_t num_kv_indices, int64_t page_size) {
-  (void)total_q;
+  if (total_q < kPrefillTcMinQueries) return 0;
   return ako_mla_prefill_tc_workspace_bytes(batch, num_kv_indices, page_size);
 }
 
@@ -515,7 +516,10 @@ extern "C" int ako4x_mla_paged_prefill(const void* q_nope, const void* q_pe, con
     return AKO4X_EINVAL;
   if (num_kv_indices > 0 && !kv_indices) return AKO4X_EINVAL;
   if (misaligned(q_nope, q_pe, ckv_cache, kpe_cache, o)) return AKO4X_EINVAL;
-  if (num_kv_indices > 0)  // tensor-core path (mla_prefill_tc.cu); without keys the rows are empty
+  // From a few query tiles on, the tensor-core path (mla_prefill_tc.cu): 4x faster at the benchmark
+  // shape. Below that its fixed cost (gather of all keys, two launches) outweighs it and the
+  // one-query-token-per-CTA kernel below answers in a third of the time.
+  if (num_kv_indices > 0 && total_q >= kPrefillTcMinQueries)
     return ako_mla_prefill_tc_launch(q_nope, q_pe, ckv_cache, kpe_cache, qo_indptr, kv_indptr, kv_indices,
                                      sm_scale, o, lse, total_q, batch, num_kv_indices, page_size, workspace,
                                      workspace_bytes, (cudaStream_t)stream);

@@ -7,6 +7,15 @@ from ako4x_b200 import dsa_attention, mla_decode, mla_prefill, workloads as W
 from conftest import assert_close_bf16, assert_lse_close, load_golden
 
 pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(autouse=True)
+def _status_clean(built_lib):
+    """No bounded wait of the attention kernels may have given up, before or after a test."""
+    from ako4x_b200 import _cabi
+    assert _cabi.lib().ako4x_mla_attention_device_status() == 0
+    yield
+    assert _cabi.lib().ako4x_mla_attention_device_status() == 0
 DKEYS = ["q_nope", "q_pe", "ckv_cache", "kpe_cache", "kv_indptr", "kv_indices", "sm_scale"]
 PKEYS = ["q_nope", "q_pe", "ckv_cache", "kpe_cache", "qo_indptr", "kv_indptr", "kv_indices", "sm_scale"]
 SKEYS = ["q_nope", "q_pe", "ckv_cache", "kpe_cache", "sparse_indices", "sm_scale"]
@@ -57,6 +66,16 @@ def test_prefill_ragged(built_lib, q_lens, kv_lens):
     _check(mla_prefill, oracle.mla_paged_prefill, PKEYS,
            W.make_mla_prefill(len(q_lens), shape_id=sum(kv_lens) % 79, q_lens=q_lens, kv_lens=kv_lens,
                               extra_pages=9))
+
+
+@pytest.mark.parametrize("q_lens,kv_lens", [([48], [48]), ([50, 0, 7], [60, 0, 300]), ([200], [2000]),
+                                             ([9, 129, 8, 1], [500, 129, 8, 257])])
+def test_prefill_tensor_core_path(built_lib, q_lens, kv_lens):
+    """48 query tokens and more take the tcgen05 kernel: partial query tiles, empty sequences,
+    kv_len == q_len, key tiles that straddle the causal limit."""
+    _check(mla_prefill, oracle.mla_paged_prefill, PKEYS,
+           W.make_mla_prefill(len(q_lens), shape_id=sum(kv_lens) % 83, q_lens=q_lens, kv_lens=kv_lens,
+                              extra_pages=17))
 
 
 def test_prefill_config_shape_reduced(built_lib):
