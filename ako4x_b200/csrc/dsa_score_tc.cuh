@@ -2,54 +2,54 @@
 // dsa_indexer.cu inside its anonymous namespace.
 //
 // score[r, t] = (sum_h w[r,h] * relu(q[r,h,:] . k[t,:])) * kscale[t]. Tokens are the M dimension of
-// the MMA (128 tokens = two 64-token cache pages), the 64 heads of up to FOUR query rows the N
-// dimension (N = 256), K = 128 e4m3 values (four tcgen05.mma K32 steps). With tokens on the TMEM
-// lanes, relu, the head weights and the head reduction are plain per-thread arithmetic on the
-// accumulator columns: no shuffles. That arithmetic (two CUDA-core instructions per accumulator
-// element) costs about as much as the MMA, so it gets sixteen warps.
+// the MMA (128 tokens = two 64-token cache pages), the 64 heads of up to EIGHT query rows the N
+// dimension (N = 512 = all of TMEM, as four accumulators of 128 columns = two rows each), K = 128
+// e4m3 values (four tcgen05.mma K32 steps). With tokens on the TMEM lanes, relu, the head weights
+// and the head reduction are plain per-thread arithmetic on the accumulator columns: no shuffles.
+// That arithmetic (two CUDA-core instructions per accumulator element) costs about as much as the
+// MMA, so it gets sixteen warps.
 //
-// A unit of work is (group of 4 consecutive query rows, pair of logical pages). When the four rows
-// map that page pair to the same physical pages (consecutive tokens of one sequence, the prefill
-// case) the key tile is loaded once and one N = 256 MMA sequence serves all four rows; otherwise
-// the unit runs as four N = 64 sequences, one key tile each, into the four column blocks of the
-// same accumulator. A persistent CTA takes a contiguous range of units, so the 32 KB query tile of
-// a row group stays in shared memory while the CTA sweeps pages.
-//   warp 18     producer. Describe step: each lane reads the block table and sequence lengths of
-//               one of the next 32 units and writes one record per key tile into shared memory.
-//               Issue step: up to six lanes at a time take one record each and issue its copies
-//               (key tile: 6-stage ring, a page is a [64 x 128 B] box of a 3-D tensor map over the
-//               8448-byte pages; per unit a slot of a 16-deep ring that carries the key scales and
-//               the unit's descriptor, so that no other warp touches the block table; query tile
-//               + head weights per row group: 2 buffers). A record that starts a row group always
+// A unit of work is (group of 8 consecutive query rows, pair of logical pages). When the rows map
+// that page pair to the same physical pages (consecutive tokens of one sequence, the prefill case)
+// the key tile is loaded ONCE for all eight rows -- every key byte brought into shared memory feeds
+// 8 x 64 dot products -- and runs as four N = 128 MMA sequences; otherwise the unit runs as eight
+// N = 64 sequences, one key tile each. A persistent CTA takes a contiguous range of units, so the
+// 64 KB query tile of a row group stays in shared memory while the CTA sweeps pages (one buffer: a
+// group is ~256 units, the refill bubble is small).
+//   warp 20     producer. Describe step: each of 16 lanes reads the block table and sequence
+//               lengths of one of the next 16 units and writes one record per key tile into shared
+//               memory. Issue step: up to six lanes at a time take one record each and issue its
+//               copies (key tile: 6-stage ring, a page is a [64 x 128 B] box of a 3-D tensor map
+//               over the 8448-byte pages; per unit a slot of an 8-deep ring that carries the key
+//               scales and the unit's descriptor, so that no other warp touches the block table;
+//               query tile + head weights per row group). A record that starts a row group always
 //               opens an issue step, so every wait of a step depends only on earlier steps;
 //   warps 16-19 MMA issuers, one thread each; warps 0-15 epilogue, four teams of four warps.
-//               TMEM holds four accumulators of 128 columns (two query rows each). Accumulator
-//               a = 2*(unit parity) + (row half) has its own issuer and its own team: the issuer
-//               runs the N = 128 MMAs of its row half for every second unit, the team reads the
-//               result (thread (w, l): token 32*(w%4)+l, both rows). The chain MMA -> commit ->
-//               team's TMEM loads -> release -> next MMA is a few thousand cycles of latency per
-//               accumulator, several times the tensor pipe's time for the tile, and every step an
-//               issuer takes (barrier test, descriptor read, MMA, commit) costs 50-100 cycles;
-//               four independent chains keep the pipe and the CUDA cores busy.
+//               Accumulator a (rows 2a, 2a+1 of the group) has its own issuer and its own team: the
+//               issuer runs the N = 128 MMAs of its rows for every unit, the team reads the result
+//               (thread (w, l): token 32*(w%4)+l, both rows). The chain MMA -> commit -> team's
+//               TMEM loads -> release -> next MMA is about a thousand cycles of latency per
+//               accumulator (commit -> waiter ~300 cycles, arrive -> waiter ~170, every step of an
+//               issuer 50-100); four chains in flight cover the tensor pipe's time for a unit.
 // Every reader of TMA-written shared memory waits on the mbarrier the copy completes on. Every
 // wait is bounded; a timeout sets the status word and all roles unwind.
 
-constexpr int TS_ROWS = 4;                      // query rows per unit
-constexpr int TS_N = TS_ROWS * NH;              // 256 accumulator columns
+constexpr int TS_ROWS = 8;                      // query rows per unit
+constexpr int TS_N = TS_ROWS * NH;              // 512 accumulator columns
 constexpr int TS_A_BYTES = 2 * PS * HD;         // 16 KB: two pages of e4m3 keys
-constexpr int TS_Q_BYTES = TS_N * HD;           // 32 KB: four rows of e4m3 queries
-constexpr int TS_W_BYTES = TS_N * 4;            // 1 KB: their head weights
+constexpr int TS_Q_BYTES = TS_N * HD;           // 64 KB: eight rows of e4m3 queries
+constexpr int TS_W_BYTES = TS_N * 4;            // 2 KB: their head weights
 constexpr int TS_A_STAGES = 6;
-constexpr int TS_SLOTS = 16;                    // per-unit ring: key scales + descriptor
+constexpr int TS_SLOTS = 8;                     // per-unit ring: key scales + descriptor
 constexpr int TS_SCALE_BYTES = 2 * PS * 4;      // 128 key scales of one key tile
 constexpr int TS_SLOT_BYTES = TS_ROWS * TS_SCALE_BYTES + 64;
-constexpr int TS_DESCRIBE = 32;                 // units described per producer round (one per lane)
-constexpr int TS_RECS = TS_DESCRIBE * TS_ROWS + 2;
-constexpr int TS_REC_BYTES = 64;
-constexpr int TS_SMEM = 2 * TS_Q_BYTES + TS_A_STAGES * TS_A_BYTES + 2 * TS_W_BYTES + TS_SLOTS * TS_SLOT_BYTES +
+constexpr int TS_DESCRIBE = 16;                 // units described per producer round (one per lane)
+constexpr int TS_RECS = TS_DESCRIBE * TS_ROWS + 1;
+constexpr int TS_REC_BYTES = 80;
+constexpr int TS_SMEM = TS_Q_BYTES + TS_A_STAGES * TS_A_BYTES + TS_W_BYTES + TS_SLOTS * TS_SLOT_BYTES +
                         TS_RECS * TS_REC_BYTES + 1024;
 constexpr int TS_ACCS = 4;                      // accumulators = teams = issuers
-constexpr int TS_ACC_COLS = TS_N / 2;           // 128 columns: two query rows
+constexpr int TS_ACC_COLS = TS_N / TS_ACCS;     // 128 columns: two query rows
 constexpr int TS_TEAM_WARPS = 4;
 constexpr int TS_EPI_WARPS = TS_ACCS * TS_TEAM_WARPS;
 constexpr int TS_MMA_WARP = TS_EPI_WARPS, TS_PRODUCER_WARP = TS_EPI_WARPS + TS_ACCS;  // issuers: warps 16-19
@@ -73,12 +73,14 @@ struct ScoreDesc {
   int row0;           // first query row of the group
   int pp;             // page pair: logical pages 2*pp, 2*pp+1
   int flags;          // TS_F_*
-  int qc;             // ordinal of the row group inside this CTA (query buffer = qc & 1)
+  int qc;             // ordinal of the row group inside this CTA (phase of the query buffer)
   int sl[TS_ROWS];    // row's sequence length, or -1 when the row takes nothing from this unit
   int ac0;            // ordinal of the unit's first key tile inside this CTA (key stage = ordinal % stages)
   int pad[3];
 };
-constexpr int TS_F_SHARED = 1, TS_F_NEWGROUP = 2, TS_F_END = 4;
+// NEWGROUP: first unit of its row group in this CTA; LASTGROUP: last one (the query buffer is
+// handed back after it).
+constexpr int TS_F_SHARED = 1, TS_F_NEWGROUP = 2, TS_F_END = 4, TS_F_LASTGROUP = 8;
 
 // One key tile to load: the producer's describe step writes these, its issue step reads them.
 struct ScoreRec {
@@ -87,7 +89,7 @@ struct ScoreRec {
   int sub;            // which key tile of the unit (0 for a shared one, else the row)
   ScoreDesc d;
 };
-static_assert(sizeof(ScoreRec) == TS_REC_BYTES, "record size");
+static_assert(sizeof(ScoreDesc) == 64 && sizeof(ScoreRec) == TS_REC_BYTES, "record size");
 
 __device__ __forceinline__ int phys_page(const ScoreParams& p, int r, int lp) {
   r = min(r, p.rows - 1);
@@ -101,8 +103,7 @@ dsa_score_tc_kernel(ScoreParams p, const __grid_constant__ CUtensorMap tm_q, con
   extern __shared__ unsigned char smem_raw[];
   __shared__ __align__(8) uint64_t s_a_full[TS_A_STAGES];
   __shared__ __align__(8) uint64_t s_a_empty[TS_A_STAGES];
-  __shared__ __align__(8) uint64_t s_q_full[2];
-  __shared__ __align__(8) uint64_t s_q_empty[2];
+  __shared__ __align__(8) uint64_t s_q_full, s_q_empty;
   __shared__ __align__(8) uint64_t s_acc_full[TS_ACCS];
   __shared__ __align__(8) uint64_t s_acc_empty[TS_ACCS];
   __shared__ __align__(8) uint64_t s_slot_full[TS_SLOTS];
@@ -112,28 +113,26 @@ dsa_score_tc_kernel(ScoreParams p, const __grid_constant__ CUtensorMap tm_q, con
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   unsigned char* smem_al = smem_raw + ((1024u - (ako::smem_u32(smem_raw) & 1023u)) & 1023u);
   const uint32_t q_base = ako::smem_u32(smem_al);
-  const uint32_t a_base = q_base + 2 * TS_Q_BYTES;
-  unsigned char* w_ptr = smem_al + 2 * TS_Q_BYTES + TS_A_STAGES * TS_A_BYTES;
-  unsigned char* slot_ptr = w_ptr + 2 * TS_W_BYTES;
+  const uint32_t a_base = q_base + TS_Q_BYTES;
+  unsigned char* w_ptr = smem_al + TS_Q_BYTES + TS_A_STAGES * TS_A_BYTES;
+  unsigned char* slot_ptr = w_ptr + TS_W_BYTES;
   const uint32_t w_base = ako::smem_u32(w_ptr);
   const uint32_t slot_base = ako::smem_u32(slot_ptr);
 
   if (tid == 0) {
     for (int s = 0; s < TS_A_STAGES; ++s) {
       ako::tc::mbar_init(ako::smem_u32(&s_a_full[s]), 1);
-      ako::tc::mbar_init(ako::smem_u32(&s_a_empty[s]), 2);  // the two issuers of the unit's parity
+      ako::tc::mbar_init(ako::smem_u32(&s_a_empty[s]), TS_ACCS);  // every issuer passes every key tile
     }
-    for (int b = 0; b < 2; ++b) {
-      ako::tc::mbar_init(ako::smem_u32(&s_q_full[b]), 1);
-      ako::tc::mbar_init(ako::smem_u32(&s_q_empty[b]), TS_ACCS + TS_EPI_WARPS);   // every issuer + every epilogue warp
-    }
+    ako::tc::mbar_init(ako::smem_u32(&s_q_full), 1);
+    ako::tc::mbar_init(ako::smem_u32(&s_q_empty), TS_ACCS + TS_EPI_WARPS);   // every issuer + every epilogue warp
     for (int a = 0; a < TS_ACCS; ++a) {
       ako::tc::mbar_init(ako::smem_u32(&s_acc_full[a]), 1);
       ako::tc::mbar_init(ako::smem_u32(&s_acc_empty[a]), TS_TEAM_WARPS);
     }
     for (int s = 0; s < TS_SLOTS; ++s) {
       ako::tc::mbar_init(ako::smem_u32(&s_slot_full[s]), 1);
-      ako::tc::mbar_init(ako::smem_u32(&s_slot_empty[s]), 2 + 2 * TS_TEAM_WARPS);  // the unit's two issuers and two teams
+      ako::tc::mbar_init(ako::smem_u32(&s_slot_empty[s]), TS_ACCS + TS_EPI_WARPS);  // every issuer and warp reads every slot
     }
     ako::tc::mbar_init_fence();
   }
@@ -160,26 +159,28 @@ dsa_score_tc_kernel(ScoreParams p, const __grid_constant__ CUtensorMap tm_q, con
     int ac = 0, qc_base = 0, uo_base = 0;
     bool done = false;
     for (int ubase = u_begin; !done; ubase += TS_DESCRIBE) {
-      // ---- describe: lane l takes unit ubase + l. Two END records follow the last unit (one per
-      // epilogue team), in the first round that has two lanes to spare.
+      // ---- describe: lane l < 16 takes unit ubase + l; the END record follows the last unit in the
+      // first round that has a lane to spare.
       const int unit = ubase + lane;
       int nsubs = 0, flags = 0, row0 = 0, pp = 0;
       int pa[TS_ROWS], pb[TS_ROWS], sl[TS_ROWS];
 #pragma unroll
       for (int i = 0; i < TS_ROWS; ++i) { pa[i] = 0; pb[i] = 0; sl[i] = -1; }
       const int n_left = max(0, u_end - ubase);
-      const bool last_round = n_left <= TS_DESCRIBE - 2;
-      if (unit < u_end) {
+      const bool last_round = n_left <= TS_DESCRIBE - 1;
+      if (lane < TS_DESCRIBE && unit < u_end) {
         row0 = (unit / pairs) * TS_ROWS;
         pp = unit % pairs;
         bool any = false, shared = true;
-        int fa = 0, fb = 0;
+        int fa = 0, fb = 0, maxlim = 0;
 #pragma unroll
         for (int i = 0; i < TS_ROWS; ++i) {
           const int r = row0 + i;
           int s0 = (r < p.rows) ? __ldg(p.seq_lens + r) : 0;
           if (s0 <= 0 || (p.skip_short && s0 <= TOPK)) s0 = 0;
-          const bool need = 2 * pp * PS < min(s0, p.max_pages * PS);
+          const int lim = min(s0, p.max_pages * PS);
+          maxlim = max(maxlim, lim);
+          const bool need = 2 * pp * PS < lim;
           pa[i] = phys_page(p, r, 2 * pp);
           pb[i] = phys_page(p, r, 2 * pp + 1);
           if (need) {
@@ -191,14 +192,17 @@ dsa_score_tc_kernel(ScoreParams p, const __grid_constant__ CUtensorMap tm_q, con
         }
         if (any) {
           nsubs = shared ? 1 : TS_ROWS;
-          // a group's needed page pairs are a prefix, so its first unit in this CTA's range opens it
-          flags = (shared ? TS_F_SHARED : 0) | ((pp == 0 || unit == u_begin) ? TS_F_NEWGROUP : 0);
+          // A group's needed page pairs are a prefix [0, last_pp]: its first unit in this CTA's
+          // range opens it, and the unit at last_pp (or the end of the range) closes it.
+          const int last_pp = (maxlim - 1) / (2 * PS);
+          flags = (shared ? TS_F_SHARED : 0) | ((pp == 0 || unit == u_begin) ? TS_F_NEWGROUP : 0) |
+                  ((pp == last_pp || unit == u_end - 1) ? TS_F_LASTGROUP : 0);
           if (shared) {
 #pragma unroll
             for (int i = 0; i < TS_ROWS; ++i) { pa[i] = fa; pb[i] = fb; }
           }
         }
-      } else if (last_round && (lane == n_left || lane == n_left + 1)) {
+      } else if (last_round && lane == n_left) {
         nsubs = 1;
         flags = TS_F_END;
       }
@@ -253,16 +257,16 @@ dsa_score_tc_kernel(ScoreParams p, const __grid_constant__ CUtensorMap tm_q, con
           const int a = ac + lane;
           const int slot = rc.uo % TS_SLOTS, stage = a % TS_A_STAGES;
           if (rc.d.flags & TS_F_NEWGROUP) {
-            const int qb = rc.d.qc & 1;
-            ok = ako::tc::mbar_wait(ako::smem_u32(&s_q_empty[qb]), (uint32_t)(((rc.d.qc >> 1) & 1) ^ 1), &g_dsa_status, 1);
+            // one query buffer: group qc is loaded once everybody has handed back group qc-1
+            ok = ako::tc::mbar_wait(ako::smem_u32(&s_q_empty), (uint32_t)((rc.d.qc & 1) ^ 1), &g_dsa_status, 1);
             if (ok) {
-              const uint32_t bar = ako::smem_u32(&s_q_full[qb]);
+              const uint32_t bar = ako::smem_u32(&s_q_full);
               ako::tc::mbar_arrive_expect_tx(bar, TS_Q_BYTES + TS_W_BYTES);
 #pragma unroll
               for (int i = 0; i < TS_ROWS; ++i) {
                 const int r = min(rc.d.row0 + i, p.rows - 1);
-                ako::tc::tma_load_2d(q_base + qb * TS_Q_BYTES + i * NH * HD, &tm_q, 0, r * NH, bar);
-                ako::tc::bulk_load_1d(w_base + qb * TS_W_BYTES + i * NH * 4, p.weights + (int64_t)r * NH, NH * 4, bar);
+                ako::tc::tma_load_2d(q_base + i * NH * HD, &tm_q, 0, r * NH, bar);
+                ako::tc::bulk_load_1d(w_base + i * NH * 4, p.weights + (int64_t)r * NH, NH * 4, bar);
               }
             }
           }
@@ -303,54 +307,50 @@ dsa_score_tc_kernel(ScoreParams p, const __grid_constant__ CUtensorMap tm_q, con
     if (lane == 0) {
       constexpr uint32_t IDESC_SHARED = ako::tc::idesc_e4m3_f32(128, TS_ACC_COLS);
       constexpr uint32_t IDESC_ROW = ako::tc::idesc_e4m3_f32(128, NH);
-      // a_lo, b_lo: descriptor low words; mma: this issuer's row half takes part in the tile
-      struct Tile { uint32_t a_lo, b_lo, d, idesc; int stage, acc_wait; bool last, mma; };
-      const int me = warp - TS_MMA_WARP;    // accumulator
-      const int par = me >> 1, rh = me & 1; // parity of the units taken; row half
-      const uint32_t a_lo0 = ako::tc::smem_desc_lo(a_base), q_lo0 = ako::tc::smem_desc_lo(q_base);
+      // a_lo, b_lo: descriptor low words; mma: this issuer's rows take part in the tile;
+      // q_done: the tile is the unit's last and the unit the group's last
+      struct Tile { uint32_t a_lo, b_lo, d, idesc; int stage, acc_wait; bool last, mma, q_done; };
+      const int me = warp - TS_MMA_WARP;    // accumulator = row pair (rows 2*me, 2*me+1 of the group)
+      const uint32_t a_lo0 = ako::tc::smem_desc_lo(a_base);
+      const uint32_t q_lo = ako::tc::smem_desc_lo(q_base) + me * ((2 * NH * HD) >> 4);  // this pair's rows
       const uint32_t acc = tmem_base + me * TS_ACC_COLS;
       int n = 0;                            // units taken so far
       int ac = 0, subs = 0, sub = 0;        // current unit: next key tile ordinal, tiles, tiles issued
-      bool shared = true;
-      uint32_t q_lo = q_lo0;
-      int q_cur = -1, q_rel = 0, q_rel_to = 0;  // group in use; groups released; groups to release
+      bool shared = true, last_unit = false;
       int acc_wait = 1;
       // 1: tile ready, 0: END record, -1: a wait gave up
       auto prepare = [&](Tile& t) -> int {
         if (sub == subs) {  // next unit
-          const int uo = 2 * n + par;
-          const int slot = uo % TS_SLOTS;
-          if (!ako::tc::mbar_wait(ako::smem_u32(&s_slot_full[slot]), (uint32_t)((uo / TS_SLOTS) & 1), &g_dsa_status, 4)) return -1;
+          const int slot = n % TS_SLOTS;
+          if (!ako::tc::mbar_wait(ako::smem_u32(&s_slot_full[slot]), (uint32_t)((n / TS_SLOTS) & 1), &g_dsa_status, 4)) return -1;
           const volatile ScoreDesc* dp = reinterpret_cast<const volatile ScoreDesc*>(slot_ptr + slot * TS_SLOT_BYTES + TS_ROWS * TS_SCALE_BYTES);
           const int flags = dp->flags, qc = dp->qc;
           ac = dp->ac0;
           ako::tc::mbar_arrive(ako::smem_u32(&s_slot_empty[slot]));
           if (flags & TS_F_END) return 0;
-          if (qc != q_cur) {
-            q_rel_to = qc;  // handed back after the tile in flight, the last one that may read them
-            q_cur = qc;
-            if (!ako::tc::mbar_wait(ako::smem_u32(&s_q_full[qc & 1]), (uint32_t)((qc >> 1) & 1), &g_dsa_status, 5)) return -1;
-            q_lo = q_lo0 + (qc & 1) * (TS_Q_BYTES >> 4) + rh * ((2 * NH * HD) >> 4);  // this half's two rows
-          }
+          if ((flags & TS_F_NEWGROUP) &&
+              !ako::tc::mbar_wait(ako::smem_u32(&s_q_full), (uint32_t)(qc & 1), &g_dsa_status, 5)) return -1;
           shared = flags & TS_F_SHARED;
+          last_unit = flags & TS_F_LASTGROUP;
           subs = shared ? 1 : TS_ROWS;
           sub = 0;
           acc_wait = (n & 1) ^ 1;  // parity to wait for before the unit's first MMA
           ++n;
         }
-        // Tiles of the other row half are waited for as well: the stage's release counts both
+        // Tiles of the other row pairs are waited for as well: the stage's release counts all
         // issuers, and this keeps an issuer from arriving for the stage's next use too early.
         const int stage = ac % TS_A_STAGES;
         if (!ako::tc::mbar_wait(ako::smem_u32(&s_a_full[stage]), (uint32_t)((ac / TS_A_STAGES) & 1), &g_dsa_status, 7)) return -1;
         ako::tc::fence_after_thread_sync();
-        t.mma = shared || (sub >> 1) == rh;
+        t.mma = shared || (sub >> 1) == me;
         t.a_lo = a_lo0 + stage * (TS_A_BYTES >> 4);
         t.b_lo = q_lo + (shared ? 0 : (sub & 1) * ((NH * HD) >> 4));
         t.d = acc + (shared ? 0 : (sub & 1) * NH);
         t.idesc = shared ? IDESC_SHARED : IDESC_ROW;
         t.stage = stage;
-        t.acc_wait = (shared || sub == 2 * rh) ? acc_wait : -1;  // first tile that writes the accumulator
-        t.last = shared || sub == 2 * rh + 1;                    // last tile that writes it
+        t.acc_wait = (shared || sub == 2 * me) ? acc_wait : -1;  // first tile that writes the accumulator
+        t.last = shared || sub == 2 * me + 1;                    // last tile that writes it
+        t.q_done = last_unit && sub == subs - 1;
         ++sub;
         ++ac;
         return 1;
@@ -364,65 +364,61 @@ dsa_score_tc_kernel(ScoreParams p, const __grid_constant__ CUtensorMap tm_q, con
               !ako::tc::mbar_wait(ako::smem_u32(&s_acc_empty[me]), (uint32_t)cur.acc_wait, &g_dsa_status, 6)) break;
           ako::tc::mma_f8_lohi<false>(cur.d, cur.a_lo, cur.b_lo, cur.idesc);  // K = 32 slices: +32 B = +2
           ako::tc::mma_f8_lohi<true>(cur.d, cur.a_lo + 2, cur.b_lo + 2, cur.idesc);
-          r = prepare(nxt);
+          if (!cur.q_done) r = prepare(nxt);
           ako::tc::mma_f8_lohi<true>(cur.d, cur.a_lo + 4, cur.b_lo + 4, cur.idesc);
           ako::tc::mma_f8_lohi<true>(cur.d, cur.a_lo + 6, cur.b_lo + 6, cur.idesc);
           ako::tc::mma_commit(ako::smem_u32(&s_a_empty[cur.stage]));
           if (cur.last) ako::tc::mma_commit(ako::smem_u32(&s_acc_full[me]));
         } else {
           ako::tc::mbar_arrive(ako::smem_u32(&s_a_empty[cur.stage]));
+          if (!cur.q_done) r = prepare(nxt);
+        }
+        if (cur.q_done) {
+          // The group's last tile: hand the query buffer back once this issuer's MMAs are done,
+          // and only then look at the next unit (its group cannot be loaded before).
+          ako::tc::mma_commit(ako::smem_u32(&s_q_empty));
           r = prepare(nxt);
         }
-        for (; q_rel < q_rel_to; ++q_rel)  // groups this issuer is past (it may never have seen some)
-          ako::tc::mma_commit(ako::smem_u32(&s_q_empty[q_rel & 1]));
         cur = nxt;
       }
     }
   } else {
     // ================================ epilogue (four teams) =======================================
-    const int team = warp / TS_TEAM_WARPS;  // accumulator
-    const int par = team >> 1;          // parity of the units taken
-    const int rh = team & 1;            // which two rows of the group
+    const int team = warp / TS_TEAM_WARPS;  // accumulator = row pair
     const int q = warp & 3;             // TMEM lane quarter
     const int t = 32 * q + lane;        // token inside the unit
     const uint32_t tmem_team = tmem_base + ((uint32_t)(32 * q) << 16) + team * TS_ACC_COLS;
-    int q_rel = 0;                      // query buffers released so far (group ordinals below this)
-    int q_cur = -1;
-    const float* wrow = nullptr;
+    const float* wrow = reinterpret_cast<const float*>(w_ptr) + team * 2 * NH;
     float* orow[2] = {nullptr, nullptr};
     for (int n = 0;; ++n) {
-      const int uo = 2 * n + par;
-      const int slot = uo % TS_SLOTS;
+      const int slot = n % TS_SLOTS;
       const unsigned char* sp = slot_ptr + slot * TS_SLOT_BYTES;
-      if (!ako::tc::mbar_wait(ako::smem_u32(&s_slot_full[slot]), (uint32_t)((uo / TS_SLOTS) & 1), &g_dsa_status, 8)) break;
-      const ScoreDesc d = *reinterpret_cast<const ScoreDesc*>(sp + TS_ROWS * TS_SCALE_BYTES);
-      if (d.flags & TS_F_END) break;
-      if (d.qc != q_cur) {
-        // Groups below d.qc are finished for this warp (it may never have seen some of them).
-        __syncwarp();
-        if (lane == 0)
-          for (; q_rel < d.qc; ++q_rel) ako::tc::mbar_arrive(ako::smem_u32(&s_q_empty[q_rel & 1]));
-        q_rel = d.qc;
-        q_cur = d.qc;
-        if (!ako::tc::mbar_wait(ako::smem_u32(&s_q_full[q_cur & 1]), (uint32_t)((q_cur >> 1) & 1), &g_dsa_status, 9)) break;
-        wrow = reinterpret_cast<const float*>(w_ptr + (q_cur & 1) * TS_W_BYTES) + rh * 2 * NH;
+      if (!ako::tc::mbar_wait(ako::smem_u32(&s_slot_full[slot]), (uint32_t)((n / TS_SLOTS) & 1), &g_dsa_status, 8)) break;
+      const int4 d0 = *reinterpret_cast<const int4*>(sp + TS_ROWS * TS_SCALE_BYTES);  // row0, pp, flags, qc
+      const int row0 = d0.x, pp = d0.y, flags = d0.z, qc = d0.w;
+      if (flags & TS_F_END) break;
+      const int2 sl2 = *reinterpret_cast<const int2*>(sp + TS_ROWS * TS_SCALE_BYTES + 16 + team * 8);  // sl[2*team], +1
+      if (flags & TS_F_NEWGROUP) {
+        if (!ako::tc::mbar_wait(ako::smem_u32(&s_q_full), (uint32_t)(qc & 1), &g_dsa_status, 9)) break;
 #pragma unroll
         for (int i = 0; i < 2; ++i)
-          orow[i] = p.scores + (int64_t)min(d.row0 + rh * 2 + i, p.rows - 1) * p.max_pages * PS;
+          orow[i] = p.scores + (int64_t)min(row0 + team * 2 + i, p.rows - 1) * p.max_pages * PS;
       }
       // key scales of this thread's token for its two rows
-      const bool shared = d.flags & TS_F_SHARED;
+      const bool shared = flags & TS_F_SHARED;
       float ksc[2];
 #pragma unroll
       for (int i = 0; i < 2; ++i)
-        ksc[i] = reinterpret_cast<const float*>(sp + (shared ? 0 : rh * 2 + i) * TS_SCALE_BYTES)[t];
+        ksc[i] = reinterpret_cast<const float*>(sp + (shared ? 0 : team * 2 + i) * TS_SCALE_BYTES)[t];
       __syncwarp();
       if (lane == 0) ako::tc::mbar_arrive(ako::smem_u32(&s_slot_empty[slot]));
 
       if (!ako::tc::mbar_wait(ako::smem_u32(&s_acc_full[team]), (uint32_t)(n & 1), &g_dsa_status, 10)) break;
       ako::tc::fence_after_thread_sync();
       // 32 accumulator columns per step: row (c>>1) of this thread's pair, heads 32*(c&1)...
-      float part[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+      // relu is one instruction per element; the weighted sums go two elements per instruction
+      // (fma.rn.f32x2): this loop is bound by instruction issue, not by the tensor pipe.
+      float2 part[2][2] = {{{0.f, 0.f}, {0.f, 0.f}}, {{0.f, 0.f}, {0.f, 0.f}}};
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         float v[32];
@@ -437,20 +433,24 @@ dsa_score_tc_kernel(ScoreParams p, const __grid_constant__ CUtensorMap tm_q, con
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           const float4 w4 = wp[j];
-          part[c >> 1][0] = fmaf(fmaxf(v[4 * j + 0], 0.f), w4.x, part[c >> 1][0]);
-          part[c >> 1][1] = fmaf(fmaxf(v[4 * j + 1], 0.f), w4.y, part[c >> 1][1]);
-          part[c >> 1][2] = fmaf(fmaxf(v[4 * j + 2], 0.f), w4.z, part[c >> 1][2]);
-          part[c >> 1][3] = fmaf(fmaxf(v[4 * j + 3], 0.f), w4.w, part[c >> 1][3]);
+          part[c >> 1][0] = __ffma2_rn(make_float2(fmaxf(v[4 * j + 0], 0.f), fmaxf(v[4 * j + 1], 0.f)),
+                                       make_float2(w4.x, w4.y), part[c >> 1][0]);
+          part[c >> 1][1] = __ffma2_rn(make_float2(fmaxf(v[4 * j + 2], 0.f), fmaxf(v[4 * j + 3], 0.f)),
+                                       make_float2(w4.z, w4.w), part[c >> 1][1]);
         }
       }
-      const int tok = d.pp * 2 * PS + t;
+      if (flags & TS_F_LASTGROUP) {  // this warp has read the group's weights for the last time
+        __syncwarp();
+        if (lane == 0) ako::tc::mbar_arrive(ako::smem_u32(&s_q_empty));
+      }
+      const int tok = pp * 2 * PS + t;
       if (tok < p.max_pages * PS) {
+        const int sls[2] = {sl2.x, sl2.y};
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
-          const int sl = d.sl[rh * 2 + i];
-          if (sl < 0) continue;
-          const float sum = (part[i][0] + part[i][1]) + (part[i][2] + part[i][3]);
-          orow[i][tok] = (tok < sl) ? sum * ksc[i] : -INFINITY;
+          if (sls[i] < 0) continue;
+          const float sum = (part[i][0].x + part[i][0].y) + (part[i][1].x + part[i][1].y);
+          orow[i][tok] = (tok < sls[i]) ? sum * ksc[i] : -INFINITY;
         }
       }
     }
