@@ -104,6 +104,9 @@ int ako4x_mla_attention_device_status(void);
  *   iter6-triton-split-K-grid-pid0-kvsplit/submission_no_cache.py:537-692.
  * Ragged batch; query i of a sequence sees keys j <= (kv_len - q_len) + i; a query that sees no
  * key gets o = 0, lse = -inf. q_nope bf16 [total_q,16,512]; q_pe bf16 [total_q,16,64].
+ * From 48 query tokens on, the call needs a workspace (256-byte aligned) of 2176 bytes per key
+ * (a contiguous copy of the keys and a transposed copy of the values for the tensor cores);
+ * smaller calls need none.
  */
 size_t ako4x_mla_paged_prefill_workspace_bytes(int64_t total_q, int64_t batch,
                                                int64_t num_kv_indices, int64_t page_size);
