@@ -362,9 +362,44 @@ def cpu_moe_sample(sample_tokens, steps, warmup):
     return pairs / 8.0 / dt, dt, cores
 
 
+def cpu_decode_sample(which, batch=4):
+    """KV tokens/s of the CPU oracle's decode operator on `batch` sequences of the benchmark's
+    length distribution (all host cores)."""
+    import oracle
+    from ako4x_b200 import workloads as W
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    if which == "gqa_decode":
+        a = W.make_gqa_decode(batch, shape_id=100, device="cpu", extra_pages=64)
+        fn = lambda: oracle.gqa_paged_decode(a["q"], a["k_cache"], a["v_cache"], a["kv_indptr"], a["kv_indices"],
+                                             a["sm_scale"])
+    else:
+        a = W.make_mla_decode(batch, shape_id=100, device="cpu", extra_pages=64)
+        fn = lambda: oracle.mla_paged_decode(a["q_nope"], a["q_pe"], a["ckv_cache"], a["kpe_cache"], a["kv_indptr"],
+                                             a["kv_indices"], a["sm_scale"])
+    n = a["kv_indices"].numel()
+    fn()
+    t0 = time.perf_counter()
+    fn()
+    dt = time.perf_counter() - t0
+    return n / dt, dt, cores, n
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
+        return
+    if args.op != "moe":
+        tps, dt, cores, n = cpu_decode_sample(args.op)
+        print(json.dumps({
+            "impl": "reference", "metric": f"{args.op}_kv_tokens_per_s", "value": tps, "unit": "kv_tokens/s",
+            "n_gpus": args.gpus, "steps": 1, "warmup": 1, "ms_per_step": dt * 1e3, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "fp32", "data": "synthetic",
+            "config": {"workload": f"{args.op} len~U[128/512,8192], page_size=1", "sample_sequences": 4},
+            "cpu_baseline": {"value": tps, "unit": "kv_tokens/s", "cores": cores, "kind": "port",
+                             "sample": f"4 sequences ({n} KV tokens), one pass of the CPU oracle"},
+            "e2e": {"value": tps, "unit": "kv_tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}), flush=True)
         return
     sample = 64
     steps = max(1, args.steps)
@@ -622,11 +657,15 @@ def main():
         if not args.no_ops_table:
             torch.cuda.empty_cache()
             line["ops"] = ops_table(peaks)
-        if not args.no_cpu_baseline:
+        if not args.no_cpu_baseline and args.op == "moe":
             tps, dt, cores = cpu_moe_sample(64, 1, 0)
             line["cpu_baseline"] = {"value": tps, "unit": "tokens/s (full-token equivalents)", "cores": cores, "kind": "port",
                                     "sample": "64 of 8192 tokens, one pass of the CPU oracle "
                                               f"({dt:.1f} s), all 32 local experts resident"}
+        elif not args.no_cpu_baseline:
+            tps, dt, cores, n = cpu_decode_sample(args.op)
+            line["cpu_baseline"] = {"value": tps, "unit": "kv_tokens/s", "cores": cores, "kind": "port",
+                                    "sample": f"4 sequences ({n} KV tokens), one pass of the CPU oracle ({dt:.1f} s)"}
     if dist_on:
         import torch.distributed as dist
         dist.barrier()

@@ -78,6 +78,19 @@ def test_prefill_tensor_core_path(built_lib, q_lens, kv_lens):
                               extra_pages=17))
 
 
+@pytest.mark.parametrize("q_len", [20, 100])
+def test_prefill_page_size_4(built_lib, q_len):
+    """Pages of four tokens (kv_len = pages x 4), on the small-call kernel and on the tensor-core one."""
+    g = torch.Generator().manual_seed(7 + q_len)
+    npages, used = 96, 70                       # 280 keys
+    a = W.make_mla_prefill(1, shape_id=5, q_lens=[q_len], kv_lens=[used * 4], extra_pages=npages * 4 - used * 4)
+    a["ckv_cache"] = a["ckv_cache"][: npages * 4].reshape(npages, 4, 512).contiguous()
+    a["kpe_cache"] = a["kpe_cache"][: npages * 4].reshape(npages, 4, 64).contiguous()
+    a["kv_indices"] = torch.randperm(npages, generator=g)[:used].to(torch.int32)
+    a["kv_indptr"] = torch.tensor([0, used], dtype=torch.int32)
+    _check(mla_prefill, oracle.mla_paged_prefill, PKEYS, a)
+
+
 def test_prefill_config_shape_reduced(built_lib):
     """Batch 8 with the configured distributions at a quarter of the lengths (oracle cost)."""
     _check(mla_prefill, oracle.mla_paged_prefill, PKEYS,
