@@ -10,7 +10,7 @@
 // fetched one tile ahead of the copies that need them. Rows sit in shared memory with a 1040-byte
 // pitch, which keeps ldmatrix bank-conflict free without a swizzle. Partials (m, l, acc) go to the
 // workspace in fp32 and a second kernel merges them; with one split the CTA writes o and lse
-// itself. Waits on the mbarriers are bounded: a wait that runs out of budget records a code in
+// itself. Waits on the mbarriers are bounded: a wait that exceeds its cycle limit records a code in
 // a device status word and the CTA stops consuming.
 #include "lse_merge.cuh"
 #include "tcgen05.cuh"

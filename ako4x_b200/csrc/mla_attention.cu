@@ -16,7 +16,7 @@
 //             and accumulates its own 64 of the 512 output columns.
 // Each token costs 1152 bytes of HBM traffic and 34816 flop, so the kernel is gather-bandwidth
 // bound; shared-memory traffic per token (about 4.4 KB) is the second limit. Waits on the
-// mbarriers are bounded: a wait that runs out of budget records a code in a device status word
+// mbarriers are bounded: a wait that exceeds its cycle limit records a code in a device status word
 // and the CTA stops consuming.
 #include "lse_merge.cuh"
 #include "mla_prefill_tc.h"

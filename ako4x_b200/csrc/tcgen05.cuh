@@ -1,7 +1,7 @@
 // Thin inline-PTX wrappers for the Blackwell (sm_100a) tensor-core path: tensor memory (TMEM)
 // allocation, tcgen05.mma with shared-memory matrix descriptors, tcgen05.commit / tcgen05.ld,
 // mbarriers with BOUNDED waits, and the proxy fence that makes cp.async-written shared memory
-// visible to the tensor core. Every wait gives up after a clock-cycle budget and reports through an
+// visible to the tensor core. Every wait gives up after a clock-cycle limit and reports through an
 // error word instead of spinning forever.
 #pragma once
 #include "common.cuh"
@@ -33,8 +33,8 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 // Waits for the phase with the given parity. Returns false when `*err` is already set or when the
-// cycle budget runs out (then `*err` is set to `code`); the caller must unwind, not retry.
-constexpr long long kWaitBudgetCycles = 400000000LL;  // ~0.2 s at 1.9 GHz
+// cycle limit is reached (then `*err` is set to `code`); the caller must unwind, not retry.
+constexpr long long kWaitLimitCycles = 400000000LL;  // ~0.2 s at 1.9 GHz
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* err, int code) {
   if (mbar_test_wait(bar, parity)) return true;
   const long long t0 = clock64();
@@ -43,7 +43,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* er
     if (mbar_test_wait(bar, parity)) return true;
     if ((++spins & 1023u) == 0u) {
       if (*reinterpret_cast<volatile int*>(err) != 0) return false;
-      if (clock64() - t0 > kWaitBudgetCycles) {
+      if (clock64() - t0 > kWaitLimitCycles) {
         atomicCAS(err, 0, code);
         return false;
       }

@@ -59,7 +59,7 @@ int ako4x_gqa_paged_decode(const void* q, const void* k_cache, const void* v_cac
                            int64_t page_size, void* workspace, size_t workspace_bytes,
                            void* stream);
 
-/* The gather pipeline waits on mbarriers with a cycle budget. A wait that gives up stores a
+/* The gather pipeline waits on mbarriers with a cycle limit. A wait that gives up stores a
  * non-zero code in a device status word and the CTA stops consuming; this call returns that word
  * (0 = no wait ever gave up). It synchronises the device: for tests and post-mortems only. */
 int ako4x_gqa_paged_decode_device_status(void);
@@ -182,7 +182,7 @@ int ako4x_moe_fp8_block_scale(const float* routing_logits, const void* routing_b
                               void* stream);
 /* Byte offset, inside a workspace for `tokens`, of a 32-bit status word that the call leaves at
  * 0 on success. The tensor-core GEMM kernels bound every wait on an mbarrier; a wait that runs out
- * of its cycle budget stores a non-zero code there (1 producer, 2/3 MMA issuer, 4 epilogue) and the
+ * of its cycle limit stores a non-zero code there (1 producer, 2/3 MMA issuer, 4 epilogue) and the
  * kernel unwinds instead of hanging. A caller may read the word after synchronising the stream. */
 size_t ako4x_moe_fp8_block_scale_status_offset(int64_t tokens);
 /* The same call with measurement hooks: `stage_events` is NULL or an array of 5 cudaEvent_t
