@@ -258,7 +258,16 @@ int pick_splits(int64_t batch, int64_t num_kv_indices, int64_t page_size) {
   int64_t s = want < cap ? want : cap;
   if (s < 1) s = 1;
   if (s > MAX_SPLITS) s = MAX_SPLITS;
-  return (int)s;
+  // Around that value, prefer the split count whose grid fills its last wave of resident CTAs best.
+  const int64_t slots = 148 * CTAS_PER_SM;
+  int64_t best = s;
+  double best_eff = 0.0;
+  for (int64_t c = (s + 1) / 2; c <= 2 * s && c <= cap && c <= MAX_SPLITS; ++c) {
+    const int64_t n = HEAD_GROUPS * batch * c;
+    const double eff = (double)n / (double)(ako::cdiv(n, slots) * slots);
+    if (eff > best_eff + 0.02 || (eff > best_eff - 0.02 && c == s)) { best_eff = eff; best = c; }
+  }
+  return (int)best;
 }
 
 }  // namespace

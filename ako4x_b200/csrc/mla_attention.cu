@@ -384,7 +384,15 @@ int pick_splits(int64_t rows, int64_t avg_keys) {
   int64_t s = want < cap ? want : cap;
   if (s < 1) s = 1;
   if (s > MAX_SPLITS) s = MAX_SPLITS;
-  return (int)s;
+  // Around that value, prefer the split count whose grid fills its last wave of CTAs (one per SM) best.
+  int64_t best = s;
+  double best_eff = 0.0;
+  for (int64_t c = (s + 1) / 2; c <= 2 * s && c <= cap && c <= MAX_SPLITS; ++c) {
+    const int64_t n = rows * c;
+    const double eff = (double)n / (double)(ako::cdiv(n, 148) * 148);
+    if (eff > best_eff + 0.02 || (eff > best_eff - 0.02 && c == s)) { best_eff = eff; best = c; }
+  }
+  return (int)best;
 }
 
 size_t workspace_for(int64_t rows, int splits) {
