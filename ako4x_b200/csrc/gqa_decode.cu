@@ -70,6 +70,16 @@ __global__ void __launch_bounds__(THREADS, CTAS_PER_SM) gqa_decode_kernel(Params
   const int tok_end = min(len, tok_begin + chunk);
   const int ntiles = (tok_end - tok_begin + TILE - 1) / TILE;
 
+  if (ntiles == 0 && p.num_splits > 1) {
+    // Nothing in this chunk (the sequence is shorter than split * chunk): an empty partial, which
+    // the merge skips without reading the accumulator.
+    if (g < GROUP && t == 0) {
+      float* ml = p.part_ml + (((int64_t)b * HQ + kvh * GROUP + g) * p.num_splits + split) * 2;
+      ml[0] = -INFINITY;
+      ml[1] = 0.f;
+    }
+    return;
+  }
   // Shared memory starts finite: rows of tokens past the end are never copied, and 0 * stale
   // must not be NaN in the PV product.
   for (int i = threadIdx.x; i < SMEM_BYTES / 16; i += THREADS) reinterpret_cast<uint4*>(smem)[i] = make_uint4(0, 0, 0, 0);
@@ -245,29 +255,26 @@ __global__ void __launch_bounds__(THREADS, CTAS_PER_SM) gqa_decode_kernel(Params
 int pick_splits(int64_t batch, int64_t num_kv_indices, int64_t page_size) {
   if (batch <= 0) return 1;
   const int64_t avg_len = num_kv_indices * page_size / batch;
-  int64_t want = ako::cdiv(148 * 4 * CTAS_PER_SM, HEAD_GROUPS * batch);  // ~4 resident waves
-  int64_t cap = avg_len / 128;                         // keep chunks >= 128 tokens on average
-  if (cap < 1) cap = 1;
-  // A small batch leaves SMs idle at that grain and each CTA walks its chunk tile by tile, so the
-  // call's latency is the chunk length: go down to two 16-token tiles per CTA, up to one wave of CTAs.
-  if (HEAD_GROUPS * batch * cap < 148 * CTAS_PER_SM) {
-    const int64_t fine = avg_len / (2 * TILE) > 1 ? avg_len / (2 * TILE) : 1;
-    const int64_t one_wave = (148 * CTAS_PER_SM) / (HEAD_GROUPS * batch) > 1 ? (148 * CTAS_PER_SM) / (HEAD_GROUPS * batch) : 1;
-    cap = fine < one_wave ? fine : one_wave;
-  }
-  int64_t s = want < cap ? want : cap;
+  const int64_t slots = 148 * CTAS_PER_SM;                      // resident CTAs
+  const int64_t pairs = HEAD_GROUPS * batch;                    // CTAs per split
+  // Long sequences: chunks of about 300 tokens. Every sequence of a batch gets the same split
+  // count, so with ragged lengths the longest chunks set the makespan; a sweep at B = 64 and 256
+  // (lengths U[128, 8192]) was best between 280 and 450 tokens per chunk and 5 % worse at 900.
+  // Short sequences: 128-token chunks, and at least two waves of CTAs when chunks of 128 allow it.
+  int64_t s = avg_len / (avg_len >= 2048 ? 300 : 128);
+  int64_t t = ako::cdiv(2 * slots, pairs);
+  if (t > avg_len / 128) t = avg_len / 128;
+  if (s < t) s = t;
   if (s < 1) s = 1;
-  if (s > MAX_SPLITS) s = MAX_SPLITS;
-  // Around that value, prefer the split count whose grid fills its last wave of resident CTAs best.
-  const int64_t slots = 148 * CTAS_PER_SM;
-  int64_t best = s;
-  double best_eff = 0.0;
-  for (int64_t c = (s + 1) / 2; c <= 2 * s && c <= cap && c <= MAX_SPLITS; ++c) {
-    const int64_t n = HEAD_GROUPS * batch * c;
-    const double eff = (double)n / (double)(ako::cdiv(n, slots) * slots);
-    if (eff > best_eff + 0.02 || (eff > best_eff - 0.02 && c == s)) { best_eff = eff; best = c; }
+  // A small batch that still leaves SMs idle: the call's latency is the chunk length, so go down
+  // to two 16-token tiles per chunk, up to one wave of CTAs.
+  if (pairs * s < slots) {
+    const int64_t fine = avg_len / (2 * TILE) > 1 ? avg_len / (2 * TILE) : 1;
+    const int64_t one_wave = slots / pairs > 1 ? slots / pairs : 1;
+    s = fine < one_wave ? fine : one_wave;
   }
-  return (int)best;
+  if (s > MAX_SPLITS) s = MAX_SPLITS;
+  return (int)s;
 }
 
 }  // namespace
