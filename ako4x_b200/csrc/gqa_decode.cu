@@ -45,16 +45,32 @@ struct Params {
   float* part_ml;   // [batch*32][splits][2]
   float scale_log2;
   int page_size;
-  int num_splits;
+  int num_splits;       // uniform mode: every sequence is cut into this many chunks
+  // work-list mode (items != nullptr): chunks of `chunk_tokens` tokens; item i = (sequence, chunk
+  // ordinal) or (-1, -1); partials are indexed by item, item_start[b] .. item_start[b+1] are the
+  // items of sequence b.
+  const int2* items;
+  int chunk_tokens;
 };
 
 __global__ void __launch_bounds__(THREADS, CTAS_PER_SM) gqa_decode_kernel(Params p) {
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ __align__(8) uint64_t s_full[STAGES];
 
-  const int split = blockIdx.x % p.num_splits;
-  const int half = (blockIdx.x / p.num_splits) % HEAD_GROUPS;
-  const int b = blockIdx.x / (p.num_splits * HEAD_GROUPS);
+  int split, half, b, item = 0;
+  if (p.items) {
+    ako::pdl_wait();  // the work list is written by the planning kernel launched just before
+    item = blockIdx.x / HEAD_GROUPS;
+    half = blockIdx.x % HEAD_GROUPS;
+    const int2 it = p.items[item];
+    b = it.x;
+    split = it.y;
+    if (b < 0) return;  // unused slot of the worst-case grid
+  } else {
+    split = blockIdx.x % p.num_splits;
+    half = (blockIdx.x / p.num_splits) % HEAD_GROUPS;
+    b = blockIdx.x / (p.num_splits * HEAD_GROUPS);
+  }
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   const int head0 = half * HPC;
@@ -64,17 +80,18 @@ __global__ void __launch_bounds__(THREADS, CTAS_PER_SM) gqa_decode_kernel(Params
   ako::pdl_trigger();  // the merge kernel may be scheduled early; it waits for this grid to finish
   const int32_t* idx = p.indices + p.indptr[b];
   const int len = (int)(p.indptr[b + 1] - p.indptr[b]) * p.page_size;
-  int chunk = (int)ako::round_up(ako::cdiv(len, p.num_splits), TILE);
+  int chunk = p.items ? p.chunk_tokens : (int)ako::round_up(ako::cdiv(len, p.num_splits), TILE);
   if (chunk < TILE) chunk = TILE;
   const int tok_begin = min(len, split * chunk);
   const int tok_end = min(len, tok_begin + chunk);
   const int ntiles = (tok_end - tok_begin + TILE - 1) / TILE;
 
-  if (ntiles == 0 && p.num_splits > 1) {
-    // Nothing in this chunk (the sequence is shorter than split * chunk): an empty partial, which
-    // the merge skips without reading the accumulator.
+  if (ntiles == 0 && (p.num_splits > 1 || p.items)) {
+    // Nothing in this chunk (the sequence is shorter than split * chunk, or empty): an empty
+    // partial, which the merge skips without reading the accumulator.
     if (g < GROUP && t == 0) {
-      float* ml = p.part_ml + (((int64_t)b * HQ + kvh * GROUP + g) * p.num_splits + split) * 2;
+      float* ml = p.part_ml + (p.items ? ((int64_t)item * HQ + kvh * GROUP + g)
+                                       : (((int64_t)b * HQ + kvh * GROUP + g) * p.num_splits + split)) * 2;
       ml[0] = -INFINITY;
       ml[1] = 0.f;
     }
@@ -230,7 +247,7 @@ __global__ void __launch_bounds__(THREADS, CTAS_PER_SM) gqa_decode_kernel(Params
 
   if (g < GROUP) {
     const int64_t rh = (int64_t)b * HQ + kvh * GROUP + g;
-    if (p.num_splits == 1) {
+    if (p.num_splits == 1 && !p.items) {
       const float inv = (l_run > 0.f) ? 1.f / l_run : 0.f;
       __nv_bfloat16* op = p.o + rh * D;
 #pragma unroll
@@ -239,17 +256,120 @@ __global__ void __launch_bounds__(THREADS, CTAS_PER_SM) gqa_decode_kernel(Params
             ako::pack_bf16x2(oacc[nd][0] * inv, oacc[nd][1] * inv);
       if (t == 0) p.lse[rh] = (l_run > 0.f) ? m_run + log2f(l_run) : -INFINITY;
     } else {
-      float* pa_out = p.part_acc + (rh * p.num_splits + split) * D;
+      const int64_t pidx = p.items ? ((int64_t)item * HQ + kvh * GROUP + g) : (rh * p.num_splits + split);
+      float* pa_out = p.part_acc + pidx * D;
 #pragma unroll
       for (int nd = 0; nd < 16; ++nd)
         *reinterpret_cast<float2*>(pa_out + nd * 8 + 2 * t) = make_float2(oacc[nd][0], oacc[nd][1]);
       if (t == 0) {
-        float* ml = p.part_ml + (rh * p.num_splits + split) * 2;
+        float* ml = p.part_ml + pidx * 2;
         ml[0] = m_run;
         ml[1] = l_run;
       }
     }
   }
+}
+
+// Work list for ragged batches: sequence b is cut into max(1, ceil(len_b / chunk)) chunks of `chunk`
+// tokens, so every CTA has about the same work whatever the mix of lengths. One block.
+__global__ void __launch_bounds__(256) gqa_plan_kernel(const int32_t* __restrict__ indptr, int batch,
+                                                       int page_size, int chunk, int max_items,
+                                                       int32_t* __restrict__ item_start,
+                                                       int2* __restrict__ items) {
+  __shared__ int s_scan[256];
+  __shared__ int s_base;
+  const int tid = threadIdx.x;
+  if (tid == 0) s_base = 0;
+  __syncthreads();
+  for (int b0 = 0; b0 < batch; b0 += 256) {
+    const int b = b0 + tid;
+    int n = 0;
+    if (b < batch) {
+      const int len = (indptr[b + 1] - indptr[b]) * page_size;
+      n = max(1, (len + chunk - 1) / chunk);
+    }
+    s_scan[tid] = n;
+    __syncthreads();
+    for (int off = 1; off < 256; off <<= 1) {  // inclusive Hillis-Steele scan
+      const int add = (tid >= off) ? s_scan[tid - off] : 0;
+      __syncthreads();
+      s_scan[tid] += add;
+      __syncthreads();
+    }
+    const int start = s_base + s_scan[tid] - n;
+    if (b < batch) {
+      item_start[b] = start;
+      for (int c = 0; c < n && start + c < max_items; ++c) items[start + c] = make_int2(b, c);
+    }
+    __syncthreads();
+    if (tid == 255) s_base += s_scan[255];
+    __syncthreads();
+  }
+  if (tid == 0) item_start[batch] = s_base;
+  for (int i = s_base + tid; i < max_items; i += 256) items[i] = make_int2(-1, -1);
+}
+
+// Merge of the work-list partials: one block per (sequence, head); 32 threads x 4 columns.
+__global__ void __launch_bounds__(D / 4) gqa_merge_items_kernel(
+    const float* __restrict__ part_acc, const float* __restrict__ part_ml,
+    const int32_t* __restrict__ item_start, __nv_bfloat16* __restrict__ o, float* __restrict__ lse) {
+  ako::pdl_wait();
+  const int b = blockIdx.x / HQ, h = blockIdx.x % HQ;
+  const int i0 = item_start[b], i1 = item_start[b + 1];
+  float M = -INFINITY;
+  for (int i = i0; i < i1; ++i) M = fmaxf(M, part_ml[((int64_t)i * HQ + h) * 2]);
+  float L = 0.f;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (M > -INFINITY) {
+    for (int i = i0; i < i1; ++i) {
+      const float* ml = part_ml + ((int64_t)i * HQ + h) * 2;
+      if (ml[0] == -INFINITY) continue;
+      const float w = exp2f(ml[0] - M);
+      L = fmaf(ml[1], w, L);
+      const float4 p4 = *reinterpret_cast<const float4*>(part_acc + ((int64_t)i * HQ + h) * D + threadIdx.x * 4);
+      acc.x = fmaf(p4.x, w, acc.x);
+      acc.y = fmaf(p4.y, w, acc.y);
+      acc.z = fmaf(p4.z, w, acc.z);
+      acc.w = fmaf(p4.w, w, acc.w);
+    }
+  }
+  const float inv = (L > 0.f) ? 1.f / L : 0.f;
+  uint2 pk;
+  pk.x = ako::pack_bf16x2(acc.x * inv, acc.y * inv);
+  pk.y = ako::pack_bf16x2(acc.z * inv, acc.w * inv);
+  *reinterpret_cast<uint2*>(o + (int64_t)blockIdx.x * D + threadIdx.x * 4) = pk;
+  if (threadIdx.x == 0) lse[blockIdx.x] = (L > 0.f) ? M + log2f(L) : -INFINITY;
+}
+
+// Work-list mode pays a third launch, so it is used where ragged lengths cost more than that:
+// batches that fill the GPU several times over with long sequences.
+struct Plan {
+  bool on;
+  int chunk;
+  int64_t max_items;
+};
+Plan pick_plan(int64_t batch, int64_t num_kv_indices, int64_t page_size) {
+  Plan pl = {false, 0, 0};
+  if (batch <= 0) return pl;
+  const int64_t total = num_kv_indices * page_size;
+  const int64_t avg_len = total / batch;
+  const int64_t slots = 148 * CTAS_PER_SM;
+  if (avg_len < 1024 || total < 64 * 1024 || total / 256 * HEAD_GROUPS < 4 * slots) return pl;
+  // about six waves of equal chunks, at least 256 tokens each
+  int64_t chunk = ako::cdiv(total, 6 * slots / HEAD_GROUPS);
+  if (chunk < 256) chunk = 256;
+  chunk = ako::round_up(chunk, (int64_t)TILE);
+  const int64_t items = ako::cdiv(total, chunk) + batch;
+  if (chunk > 0x3fffffff || items * HEAD_GROUPS > 0x7fffffffLL) return pl;
+  pl.on = true;
+  pl.chunk = (int)chunk;
+  pl.max_items = items;
+  return pl;
+}
+size_t plan_workspace(const Plan& pl, int64_t batch) {
+  // partial accumulators, partial (m, l), item table, item_start
+  return (size_t)pl.max_items * HQ * (D + 2) * sizeof(float) + (size_t)pl.max_items * sizeof(int2) +
+         ((size_t)(batch + 1) * sizeof(int32_t) + 15) / 16 * 16;
 }
 
 int pick_splits(int64_t batch, int64_t num_kv_indices, int64_t page_size) {
@@ -281,6 +401,8 @@ int pick_splits(int64_t batch, int64_t num_kv_indices, int64_t page_size) {
 
 extern "C" size_t ako4x_gqa_paged_decode_workspace_bytes(int64_t batch, int64_t num_kv_indices,
                                                          int64_t page_size) {
+  const Plan pl = pick_plan(batch, num_kv_indices, page_size);
+  if (pl.on) return plan_workspace(pl, batch);
   const int s = pick_splits(batch, num_kv_indices, page_size);
   if (s == 1) return 0;
   return (size_t)batch * HQ * s * (D + 2) * sizeof(float);
@@ -296,9 +418,11 @@ extern "C" int ako4x_gqa_paged_decode(const void* q, const void* k_cache, const 
   if (!q || !k_cache || !v_cache || !kv_indptr || !o || !lse) return AKO4X_EINVAL;
   if (num_kv_indices > 0 && !kv_indices) return AKO4X_EINVAL;
   if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)o) & 15) return AKO4X_EINVAL;
-  const int splits = pick_splits(batch, num_kv_indices, page_size);
+  const Plan pl = pick_plan(batch, num_kv_indices, page_size);
+  const int splits = pl.on ? 1 : pick_splits(batch, num_kv_indices, page_size);
   const size_t need = ako4x_gqa_paged_decode_workspace_bytes(batch, num_kv_indices, page_size);
   if (need > 0 && (!workspace || workspace_bytes < need)) return AKO4X_EWORKSPACE;
+  if (need > 0 && ((uintptr_t)workspace & 15)) return AKO4X_EINVAL;
   cudaStream_t st = (cudaStream_t)stream;
 
   Params p;
@@ -314,8 +438,46 @@ extern "C" int ako4x_gqa_paged_decode(const void* q, const void* k_cache, const 
   p.scale_log2 = sm_scale * AKO_LOG2E;
   p.page_size = (int)page_size;
   p.num_splits = splits;
+  p.items = nullptr;
+  p.chunk_tokens = 0;
 
   if (!ako::ensure_dynamic_smem<gqa_decode_kernel>(SMEM_BYTES)) return AKO4X_ELAUNCH;
+  if (pl.on) {
+    // workspace: [items][32][128] accumulators | [items][32][2] (m, l) | item table | item_start
+    p.part_ml = p.part_acc + (size_t)pl.max_items * HQ * D;
+    int2* items = reinterpret_cast<int2*>(p.part_ml + (size_t)pl.max_items * HQ * 2);
+    int32_t* item_start = reinterpret_cast<int32_t*>(items + pl.max_items);
+    p.items = items;
+    p.chunk_tokens = pl.chunk;
+    gqa_plan_kernel<<<1, 256, 0, st>>>(kv_indptr, (int)batch, (int)page_size, pl.chunk, (int)pl.max_items,
+                                       item_start, items);
+    AKO_CHECK_LAUNCH();
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(pl.max_items * HEAD_GROUPS));
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = SMEM_BYTES;
+    cfg.stream = st;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (cudaLaunchKernelEx(&cfg, gqa_decode_kernel, p) != cudaSuccess) return AKO4X_ELAUNCH;
+    cudaLaunchConfig_t mcfg = {};
+    mcfg.gridDim = dim3((unsigned)(batch * HQ));
+    mcfg.blockDim = dim3(D / 4);
+    mcfg.stream = st;
+    mcfg.attrs = attr;
+    mcfg.numAttrs = 1;
+    const float* pacc = p.part_acc;
+    const float* pml = p.part_ml;
+    const int32_t* is = item_start;
+    __nv_bfloat16* op = p.o;
+    float* lp = p.lse;
+    if (cudaLaunchKernelEx(&mcfg, gqa_merge_items_kernel, pacc, pml, is, op, lp) != cudaSuccess)
+      return AKO4X_ELAUNCH;
+    return AKO4X_OK;
+  }
   const int64_t grid = batch * HEAD_GROUPS * splits;
   if (grid > 0x7fffffffLL) return AKO4X_EINVAL;
   gqa_decode_kernel<<<(unsigned)grid, THREADS, SMEM_BYTES, st>>>(p);

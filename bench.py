@@ -598,7 +598,8 @@ def run_decode(args, rank, world, dist_on, peaks, which):
                 "h2d_bytes_per_step": sum(v.numel() * v.element_size() for v in h_in.values()),
                 "d2h_bytes_per_step": h_o.numel() * h_o.element_size() + h_l.numel() * 4,
                 "note": "the KV cache is resident state; q and the page lists are the step's inputs"},
-        "gpu_launches": 2 * args.steps,
+        # GQA at this size runs in work-list mode: plan + decode + merge; MLA: decode + merge
+        "gpu_launches": (3 if which == "gqa_decode" else 2) * args.steps,
         "roofline": {"bound": "hbm", "kernel": f"{which} split kernel + merge", "achieved": achieved,
                      "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
                      "traffic": None, "peak_source": peaks["source"]},

@@ -41,6 +41,14 @@ def test_config_shapes(built_lib, batch):
     _check(W.make_gqa_decode(batch, shape_id=batch, len_lo=128, len_hi=1024 if batch > 1 else 8192))
 
 
+def test_work_list_mode_ragged(built_lib):
+    """A batch large and long enough for the work-list mode (equal chunks per CTA): very long next to
+    very short and empty sequences, checked against the oracle for every row."""
+    lens = [8192] * 20 + [1, 17, 300, 0, 2049, 255, 256, 257] + [5000, 16, 0, 777] * 5
+    assert sum(lens) >= 160 * 1024
+    _check(W.make_gqa_decode(len(lens), shape_id=41, lens=lens, extra_pages=29))
+
+
 def test_page_size_4(built_lib):
     g = torch.Generator().manual_seed(5)
     pages, P = 50, 4
