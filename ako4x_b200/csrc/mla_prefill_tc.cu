@@ -38,11 +38,10 @@ constexpr int BK = 128;                   // keys per tile
 constexpr int NCH = DQK / 64;             // nine reduction chunks of 64 columns
 constexpr int CH_BYTES = BM * 128;        // one 128-row x 64-column bf16 chunk: 16 KB
 constexpr int ST_BYTES = 2 * CH_BYTES;    // Q chunk + K chunk
-constexpr int NST = 3;
+constexpr int NST = 4;
 constexpr int V_BYTES = 2 * 256 * 128;    // two boxes of 256 rows x 64 keys
-constexpr int P_BYTES = 2 * CH_BYTES;     // two 64-key atoms of 128 rows
-constexpr int AUX_BYTES = 2048;           // alpha[2][128], final l[128]
-constexpr int SMEM = NST * ST_BYTES + V_BYTES + P_BYTES + AUX_BYTES + 1024;
+constexpr int AUX_BYTES = 3072;           // alpha[4][128], final l[128]
+constexpr int SMEM = NST * ST_BYTES + V_BYTES + AUX_BYTES + 1024;
 constexpr int THREADS = 512;
 constexpr int REGS_O = 184, REGS_SOFTMAX = 104, REGS_OTHER = 40;  // 2*184 + 104 + 40 = 4*128
 constexpr float NEG = -1.0e30f;           // finite stand-in for -inf
@@ -118,7 +117,7 @@ mla_prefill_tc_kernel(PfParams p, const __grid_constant__ CUtensorMap tm_qn, con
   extern __shared__ unsigned char smem_raw[];
   __shared__ __align__(8) uint64_t st_full[NST], st_empty[NST];
   __shared__ __align__(8) uint64_t s_full[2], s_empty[2];
-  __shared__ __align__(8) uint64_t p_full, p_empty, v_full, v_empty, pv_full, pv_empty, fin;
+  __shared__ __align__(8) uint64_t p_full, v_full, v_empty, pv_full, pv_empty, fin;
   __shared__ uint32_t s_tmem;
   __shared__ int s_work[4];  // sequence, tile inside the sequence (or -1)
 
@@ -127,10 +126,8 @@ mla_prefill_tc_kernel(PfParams p, const __grid_constant__ CUtensorMap tm_qn, con
   unsigned char* smem_al = smem_raw + ((1024u - (ako::smem_u32(smem_raw) & 1023u)) & 1023u);
   const uint32_t st_base = ako::smem_u32(smem_al);
   const uint32_t v_base = st_base + NST * ST_BYTES;
-  const uint32_t p_base = v_base + V_BYTES;
-  unsigned char* p_ptr = smem_al + NST * ST_BYTES + V_BYTES;
-  float* alpha_s = reinterpret_cast<float*>(p_ptr + P_BYTES);  // [2][128]
-  float* fin_l = alpha_s + 2 * BM;                             // [128]
+  float* alpha_s = reinterpret_cast<float*>(smem_al + NST * ST_BYTES + V_BYTES);  // [4][128]
+  float* fin_l = alpha_s + 4 * BM;                                                // [128]
 
   if (tid == 0) {
     int t = blockIdx.x, b = 0;
@@ -147,10 +144,9 @@ mla_prefill_tc_kernel(PfParams p, const __grid_constant__ CUtensorMap tm_qn, con
     }
     for (int s = 0; s < 2; ++s) {
       ako::tc::mbar_init(ako::smem_u32(&s_full[s]), 1);
-      ako::tc::mbar_init(ako::smem_u32(&s_empty[s]), 4);
+      ako::tc::mbar_init(ako::smem_u32(&s_empty[s]), 1);
     }
     ako::tc::mbar_init(ako::smem_u32(&p_full), 4);
-    ako::tc::mbar_init(ako::smem_u32(&p_empty), 1);
     ako::tc::mbar_init(ako::smem_u32(&v_full), 1);
     ako::tc::mbar_init(ako::smem_u32(&v_empty), 1);
     ako::tc::mbar_init(ako::smem_u32(&pv_full), 1);
@@ -194,7 +190,7 @@ mla_prefill_tc_kernel(PfParams p, const __grid_constant__ CUtensorMap tm_qn, con
     for (int j = 0; j < ntk; ++j) {
       if (!ako::tc::mbar_wait(ako::smem_u32(&pv_full), (uint32_t)(j & 1), &g_pf_status, 1)) { ok = false; break; }
       ako::tc::fence_after_thread_sync();
-      const float a = alpha_s[(j & 1) * BM + r];
+      const float a = alpha_s[(j & 3) * BM + r];
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         float v[32];
@@ -234,7 +230,6 @@ mla_prefill_tc_kernel(PfParams p, const __grid_constant__ CUtensorMap tm_qn, con
     const bool row_ok = tile >= 0 && qtok < nq;
     const int kv_lim = row_ok ? max(0, min(kv_len, kv_len - q_len + tile * QT + qtok + 1)) : 0;
     const uint32_t tq = tmem + ((uint32_t)(32 * (warp & 3)) << 16);
-    unsigned char* prow = p_ptr + (r >> 3) * 1024 + (r & 7) * 128;
     float m = NEG, l = 0.f;
     bool ok = true;
     for (int j = 0; j < ntk; ++j) {
@@ -254,41 +249,30 @@ mla_prefill_tc_kernel(PfParams p, const __grid_constant__ CUtensorMap tm_qn, con
       }
       const float m_new = fmaxf(m, tmax);
       const float alpha = ako::fast_exp2(m - m_new);
-      // the PV MMAs of the previous tile have read P
-      if (!ako::tc::mbar_wait(ako::smem_u32(&p_empty), (uint32_t)((j & 1) ^ 1), &g_pf_status, 4)) { ok = false; break; }
       float sum = 0.f;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         float v[32];
         ako::tc::tmem_ld32(ts + 32 * c, v);
         ako::tc::tmem_ld_wait_regs(v);
-        if (c == 3) {  // S buffer read for the last time
-          ako::tc::fence_before_thread_sync();
-          __syncwarp();
-          if (lane == 0) ako::tc::mbar_arrive(ako::smem_u32(&s_empty[buf]));
-        }
+        // P overwrites the S buffer it came from, as bf16 pairs: the 32 columns just read become
+        // columns [16c, 16c+16), all of them read already; the PV MMAs take P from there (A operand
+        // in TMEM), so P never crosses shared memory
+        uint32_t w[16];
 #pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {  // 8 keys = one 16-byte chunk of the row
-          float e[8];
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const int kk = 32 * c + 8 * q4 + i;
-            e[i] = (kk < nvis) ? ako::fast_exp2(v[8 * q4 + i] * p.scale_log2 - m_new) : 0.f;
-            sum += e[i];
-          }
-          const int cc = 4 * c + q4;  // chunk 0..15 of the 128-key row: atom cc>>3, chunk cc&7
-          uint4 w;
-          w.x = ako::pack_bf16x2(e[0], e[1]);
-          w.y = ako::pack_bf16x2(e[2], e[3]);
-          w.z = ako::pack_bf16x2(e[4], e[5]);
-          w.w = ako::pack_bf16x2(e[6], e[7]);
-          *reinterpret_cast<uint4*>(prow + (cc >> 3) * CH_BYTES + (((cc & 7) ^ (r & 7)) << 4)) = w;
+        for (int i = 0; i < 32; i += 2) {
+          const float e0 = (32 * c + i < nvis) ? ako::fast_exp2(v[i] * p.scale_log2 - m_new) : 0.f;
+          const float e1 = (32 * c + i + 1 < nvis) ? ako::fast_exp2(v[i + 1] * p.scale_log2 - m_new) : 0.f;
+          sum += e0 + e1;
+          w[i >> 1] = ako::pack_bf16x2(e0, e1);
         }
+        ako::tc::tmem_st16(ts + 16 * c, w);
       }
+      ako::tc::tmem_st_wait();
       l = l * alpha + sum;
       m = m_new;
-      alpha_s[buf * BM + r] = alpha;
-      ako::tc::fence_proxy_async_smem();  // P is read by the tensor core (async proxy)
+      alpha_s[(j & 3) * BM + r] = alpha;
+      ako::tc::fence_before_thread_sync();
       __syncwarp();
       if (lane == 0) ako::tc::mbar_arrive(ako::smem_u32(&p_full));
     }
@@ -337,7 +321,7 @@ mla_prefill_tc_kernel(PfParams p, const __grid_constant__ CUtensorMap tm_qn, con
       constexpr uint32_t IDESC_S = ako::tc::idesc_bf16_f32(BM, BK);
       constexpr uint32_t IDESC_PV = ako::tc::idesc_bf16_f32(BM, 256);
       const uint32_t st_lo0 = ako::tc::smem_desc_lo(st_base);
-      const uint32_t p_lo0 = ako::tc::smem_desc_lo(p_base), v_lo0 = ako::tc::smem_desc_lo(v_base);
+      const uint32_t v_lo0 = ako::tc::smem_desc_lo(v_base);
       int g = 0;
       bool ok = true;
       auto issue_s = [&](int j) {
@@ -367,11 +351,11 @@ mla_prefill_tc_kernel(PfParams p, const __grid_constant__ CUtensorMap tm_qn, con
         for (int at = 0; at < 2; ++at)
 #pragma unroll
           for (int ks = 0; ks < 4; ++ks)
-            ako::tc::mma_bf16_lohi(d, p_lo0 + at * (CH_BYTES >> 4) + 2 * ks, v_lo0 + at * ((V_BYTES / 2) >> 4) + 2 * ks,
-                                   IDESC_PV, (at > 0 || ks > 0) ? 1u : 0u);
+            ako::tc::mma_bf16_tmem_a(d, tmem + (j & 1) * BK + 8 * (4 * at + ks), v_lo0 + at * ((V_BYTES / 2) >> 4) + 2 * ks,
+                                     IDESC_PV, (at > 0 || ks > 0) ? 1u : 0u);
         ako::tc::mma_commit(ako::smem_u32(&pv_full));
         ako::tc::mma_commit(ako::smem_u32(&v_empty));
-        ako::tc::mma_commit(ako::smem_u32(&p_empty));
+        ako::tc::mma_commit(ako::smem_u32(&s_empty[j & 1]));  // P (inside the S buffer) has been read
       };
       issue_s(0);
       for (int j = 0; ok && j < ntk; ++j) {

@@ -192,6 +192,32 @@ __device__ __forceinline__ void tmem_ld_wait_regs(float (&v)[32]) {
       : "memory");
 }
 
+// 32 lanes x 16 consecutive 32-bit columns, registers -> TMEM: thread i of the warp writes columns
+// [col, col+16) of TMEM lane (lane_base + i). Same lane-quarter rule as the loads.
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};\n" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+// Waits until this thread's tcgen05.st have been performed.
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
+
+// bf16 MMA whose A operand (128 rows x 16 reduction elements) sits in TMEM: row i in lane i, the 16
+// bf16 values packed two per 32-bit column (even element in the low half) in columns [a_tmem, a_tmem+8).
+__device__ __forceinline__ void mma_bf16_tmem_a(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t idesc,
+                                                uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .b64 db;\n.reg .pred p;\n"
+      "mov.b64 db, {%2, %4};\n"
+      "setp.ne.b32 p, %5, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %3, p;\n}\n" ::"r"(d_tmem),
+      "r"(a_tmem), "r"(b_lo), "r"(idesc), "r"(kSmemDescHiSw128), "r"(accumulate)
+      : "memory");
+}
+
 // ---- register re-balancing between warp groups ---------------------------------------------------
 template <int N>
 __device__ __forceinline__ void reg_dec() {
