@@ -238,14 +238,29 @@ mla_prefill_tc_kernel(PfParams p, const __grid_constant__ CUtensorMap tm_qn, con
       ako::tc::fence_after_thread_sync();
       const uint32_t ts = tq + buf * BK;
       const int nvis = kv_lim - j * BK;  // visible keys of this tile for this row (may be <= 0 or > 128)
+      // no masked key for any row of this warp in this tile; warp-uniform, because the aligned TMEM
+      // loads and stores below must be reached by the whole warp together
+      const bool fast = __all_sync(0xffffffffu, nvis >= BK) && p.scale_log2 > 0.f;
       float tmax = NEG;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         float v[32];
         ako::tc::tmem_ld32(ts + 32 * c, v);
         ako::tc::tmem_ld_wait_regs(v);
+        if (fast) {  // four independent chains, the (positive) scale applied once
+          float t0 = v[0], t1 = v[1], t2 = v[2], t3 = v[3];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) tmax = fmaxf(tmax, (32 * c + i < nvis) ? v[i] * p.scale_log2 : NEG);
+          for (int i = 4; i < 32; i += 4) {
+            t0 = fmaxf(t0, v[i]);
+            t1 = fmaxf(t1, v[i + 1]);
+            t2 = fmaxf(t2, v[i + 2]);
+            t3 = fmaxf(t3, v[i + 3]);
+          }
+          tmax = fmaxf(tmax, fmaxf(fmaxf(t0, t1), fmaxf(t2, t3)) * p.scale_log2);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) tmax = fmaxf(tmax, (32 * c + i < nvis) ? v[i] * p.scale_log2 : NEG);
+        }
       }
       const float m_new = fmaxf(m, tmax);
       const float alpha = ako::fast_exp2(m - m_new);
@@ -259,12 +274,25 @@ mla_prefill_tc_kernel(PfParams p, const __grid_constant__ CUtensorMap tm_qn, con
         // columns [16c, 16c+16), all of them read already; the PV MMAs take P from there (A operand
         // in TMEM), so P never crosses shared memory
         uint32_t w[16];
+        if (fast) {
+          float s0 = 0.f, s1 = 0.f;
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          const float e0 = (32 * c + i < nvis) ? ako::fast_exp2(v[i] * p.scale_log2 - m_new) : 0.f;
-          const float e1 = (32 * c + i + 1 < nvis) ? ako::fast_exp2(v[i + 1] * p.scale_log2 - m_new) : 0.f;
-          sum += e0 + e1;
-          w[i >> 1] = ako::pack_bf16x2(e0, e1);
+          for (int i = 0; i < 32; i += 2) {
+            const float e0 = ako::fast_exp2(v[i] * p.scale_log2 - m_new);
+            const float e1 = ako::fast_exp2(v[i + 1] * p.scale_log2 - m_new);
+            s0 += e0;
+            s1 += e1;
+            w[i >> 1] = ako::pack_bf16x2(e0, e1);
+          }
+          sum += s0 + s1;
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const float e0 = (32 * c + i < nvis) ? ako::fast_exp2(v[i] * p.scale_log2 - m_new) : 0.f;
+            const float e1 = (32 * c + i + 1 < nvis) ? ako::fast_exp2(v[i + 1] * p.scale_log2 - m_new) : 0.f;
+            sum += e0 + e1;
+            w[i >> 1] = ako::pack_bf16x2(e0, e1);
+          }
         }
         ako::tc::tmem_st16(ts + 16 * c, w);
       }
