@@ -345,20 +345,19 @@ mla_prefill_tc_kernel(PfParams p, const __grid_constant__ CUtensorMap tm_qn, con
         ako::tc::tma_load_2d(v_base + V_BYTES / 2, &tm_v, x + 64, half * 256, bar);
       }
     } else if (warp == 13 && lane == 0 && ntk > 0) {
-      // ================================ MMA issuer ==============================================
+      // ================================ S issuer ================================================
       constexpr uint32_t IDESC_S = ako::tc::idesc_bf16_f32(BM, BK);
-      constexpr uint32_t IDESC_PV = ako::tc::idesc_bf16_f32(BM, 256);
       const uint32_t st_lo0 = ako::tc::smem_desc_lo(st_base);
-      const uint32_t v_lo0 = ako::tc::smem_desc_lo(v_base);
       int g = 0;
-      bool ok = true;
-      auto issue_s = [&](int j) {
+      for (int j = 0; j < ntk; ++j) {
         const int buf = j & 1;
-        if (!ako::tc::mbar_wait(ako::smem_u32(&s_empty[buf]), (uint32_t)(((j >> 1) & 1) ^ 1), &g_pf_status, 7)) { ok = false; return; }
+        // the PV MMAs of tile j-2 have read P out of this buffer
+        if (!ako::tc::mbar_wait(ako::smem_u32(&s_empty[buf]), (uint32_t)(((j >> 1) & 1) ^ 1), &g_pf_status, 7)) break;
         const uint32_t d = tmem + buf * BK;
+        bool ok = true;
         for (int c = 0; c < NCH; ++c, ++g) {
           const int stage = g % NST;
-          if (!ako::tc::mbar_wait(ako::smem_u32(&st_full[stage]), (uint32_t)((g / NST) & 1), &g_pf_status, 8)) { ok = false; return; }
+          if (!ako::tc::mbar_wait(ako::smem_u32(&st_full[stage]), (uint32_t)((g / NST) & 1), &g_pf_status, 8)) { ok = false; break; }
           ako::tc::fence_after_thread_sync();
           const uint32_t a_lo = st_lo0 + stage * (ST_BYTES >> 4);
           const uint32_t b_lo = a_lo + (CH_BYTES >> 4);
@@ -367,12 +366,19 @@ mla_prefill_tc_kernel(PfParams p, const __grid_constant__ CUtensorMap tm_qn, con
             ako::tc::mma_bf16_lohi(d, a_lo + 2 * ks, b_lo + 2 * ks, IDESC_S, (c > 0 || ks > 0) ? 1u : 0u);
           ako::tc::mma_commit(ako::smem_u32(&st_empty[stage]));
         }
+        if (!ok) break;
         ako::tc::mma_commit(ako::smem_u32(&s_full[buf]));
-      };
-      auto issue_pv = [&](int j) {
-        if (!ako::tc::mbar_wait(ako::smem_u32(&p_full), (uint32_t)(j & 1), &g_pf_status, 9)) { ok = false; return; }
-        if (!ako::tc::mbar_wait(ako::smem_u32(&v_full), (uint32_t)(j & 1), &g_pf_status, 10)) { ok = false; return; }
-        if (!ako::tc::mbar_wait(ako::smem_u32(&pv_empty), (uint32_t)((j & 1) ^ 1), &g_pf_status, 11)) { ok = false; return; }
+      }
+    } else if (warp == 15 && lane == 0 && ntk > 0) {
+      // ================================ PV issuer ===============================================
+      // a thread of its own: PV of tile j goes to the tensor pipe the moment P is written, while
+      // the S issuer is still waiting on the operand stream of a later tile
+      constexpr uint32_t IDESC_PV = ako::tc::idesc_bf16_f32(BM, 256);
+      const uint32_t v_lo0 = ako::tc::smem_desc_lo(v_base);
+      for (int j = 0; j < ntk; ++j) {
+        if (!ako::tc::mbar_wait(ako::smem_u32(&p_full), (uint32_t)(j & 1), &g_pf_status, 9)) break;
+        if (!ako::tc::mbar_wait(ako::smem_u32(&v_full), (uint32_t)(j & 1), &g_pf_status, 10)) break;
+        if (!ako::tc::mbar_wait(ako::smem_u32(&pv_empty), (uint32_t)((j & 1) ^ 1), &g_pf_status, 11)) break;
         ako::tc::fence_after_thread_sync();
         const uint32_t d = tmem + 256;
 #pragma unroll
@@ -384,11 +390,6 @@ mla_prefill_tc_kernel(PfParams p, const __grid_constant__ CUtensorMap tm_qn, con
         ako::tc::mma_commit(ako::smem_u32(&pv_full));
         ako::tc::mma_commit(ako::smem_u32(&v_empty));
         ako::tc::mma_commit(ako::smem_u32(&s_empty[j & 1]));  // P (inside the S buffer) has been read
-      };
-      issue_s(0);
-      for (int j = 0; ok && j < ntk; ++j) {
-        if (j + 1 < ntk) issue_s(j + 1);
-        if (ok) issue_pv(j);
       }
     }
   }
