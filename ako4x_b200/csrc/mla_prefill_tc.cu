@@ -38,10 +38,14 @@ constexpr int BK = 128;                   // keys per tile
 constexpr int NCH = DQK / 64;             // nine reduction chunks of 64 columns
 constexpr int CH_BYTES = BM * 128;        // one 128-row x 64-column bf16 chunk: 16 KB
 constexpr int ST_BYTES = 2 * CH_BYTES;    // Q chunk + K chunk
-constexpr int NST = 4;
+constexpr int NST = 5;
 constexpr int V_BYTES = 2 * 256 * 128;    // two boxes of 256 rows x 64 keys
-constexpr int AUX_BYTES = 3072;           // alpha[4][128], final l[128]
-constexpr int SMEM = NST * ST_BYTES + V_BYTES + AUX_BYTES + 1024;
+constexpr int AUX_BYTES = 3072;           // alpha[4][128], final l[128], mbarriers, TMEM address, work item
+// exactly the 227 KB a CTA may have: no static shared memory in this kernel, so that the dynamic
+// region starts on a 1024-byte boundary (checked at entry) and needs no alignment slack
+constexpr int SMEM = NST * ST_BYTES + V_BYTES + AUX_BYTES;
+static_assert(SMEM <= 232448, "shared memory per CTA");
+static_assert(2560 + (2 * NST + 11) * 8 + 8 + 16 <= AUX_BYTES, "aux region");
 constexpr int THREADS = 512;
 constexpr int REGS_O = 184, REGS_SOFTMAX = 104, REGS_OTHER = 40;  // 2*184 + 104 + 40 = 4*128
 constexpr float NEG = -1.0e30f;           // finite stand-in for -inf
@@ -114,20 +118,31 @@ __global__ void __launch_bounds__(256) mla_prefill_gather_kernel(
 __global__ void __launch_bounds__(THREADS, 1)
 mla_prefill_tc_kernel(PfParams p, const __grid_constant__ CUtensorMap tm_qn, const __grid_constant__ CUtensorMap tm_qp,
                       const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v) {
-  extern __shared__ unsigned char smem_raw[];
-  __shared__ __align__(8) uint64_t st_full[NST], st_empty[NST];
-  __shared__ __align__(8) uint64_t s_full[2], s_empty[2];
-  __shared__ __align__(8) uint64_t p_full, v_full, v_empty, pv_full, pv_empty, fin;
-  __shared__ uint32_t s_tmem;
-  __shared__ int s_work[4];  // sequence, tile inside the sequence (or -1)
-
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int half = blockIdx.y;  // which 256 output columns
-  unsigned char* smem_al = smem_raw + ((1024u - (ako::smem_u32(smem_raw) & 1023u)) & 1023u);
+  unsigned char* smem_al = smem_raw;
+  if (ako::smem_u32(smem_raw) & 1023u) {  // the swizzled operand tiles need this; nothing is started yet
+    if (tid == 0) atomicCAS(&g_pf_status, 0, 13);
+    return;
+  }
   const uint32_t st_base = ako::smem_u32(smem_al);
   const uint32_t v_base = st_base + NST * ST_BYTES;
   float* alpha_s = reinterpret_cast<float*>(smem_al + NST * ST_BYTES + V_BYTES);  // [4][128]
   float* fin_l = alpha_s + 4 * BM;                                                // [128]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(fin_l + BM);
+  uint64_t* st_full = bars;
+  uint64_t* st_empty = bars + NST;
+  uint64_t* s_full = bars + 2 * NST;
+  uint64_t* s_empty = bars + 2 * NST + 2;
+  uint64_t& p_full = bars[2 * NST + 4];
+  uint64_t& v_full = bars[2 * NST + 5];
+  uint64_t& v_empty = bars[2 * NST + 6];
+  uint64_t& pv_full = bars[2 * NST + 7];
+  uint64_t& pv_empty = bars[2 * NST + 8];
+  uint64_t& fin = bars[2 * NST + 9];
+  uint32_t& s_tmem = *reinterpret_cast<uint32_t*>(bars + 2 * NST + 10);
+  int* s_work = reinterpret_cast<int*>(bars + 2 * NST + 11);  // sequence, tile inside the sequence (or -1)
 
   if (tid == 0) {
     int t = blockIdx.x, b = 0;
