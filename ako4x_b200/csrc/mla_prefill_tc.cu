@@ -7,19 +7,23 @@
 // the 512 output columns; the O tile would fill all of TMEM, so the two halves are separate CTAs that
 // both compute S. Per tile of 128 keys:
 //   S  = Q Kc^T        128 x 128, reduction 576 streamed in nine 64-column chunks of Q and Kc through
-//                      a 3-stage TMA ring; 36 tcgen05.mma (bf16, N = 128, K = 16) into one of two
+//                      a 5-stage TMA ring; 36 tcgen05.mma (bf16, N = 128, K = 16) into one of two
 //                      128-column TMEM buffers;
 //   P  = softmax step  four warps, one thread per row: two sweeps over the S buffer (row maximum,
-//                      then exp2), causal mask, running (m, l); P is written to shared memory as
-//                      bf16 in the 128-byte-swizzled K-major operand layout, alpha = 2^(m_old-m_new)
-//                      beside it;
-//   PV = P Vt^T        128 x 256, 8 MMAs (N = 256) into a 256-column TMEM buffer, NOT accumulated:
+//                      then exp2), causal mask, running (m, l); P is written back with tcgen05.st as
+//                      packed bf16 pairs over the first 64 columns of the S buffer it was read from,
+//                      alpha = 2^(m_old-m_new) goes to shared memory;
+//   PV = P Vt^T        128 x 256, 8 MMAs (N = 256) with the A operand (P) taken from TMEM, into a
+//                      256-column TMEM buffer, NOT accumulated; their commit frees the S buffer;
 //   O  = O alpha + PV  eight warps hold the 128 x 256 fp32 O tile in registers (128 per thread) and
 //                      fold every PV tile in -- no rescaling of TMEM contents.
-// S of tile j+1 is issued before PV of tile j, so the MMAs of one overlap the softmax of the other.
-// Warps: 0-7 O accumulation (setmaxnreg 184), 8-11 softmax (104), 12 Q/K producer, 13 MMA issuer,
-// 14 V producer, 15 idle (40). Rows of a partial last tile and keys past the causal limit are
-// masked; every mbarrier wait is bounded and a timeout sets the status word.
+// S of tile j+1 streams in while the softmax works on tile j; PV of tile j is issued by a thread of
+// its own as soon as P is complete. The kernel is bound by the bytes that cross shared memory (TMA
+// writes + MMA operand reads, 128 B/clk per SM), which is why P stays in TMEM.
+// Warps: 0-7 O accumulation (setmaxnreg 184), 8-11 softmax (104), 12 Q/K producer, 13 S issuer,
+// 14 V producer, 15 PV issuer (40). Rows of a partial last tile and keys past the causal limit are
+// masked; every mbarrier wait is bounded and a timeout sets the status word. Shared memory: ring
+// 160 KB + Vt tile 64 KB + 3 KB (alpha, l, mbarriers) = the whole 227 KB, none of it static.
 #include "mla_prefill_tc.h"
 
 #include <cuda_bf16.h>
