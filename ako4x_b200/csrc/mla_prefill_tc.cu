@@ -149,7 +149,9 @@ mla_prefill_tc_kernel(PfParams p, const __grid_constant__ CUtensorMap tm_qn, con
   int* s_work = reinterpret_cast<int*>(bars + 2 * NST + 11);  // sequence, tile inside the sequence (or -1)
 
   if (tid == 0) {
-    int t = blockIdx.x, b = 0;
+    // reversed: within a sequence the later query tiles see more keys, so the long CTAs start
+    // first and the short ones fill the end of the grid
+    int t = (int)(gridDim.x - 1 - blockIdx.x), b = 0;
     for (; b < p.batch; ++b) {
       const int nt = (p.qo_indptr[b + 1] - p.qo_indptr[b] + QT - 1) / QT;
       if (t < nt) break;
@@ -320,6 +322,11 @@ mla_prefill_tc_kernel(PfParams p, const __grid_constant__ CUtensorMap tm_qn, con
       m = m_new;
       alpha_s[(j & 3) * BM + r] = alpha;
       ako::tc::fence_before_thread_sync();
+      // Nothing else holds a fast warp back (tiles without masked keys take the short path, a warp
+      // with masked rows does not), so it may finish tile j before a slow warp has finished tile
+      // j-1; its arrival would then complete the phase of tile j-1 in the slow warp's place. Wait
+      // until all four warps have arrived for tile j-1 before arriving for tile j.
+      if (j > 0 && !ako::tc::mbar_wait(ako::smem_u32(&p_full), (uint32_t)((j - 1) & 1), &g_pf_status, 4)) { ok = false; break; }
       __syncwarp();
       if (lane == 0) ako::tc::mbar_arrive(ako::smem_u32(&p_full));
     }

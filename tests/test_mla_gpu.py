@@ -111,6 +111,23 @@ def test_prefill_last_query_equals_decode(built_lib):
     assert torch.isfinite(lse).all()
 
 
+def test_prefill_repeatable_full_size(built_lib):
+    """Twenty calls on the full-size ragged batch give bit-identical outputs. The batch has a last
+    query tile of 7 tokens, i.e. a softmax warp with masked rows beside three warps on the short
+    unmasked path: the warps of one CTA then run a whole key tile apart, which is the timing that
+    once let a fast warp's mbarrier arrival stand in for a slow warp's."""
+    a = W.make_mla_prefill(8, shape_id=2, device="cuda")
+    small = W.make_mla_prefill(3, device="cuda", q_lens=[64, 200, 9], kv_lens=[64, 1000, 500], extra_pages=64)
+    o0, lse0 = mla_prefill.run(*[a[k] for k in PKEYS])
+    o0, lse0 = o0.clone(), lse0.clone()
+    for _ in range(20):
+        mla_prefill.run(*[small[k] for k in PKEYS])
+        o, lse = mla_prefill.run(*[a[k] for k in PKEYS])
+        assert torch.equal(o, o0)
+        assert torch.equal(lse, lse0)
+    assert torch.isfinite(o0.float()).all()
+
+
 # ---- DSA sparse attention ----------------------------------------------------------------------
 def test_sparse_golden(built_lib):
     g = load_golden("dsa_attention_t4")
