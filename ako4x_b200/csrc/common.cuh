@@ -4,6 +4,9 @@
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
 #include <stdint.h>
+
+#include <atomic>
+
 #include "../../include/ako4x_b200.h"
 
 #define AKO_LOG2E 1.4426950408889634f
@@ -98,16 +101,29 @@ __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.lau
 // the call.
 template <auto kernel>
 inline bool ensure_dynamic_smem(int bytes) {
-  static bool done[64] = {};
+  static std::atomic<bool> done[64] = {};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
-  if (!done[dev]) {
+  if (!done[dev].load(std::memory_order_acquire)) {
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) !=
         cudaSuccess)
       return false;
-    done[dev] = true;
+    done[dev].store(true, std::memory_order_release);
   }
   return true;
+}
+
+// Number of SMs of the current device, looked up once per device (148 when the query fails).
+inline int sm_count() {
+  static std::atomic<int> cached[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  int n = cached[dev].load(std::memory_order_relaxed);
+  if (n == 0) {
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev].store(n, std::memory_order_relaxed);
+  }
+  return n;
 }
 
 }  // namespace ako

@@ -5,11 +5,12 @@
 // on the N dimension, TMA-fed, relu + head weights + head sum as per-thread arithmetic on the
 // accumulator. Scores are written as fp32.
 //
-// Select kernel: one CTA per row. Keys are the order-preserving unsigned image of the fp32 scores;
-// a 4 x 8-bit most-significant-digit radix select (warp-aggregated shared-memory histograms)
-// finds the 2048-th largest key, then a stable compaction in token order emits every token above
-// the threshold plus the first tokens equal to it (ties: lower position wins), translated to
-// global cache slots through the block table.
+// Select kernel: one CTA per row. Keys are the order-preserving unsigned image of the fp32 scores,
+// read once into shared memory; a three-pass most-significant-digit radix select (11, 11 and 10
+// bits; the heavily repeated leading digit is warp-aggregated) finds the 2048-th largest key, then
+// a stable compaction in token order emits every token above the threshold plus the first tokens
+// equal to it (ties: lower position wins), translated to global cache slots through the block
+// table.
 #include "common.cuh"
 #include "tcgen05.cuh"
 #include "tma_host.cuh"
@@ -237,18 +238,6 @@ __global__ void __launch_bounds__(SEL_THREADS, 1) dsa_select_kernel(
   }
 }
 
-int sm_count() {
-  static int cached[64] = {};
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
-  if (cached[dev] == 0) {
-    int n = 0;
-    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-    cached[dev] = n;
-  }
-  return cached[dev];
-}
-
 int launch_scores(const void* q, const void* cache, const float* weights, const int32_t* seq_lens,
                   const int32_t* block_table, float* scores, int64_t rows, int64_t max_pages,
                   int64_t num_cache_pages, int skip_short, cudaStream_t st) {
@@ -269,7 +258,7 @@ int launch_scores(const void* q, const void* cache, const float* weights, const 
   p.num_cache_pages = num_cache_pages;
   p.skip_short = skip_short;
   const int64_t units = ako::cdiv(rows, TS_ROWS) * ako::cdiv(max_pages, 2);
-  const int grid = (int)(units < sm_count() ? units : sm_count());
+  const int grid = (int)(units < ako::sm_count() ? units : ako::sm_count());
   dsa_score_tc_kernel<<<grid, TS_THREADS, TS_SMEM, st>>>(p, tm_q, tm_k);
   AKO_CHECK_LAUNCH();
   return AKO4X_OK;
@@ -324,6 +313,7 @@ extern "C" int ako4x_dsa_topk_select(const float* scores, const int32_t* seq_len
   if (bad_dims(rows, max_pages)) return AKO4X_EINVAL;
   if (rows == 0) return AKO4X_OK;
   if (!scores || !seq_lens || !block_table || !topk_indices) return AKO4X_EINVAL;
+  if ((uintptr_t)scores & 15) return AKO4X_EINVAL;  // rows are read as float4
   return launch_select(scores, seq_lens, block_table, topk_indices, rows, max_pages, false,
                        (cudaStream_t)stream);
 }

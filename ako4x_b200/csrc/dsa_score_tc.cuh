@@ -109,6 +109,7 @@ dsa_score_tc_kernel(ScoreParams p, const __grid_constant__ CUtensorMap tm_q, con
   __shared__ __align__(8) uint64_t s_slot_full[TS_SLOTS];
   __shared__ __align__(8) uint64_t s_slot_empty[TS_SLOTS];
   __shared__ uint32_t s_tmem_base;
+  __shared__ int s_err;  // code of a wait of this CTA that gave up (0 = none), published on exit
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   unsigned char* smem_al = smem_raw + ((1024u - (ako::smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -120,6 +121,7 @@ dsa_score_tc_kernel(ScoreParams p, const __grid_constant__ CUtensorMap tm_q, con
   const uint32_t slot_base = ako::smem_u32(slot_ptr);
 
   if (tid == 0) {
+    s_err = 0;
     for (int s = 0; s < TS_A_STAGES; ++s) {
       ako::tc::mbar_init(ako::smem_u32(&s_a_full[s]), 1);
       ako::tc::mbar_init(ako::smem_u32(&s_a_empty[s]), TS_ACCS);  // every issuer passes every key tile
@@ -258,7 +260,7 @@ dsa_score_tc_kernel(ScoreParams p, const __grid_constant__ CUtensorMap tm_q, con
           const int slot = rc.uo % TS_SLOTS, stage = a % TS_A_STAGES;
           if (rc.d.flags & TS_F_NEWGROUP) {
             // one query buffer: group qc is loaded once everybody has handed back group qc-1
-            ok = ako::tc::mbar_wait(ako::smem_u32(&s_q_empty), (uint32_t)((rc.d.qc & 1) ^ 1), &g_dsa_status, 1);
+            ok = ako::tc::mbar_wait(ako::smem_u32(&s_q_empty), (uint32_t)((rc.d.qc & 1) ^ 1), &s_err, 1);
             if (ok) {
               const uint32_t bar = ako::smem_u32(&s_q_full);
               ako::tc::mbar_arrive_expect_tx(bar, TS_Q_BYTES + TS_W_BYTES);
@@ -271,7 +273,7 @@ dsa_score_tc_kernel(ScoreParams p, const __grid_constant__ CUtensorMap tm_q, con
             }
           }
           // every key tile of the unit waits for the slot: the tiles of one unit may be issued together
-          ok = ok && ako::tc::mbar_wait(ako::smem_u32(&s_slot_empty[slot]), (uint32_t)(((rc.uo / TS_SLOTS) & 1) ^ 1), &g_dsa_status, 2);
+          ok = ok && ako::tc::mbar_wait(ako::smem_u32(&s_slot_empty[slot]), (uint32_t)(((rc.uo / TS_SLOTS) & 1) ^ 1), &s_err, 2);
           if (ok) {
             const uint32_t sbar = ako::smem_u32(&s_slot_full[slot]);
             if (rc.sub == 0) {
@@ -283,7 +285,7 @@ dsa_score_tc_kernel(ScoreParams p, const __grid_constant__ CUtensorMap tm_q, con
               const uint32_t sdst = slot_base + slot * TS_SLOT_BYTES + rc.sub * TS_SCALE_BYTES;
               ako::tc::bulk_load_1d(sdst, p.cache + (int64_t)rc.pa * PAGE_BYTES + PS * HD, PS * 4, sbar);
               ako::tc::bulk_load_1d(sdst + PS * 4, p.cache + (int64_t)rc.pb * PAGE_BYTES + PS * HD, PS * 4, sbar);
-              ok = ako::tc::mbar_wait(ako::smem_u32(&s_a_empty[stage]), (uint32_t)(((a / TS_A_STAGES) & 1) ^ 1), &g_dsa_status, 3);
+              ok = ako::tc::mbar_wait(ako::smem_u32(&s_a_empty[stage]), (uint32_t)(((a / TS_A_STAGES) & 1) ^ 1), &s_err, 3);
               if (ok) {
                 const uint32_t bar = ako::smem_u32(&s_a_full[stage]);
                 const uint32_t dst = a_base + stage * TS_A_BYTES;
@@ -322,14 +324,14 @@ dsa_score_tc_kernel(ScoreParams p, const __grid_constant__ CUtensorMap tm_q, con
       auto prepare = [&](Tile& t) -> int {
         if (sub == subs) {  // next unit
           const int slot = n % TS_SLOTS;
-          if (!ako::tc::mbar_wait(ako::smem_u32(&s_slot_full[slot]), (uint32_t)((n / TS_SLOTS) & 1), &g_dsa_status, 4)) return -1;
+          if (!ako::tc::mbar_wait(ako::smem_u32(&s_slot_full[slot]), (uint32_t)((n / TS_SLOTS) & 1), &s_err, 4)) return -1;
           const volatile ScoreDesc* dp = reinterpret_cast<const volatile ScoreDesc*>(slot_ptr + slot * TS_SLOT_BYTES + TS_ROWS * TS_SCALE_BYTES);
           const int flags = dp->flags, qc = dp->qc;
           ac = dp->ac0;
           ako::tc::mbar_arrive(ako::smem_u32(&s_slot_empty[slot]));
           if (flags & TS_F_END) return 0;
           if ((flags & TS_F_NEWGROUP) &&
-              !ako::tc::mbar_wait(ako::smem_u32(&s_q_full), (uint32_t)(qc & 1), &g_dsa_status, 5)) return -1;
+              !ako::tc::mbar_wait(ako::smem_u32(&s_q_full), (uint32_t)(qc & 1), &s_err, 5)) return -1;
           shared = flags & TS_F_SHARED;
           last_unit = flags & TS_F_LASTGROUP;
           subs = shared ? 1 : TS_ROWS;
@@ -340,7 +342,7 @@ dsa_score_tc_kernel(ScoreParams p, const __grid_constant__ CUtensorMap tm_q, con
         // Tiles of the other row pairs are waited for as well: the stage's release counts all
         // issuers, and this keeps an issuer from arriving for the stage's next use too early.
         const int stage = ac % TS_A_STAGES;
-        if (!ako::tc::mbar_wait(ako::smem_u32(&s_a_full[stage]), (uint32_t)((ac / TS_A_STAGES) & 1), &g_dsa_status, 7)) return -1;
+        if (!ako::tc::mbar_wait(ako::smem_u32(&s_a_full[stage]), (uint32_t)((ac / TS_A_STAGES) & 1), &s_err, 7)) return -1;
         ako::tc::fence_after_thread_sync();
         t.mma = shared || (sub >> 1) == me;
         t.a_lo = a_lo0 + stage * (TS_A_BYTES >> 4);
@@ -361,7 +363,7 @@ dsa_score_tc_kernel(ScoreParams p, const __grid_constant__ CUtensorMap tm_q, con
         if (cur.mma) {
           // This issuer's units share one accumulator: the team must have read the previous result.
           if (cur.acc_wait >= 0 &&
-              !ako::tc::mbar_wait(ako::smem_u32(&s_acc_empty[me]), (uint32_t)cur.acc_wait, &g_dsa_status, 6)) break;
+              !ako::tc::mbar_wait(ako::smem_u32(&s_acc_empty[me]), (uint32_t)cur.acc_wait, &s_err, 6)) break;
           ako::tc::mma_f8_lohi<false>(cur.d, cur.a_lo, cur.b_lo, cur.idesc);  // K = 32 slices: +32 B = +2
           ako::tc::mma_f8_lohi<true>(cur.d, cur.a_lo + 2, cur.b_lo + 2, cur.idesc);
           if (!cur.q_done) r = prepare(nxt);
@@ -393,13 +395,13 @@ dsa_score_tc_kernel(ScoreParams p, const __grid_constant__ CUtensorMap tm_q, con
     for (int n = 0;; ++n) {
       const int slot = n % TS_SLOTS;
       const unsigned char* sp = slot_ptr + slot * TS_SLOT_BYTES;
-      if (!ako::tc::mbar_wait(ako::smem_u32(&s_slot_full[slot]), (uint32_t)((n / TS_SLOTS) & 1), &g_dsa_status, 8)) break;
+      if (!ako::tc::mbar_wait(ako::smem_u32(&s_slot_full[slot]), (uint32_t)((n / TS_SLOTS) & 1), &s_err, 8)) break;
       const int4 d0 = *reinterpret_cast<const int4*>(sp + TS_ROWS * TS_SCALE_BYTES);  // row0, pp, flags, qc
       const int row0 = d0.x, pp = d0.y, flags = d0.z, qc = d0.w;
       if (flags & TS_F_END) break;
       const int2 sl2 = *reinterpret_cast<const int2*>(sp + TS_ROWS * TS_SCALE_BYTES + 16 + team * 8);  // sl[2*team], +1
       if (flags & TS_F_NEWGROUP) {
-        if (!ako::tc::mbar_wait(ako::smem_u32(&s_q_full), (uint32_t)(qc & 1), &g_dsa_status, 9)) break;
+        if (!ako::tc::mbar_wait(ako::smem_u32(&s_q_full), (uint32_t)(qc & 1), &s_err, 9)) break;
 #pragma unroll
         for (int i = 0; i < 2; ++i)
           orow[i] = p.scores + (int64_t)min(row0 + team * 2 + i, p.rows - 1) * p.max_pages * PS;
@@ -413,7 +415,7 @@ dsa_score_tc_kernel(ScoreParams p, const __grid_constant__ CUtensorMap tm_q, con
       __syncwarp();
       if (lane == 0) ako::tc::mbar_arrive(ako::smem_u32(&s_slot_empty[slot]));
 
-      if (!ako::tc::mbar_wait(ako::smem_u32(&s_acc_full[team]), (uint32_t)(n & 1), &g_dsa_status, 10)) break;
+      if (!ako::tc::mbar_wait(ako::smem_u32(&s_acc_full[team]), (uint32_t)(n & 1), &s_err, 10)) break;
       ako::tc::fence_after_thread_sync();
       // 32 accumulator columns per step: row (c>>1) of this thread's pair, heads 32*(c&1)...
       // relu is one instruction per element; the weighted sums go two elements per instruction
@@ -458,6 +460,7 @@ dsa_score_tc_kernel(ScoreParams p, const __grid_constant__ CUtensorMap tm_q, con
 
   ako::tc::fence_before_thread_sync();
   __syncthreads();
+  if (tid == 0 && s_err != 0) atomicCAS(&g_dsa_status, 0, s_err);
   if (warp == TS_MMA_WARP) {
     ako::tc::fence_after_thread_sync();
     ako::tc::tmem_dealloc(tmem_base, 512);

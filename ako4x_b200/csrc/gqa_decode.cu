@@ -56,6 +56,7 @@ struct Params {
 __global__ void __launch_bounds__(THREADS, CTAS_PER_SM) gqa_decode_kernel(Params p) {
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ __align__(8) uint64_t s_full[STAGES];
+  __shared__ int s_err;  // code of a wait of this CTA that gave up (0 = none), published on exit
 
   int split, half, b, item = 0;
   if (p.items) {
@@ -103,6 +104,7 @@ __global__ void __launch_bounds__(THREADS, CTAS_PER_SM) gqa_decode_kernel(Params
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) ako::tc::mbar_init(ako::smem_u32(&s_full[s]), 1);
     ako::tc::mbar_init_fence();
+    s_err = 0;
   }
   ako::tc::fence_proxy_async_smem();  // the zero fill is ordered before the bulk copies
   __syncthreads();
@@ -166,7 +168,7 @@ __global__ void __launch_bounds__(THREADS, CTAS_PER_SM) gqa_decode_kernel(Params
   for (int it = 0; it < ntiles; ++it) {
     const int stage = it % STAGES;
     const bool landed = ako::tc::mbar_wait(ako::smem_u32(&s_full[stage]), (uint32_t)((it / STAGES) & 1),
-                                           &g_gqa_status, 1);
+                                           &s_err, 1);
     // every warp has finished tile it-1: its stage is free for tile it+STAGES-1
     if (!__syncthreads_and(landed)) break;  // a wait gave up: the whole CTA stops consuming
     if (warp == 0) {
@@ -244,6 +246,7 @@ __global__ void __launch_bounds__(THREADS, CTAS_PER_SM) gqa_decode_kernel(Params
       }
     }
   }
+  if (threadIdx.x == 0 && s_err != 0) atomicCAS(&g_gqa_status, 0, s_err);
 
   if (g < GROUP) {
     const int64_t rh = (int64_t)b * HQ + kvh * GROUP + g;
@@ -298,14 +301,20 @@ __global__ void __launch_bounds__(256) gqa_plan_kernel(const int32_t* __restrict
     }
     const int start = s_base + s_scan[tid] - n;
     if (b < batch) {
-      item_start[b] = start;
+      // kv_indptr[batch] beyond the num_kv_indices the workspace was sized for: the list is cut at
+      // max_items (those sequences lose their tail), the merge stays inside the partial area, and
+      // the status word records it.
+      item_start[b] = min(start, max_items);
       for (int c = 0; c < n && start + c < max_items; ++c) items[start + c] = make_int2(b, c);
     }
     __syncthreads();
     if (tid == 255) s_base += s_scan[255];
     __syncthreads();
   }
-  if (tid == 0) item_start[batch] = s_base;
+  if (tid == 0) {
+    item_start[batch] = min(s_base, max_items);
+    if (s_base > max_items) atomicCAS(&g_gqa_status, 0, 20);
+  }
   for (int i = s_base + tid; i < max_items; i += 256) items[i] = make_int2(-1, -1);
 }
 

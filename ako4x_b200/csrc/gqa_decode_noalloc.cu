@@ -17,6 +17,8 @@
 //     at zero;
 //   * the first call on each device resolves the array's device address (cudaGetSymbolAddress).
 //     Make that first call during start-up, before any stream capture begins.
+#include <atomic>
+
 #include "common.cuh"
 
 namespace {
@@ -29,19 +31,19 @@ static __device__ __align__(256) unsigned char g_gqa_scratch[kScratchBytes];
 
 // Device address of g_gqa_scratch on the current device, resolved once per device.
 int scratch_address(void** out) {
-  static void* addr[64] = {};
+  static std::atomic<void*> addr[64] = {};  // host threads may race here: the value is idempotent
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return AKO4X_ELAUNCH;
-  if (addr[dev] == nullptr) {
+  if (addr[dev].load(std::memory_order_acquire) == nullptr) {
     void* p = nullptr;
     // the device `dev` is current here, so the address belongs to its copy of the array
     if (cudaGetSymbolAddress(&p, g_gqa_scratch) != cudaSuccess || p == nullptr) {
       (void)cudaGetLastError();
       return AKO4X_ELAUNCH;
     }
-    addr[dev] = p;
+    addr[dev].store(p, std::memory_order_release);
   }
-  *out = addr[dev];
+  *out = addr[dev].load(std::memory_order_acquire);
   return AKO4X_OK;
 }
 

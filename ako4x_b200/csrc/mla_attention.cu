@@ -102,6 +102,7 @@ __global__ void __launch_bounds__(THREADS, 1) mla_attention_kernel(Params p) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   __shared__ __align__(8) uint64_t s_full[STAGES];
   __shared__ uint32_t s_valid[STAGES][2];  // per stage: which of the 64 tokens were copied
+  __shared__ int s_err;  // code of a wait of this CTA that gave up (0 = none), published on exit
   float* sbuf = reinterpret_cast<float*>(smem_raw + STAGES * STAGE_BYTES);
   const uint32_t smem_base = ako::smem_u32(smem_raw);
 
@@ -129,6 +130,7 @@ __global__ void __launch_bounds__(THREADS, 1) mla_attention_kernel(Params p) {
     // thread that fires when its kpe cp.async copies have landed
     for (int s = 0; s < STAGES; ++s) ako::tc::mbar_init(ako::smem_u32(&s_full[s]), 2 + THREADS);
     ako::tc::mbar_init_fence();
+    s_err = 0;
   }
   ako::tc::fence_proxy_async_smem();
   __syncthreads();
@@ -224,7 +226,7 @@ __global__ void __launch_bounds__(THREADS, 1) mla_attention_kernel(Params p) {
   for (int it = 0; it < ntiles; ++it) {
     const int stage = it & 1;
     const bool landed = ako::tc::mbar_wait(ako::smem_u32(&s_full[stage]), (uint32_t)((it >> 1) & 1),
-                                           &g_mla_status, 1);
+                                           &s_err, 1);
     // every warp has finished tile it-1: its stage (and s_valid entry) is free for tile it+1
     if (!__syncthreads_and(landed)) break;
     if (it + 1 < ntiles) {
@@ -343,6 +345,7 @@ __global__ void __launch_bounds__(THREADS, 1) mla_attention_kernel(Params p) {
   }
 
   // ---- epilogue ---------------------------------------------------------------------------------
+  if (threadIdx.x == 0 && s_err != 0) atomicCAS(&g_mla_status, 0, s_err);
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
     const int64_t rh = row * H + g + 8 * r;

@@ -147,6 +147,7 @@ mla_prefill_tc_kernel(PfParams p, const __grid_constant__ CUtensorMap tm_qn, con
   uint64_t& fin = bars[2 * NST + 9];
   uint32_t& s_tmem = *reinterpret_cast<uint32_t*>(bars + 2 * NST + 10);
   int* s_work = reinterpret_cast<int*>(bars + 2 * NST + 11);  // sequence, tile inside the sequence (or -1)
+  int* s_err = s_work + 2;  // code of a wait of this CTA that gave up (0 = none), published on exit
 
   if (tid == 0) {
     // reversed: within a sequence the later query tiles see more keys, so the long CTAs start
@@ -159,6 +160,7 @@ mla_prefill_tc_kernel(PfParams p, const __grid_constant__ CUtensorMap tm_qn, con
     }
     s_work[0] = b;
     s_work[1] = (b < p.batch) ? t : -1;
+    *s_err = 0;
     for (int s = 0; s < NST; ++s) {
       ako::tc::mbar_init(ako::smem_u32(&st_full[s]), 1);
       ako::tc::mbar_init(ako::smem_u32(&st_empty[s]), 1);
@@ -209,7 +211,7 @@ mla_prefill_tc_kernel(PfParams p, const __grid_constant__ CUtensorMap tm_qn, con
     for (int i = 0; i < 128; ++i) o[i] = 0.f;
     bool ok = true;
     for (int j = 0; j < ntk; ++j) {
-      if (!ako::tc::mbar_wait(ako::smem_u32(&pv_full), (uint32_t)(j & 1), &g_pf_status, 1)) { ok = false; break; }
+      if (!ako::tc::mbar_wait(ako::smem_u32(&pv_full), (uint32_t)(j & 1), s_err, 1)) { ok = false; break; }
       ako::tc::fence_after_thread_sync();
       const float a = alpha_s[(j & 3) * BM + r];
 #pragma unroll
@@ -226,7 +228,7 @@ mla_prefill_tc_kernel(PfParams p, const __grid_constant__ CUtensorMap tm_qn, con
         for (int i = 0; i < 32; ++i) o[32 * c + i] = fmaf(o[32 * c + i], a, v[i]);
       }
     }
-    if (ok && tile >= 0 && ako::tc::mbar_wait(ako::smem_u32(&fin), 0u, &g_pf_status, 2)) {
+    if (ok && tile >= 0 && ako::tc::mbar_wait(ako::smem_u32(&fin), 0u, s_err, 2)) {
       const int qtok = r >> 4;
       if (qtok < nq) {
         const float l = fin_l[r];
@@ -255,7 +257,7 @@ mla_prefill_tc_kernel(PfParams p, const __grid_constant__ CUtensorMap tm_qn, con
     bool ok = true;
     for (int j = 0; j < ntk; ++j) {
       const int buf = j & 1;
-      if (!ako::tc::mbar_wait(ako::smem_u32(&s_full[buf]), (uint32_t)((j >> 1) & 1), &g_pf_status, 3)) { ok = false; break; }
+      if (!ako::tc::mbar_wait(ako::smem_u32(&s_full[buf]), (uint32_t)((j >> 1) & 1), s_err, 3)) { ok = false; break; }
       ako::tc::fence_after_thread_sync();
       const uint32_t ts = tq + buf * BK;
       const int nvis = kv_lim - j * BK;  // visible keys of this tile for this row (may be <= 0 or > 128)
@@ -326,7 +328,7 @@ mla_prefill_tc_kernel(PfParams p, const __grid_constant__ CUtensorMap tm_qn, con
       // with masked rows does not), so it may finish tile j before a slow warp has finished tile
       // j-1; its arrival would then complete the phase of tile j-1 in the slow warp's place. Wait
       // until all four warps have arrived for tile j-1 before arriving for tile j.
-      if (j > 0 && !ako::tc::mbar_wait(ako::smem_u32(&p_full), (uint32_t)((j - 1) & 1), &g_pf_status, 4)) { ok = false; break; }
+      if (j > 0 && !ako::tc::mbar_wait(ako::smem_u32(&p_full), (uint32_t)((j - 1) & 1), s_err, 4)) { ok = false; break; }
       __syncwarp();
       if (lane == 0) ako::tc::mbar_arrive(ako::smem_u32(&p_full));
     }
@@ -349,7 +351,7 @@ mla_prefill_tc_kernel(PfParams p, const __grid_constant__ CUtensorMap tm_qn, con
         bool ok = true;
         for (int c = 0; c < NCH; ++c, ++g) {
           const int stage = g % NST;
-          if (!ako::tc::mbar_wait(ako::smem_u32(&st_empty[stage]), (uint32_t)(((g / NST) & 1) ^ 1), &g_pf_status, 5)) { ok = false; break; }
+          if (!ako::tc::mbar_wait(ako::smem_u32(&st_empty[stage]), (uint32_t)(((g / NST) & 1) ^ 1), s_err, 5)) { ok = false; break; }
           const uint32_t bar = ako::smem_u32(&st_full[stage]);
           const uint32_t dst = st_base + stage * ST_BYTES;
           ako::tc::mbar_arrive_expect_tx(bar, ST_BYTES);
@@ -363,7 +365,7 @@ mla_prefill_tc_kernel(PfParams p, const __grid_constant__ CUtensorMap tm_qn, con
       // ================================ V producer ==============================================
       ako::tc::tma_prefetch_desc(&tm_v);
       for (int j = 0; j < ntk; ++j) {
-        if (!ako::tc::mbar_wait(ako::smem_u32(&v_empty), (uint32_t)((j & 1) ^ 1), &g_pf_status, 6)) break;
+        if (!ako::tc::mbar_wait(ako::smem_u32(&v_empty), (uint32_t)((j & 1) ^ 1), s_err, 6)) break;
         const uint32_t bar = ako::smem_u32(&v_full);
         ako::tc::mbar_arrive_expect_tx(bar, V_BYTES);
         const int x = (int)(vbase + (int64_t)j * BK);
@@ -378,12 +380,12 @@ mla_prefill_tc_kernel(PfParams p, const __grid_constant__ CUtensorMap tm_qn, con
       for (int j = 0; j < ntk; ++j) {
         const int buf = j & 1;
         // the PV MMAs of tile j-2 have read P out of this buffer
-        if (!ako::tc::mbar_wait(ako::smem_u32(&s_empty[buf]), (uint32_t)(((j >> 1) & 1) ^ 1), &g_pf_status, 7)) break;
+        if (!ako::tc::mbar_wait(ako::smem_u32(&s_empty[buf]), (uint32_t)(((j >> 1) & 1) ^ 1), s_err, 7)) break;
         const uint32_t d = tmem + buf * BK;
         bool ok = true;
         for (int c = 0; c < NCH; ++c, ++g) {
           const int stage = g % NST;
-          if (!ako::tc::mbar_wait(ako::smem_u32(&st_full[stage]), (uint32_t)((g / NST) & 1), &g_pf_status, 8)) { ok = false; break; }
+          if (!ako::tc::mbar_wait(ako::smem_u32(&st_full[stage]), (uint32_t)((g / NST) & 1), s_err, 8)) { ok = false; break; }
           ako::tc::fence_after_thread_sync();
           const uint32_t a_lo = st_lo0 + stage * (ST_BYTES >> 4);
           const uint32_t b_lo = a_lo + (CH_BYTES >> 4);
@@ -402,9 +404,9 @@ mla_prefill_tc_kernel(PfParams p, const __grid_constant__ CUtensorMap tm_qn, con
       constexpr uint32_t IDESC_PV = ako::tc::idesc_bf16_f32(BM, 256);
       const uint32_t v_lo0 = ako::tc::smem_desc_lo(v_base);
       for (int j = 0; j < ntk; ++j) {
-        if (!ako::tc::mbar_wait(ako::smem_u32(&p_full), (uint32_t)(j & 1), &g_pf_status, 9)) break;
-        if (!ako::tc::mbar_wait(ako::smem_u32(&v_full), (uint32_t)(j & 1), &g_pf_status, 10)) break;
-        if (!ako::tc::mbar_wait(ako::smem_u32(&pv_empty), (uint32_t)((j & 1) ^ 1), &g_pf_status, 11)) break;
+        if (!ako::tc::mbar_wait(ako::smem_u32(&p_full), (uint32_t)(j & 1), s_err, 9)) break;
+        if (!ako::tc::mbar_wait(ako::smem_u32(&v_full), (uint32_t)(j & 1), s_err, 10)) break;
+        if (!ako::tc::mbar_wait(ako::smem_u32(&pv_empty), (uint32_t)((j & 1) ^ 1), s_err, 11)) break;
         ako::tc::fence_after_thread_sync();
         const uint32_t d = tmem + 256;
 #pragma unroll
@@ -422,6 +424,7 @@ mla_prefill_tc_kernel(PfParams p, const __grid_constant__ CUtensorMap tm_qn, con
 
   ako::tc::fence_before_thread_sync();
   __syncthreads();
+  if (tid == 0 && *s_err != 0) atomicCAS(&g_pf_status, 0, *s_err);
   if (warp == 13) {
     ako::tc::fence_after_thread_sync();
     ako::tc::tmem_dealloc(tmem, 512);

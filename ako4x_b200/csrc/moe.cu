@@ -371,18 +371,6 @@ int launch_gemms_tc(const GemmParams& p1, const GemmParams& p2, int64_t cap, int
   return AKO4X_OK;
 }
 
-int sm_count() {
-  static int cached[64] = {};
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
-  if (cached[dev] == 0) {
-    int n = 0;
-    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-    cached[dev] = n;
-  }
-  return cached[dev];
-}
-
 }  // namespace
 
 extern "C" size_t ako4x_moe_fp8_block_scale_workspace_bytes(int64_t tokens, int64_t num_local_experts) {
@@ -467,7 +455,7 @@ extern "C" int ako4x_moe_fp8_block_scale_staged(
   p2.w_scale = gemm2_weights_scale;
   p2.y = w.y;
   p2.a_scale_stride = cap;
-  const int sms = sm_count();
+  const int sms = ako::sm_count();
   mark(1);
   int rc;
   moe_permute_kernel<<<(unsigned)ako::cdiv(tokens * TOPK, 8), 256, 0, st>>>(

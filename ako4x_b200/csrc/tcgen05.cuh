@@ -34,6 +34,10 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
 }
 // Waits for the phase with the given parity. Returns false when `*err` is already set or when the
 // cycle limit is reached (then `*err` is set to `code`); the caller must unwind, not retry.
+// `err` is a word that starts every launch at 0: a shared-memory word of the CTA (which the kernel
+// copies into its device status word on exit) or a word of the call's workspace that the call
+// clears. A status word that outlives the call must not be passed here: once set, it would make
+// every later launch give up its waits early.
 constexpr long long kWaitLimitCycles = 400000000LL;  // ~0.2 s at 1.9 GHz
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* err, int code) {
   if (mbar_test_wait(bar, parity)) return true;

@@ -20,13 +20,15 @@ def run(q_nope, q_pe, ckv_cache, kpe_cache, sparse_indices, sm_scale):
     topk = sparse_indices.shape[1]
     rows = ckv_cache.shape[0] * ckv_cache.shape[1]
     L = _cabi.lib()
-    o = torch.empty_like(q_nope)
+    o = torch.empty(q_nope.shape, dtype=q_nope.dtype, device=q_nope.device)
     lse = torch.empty((tokens, 16), dtype=torch.float32, device=q_nope.device)
     ws_bytes = L.ako4x_dsa_sparse_attention_workspace_bytes(tokens, topk)
     ws = _cabi.workspace(ws_bytes, q_nope.device)
+    qn, qp, idx = q_nope.contiguous(), q_pe.contiguous(), sparse_indices.contiguous()
     st = L.ako4x_dsa_sparse_attention(
-        _cabi.ptr(q_nope.contiguous()), _cabi.ptr(q_pe.contiguous()), _cabi.ptr(ckv_cache),
-        _cabi.ptr(kpe_cache), _cabi.ptr(sparse_indices.contiguous()), float(sm_scale),
+        _cabi.ptr(qn), _cabi.ptr(qp), _cabi.ptr(ckv_cache),
+        _cabi.ptr(kpe_cache), _cabi.ptr(idx), float(sm_scale),
         _cabi.ptr(o), _cabi.ptr(lse), tokens, topk, rows, _cabi.ptr(ws), ws_bytes, _cabi.stream())
+    del qn, qp, idx
     _cabi.check(st, "ako4x_dsa_sparse_attention")
     return o, lse

@@ -39,11 +39,11 @@ def run(q_index_fp8, k_index_cache_fp8, weights, seq_lens, block_table):
     out = torch.empty((rows, TOPK), dtype=torch.int32, device=dev)
     ws_bytes = L.ako4x_dsa_topk_indexer_workspace_bytes(rows, max_pages)
     ws = _cabi.workspace(ws_bytes, dev)
+    keep = [t.contiguous() for t in (q_index_fp8, k_index_cache_fp8, weights, seq_lens, block_table)]
     st = L.ako4x_dsa_topk_indexer(
-        _cabi.ptr(q_index_fp8.contiguous()), _cabi.ptr(k_index_cache_fp8.contiguous()),
-        _cabi.ptr(weights.contiguous()), _cabi.ptr(seq_lens.contiguous()),
-        _cabi.ptr(block_table.contiguous()), _cabi.ptr(out), rows, max_pages, npages,
+        *[_cabi.ptr(t) for t in keep], _cabi.ptr(out), rows, max_pages, npages,
         _cabi.ptr(ws), ws_bytes, _cabi.stream())
+    del keep   # contiguous copies live until the launch has been enqueued
     _cabi.check(st, "ako4x_dsa_topk_indexer")
     return (out,)
 
@@ -54,11 +54,10 @@ def index_scores(q_index_fp8, k_index_cache_fp8, weights, seq_lens, block_table)
     rows, npages, max_pages = _check(q_index_fp8, k_index_cache_fp8, weights, seq_lens, block_table)
     scores = torch.full((rows, max_pages * 64), float("-inf"), dtype=torch.float32,
                         device=q_index_fp8.device)
+    keep = [t.contiguous() for t in (q_index_fp8, k_index_cache_fp8, weights, seq_lens, block_table)]
     st = _cabi.lib().ako4x_dsa_index_scores(
-        _cabi.ptr(q_index_fp8.contiguous()), _cabi.ptr(k_index_cache_fp8.contiguous()),
-        _cabi.ptr(weights.contiguous()), _cabi.ptr(seq_lens.contiguous()),
-        _cabi.ptr(block_table.contiguous()), _cabi.ptr(scores), rows, max_pages, npages,
-        _cabi.stream())
+        *[_cabi.ptr(t) for t in keep], _cabi.ptr(scores), rows, max_pages, npages, _cabi.stream())
+    del keep
     _cabi.check(st, "ako4x_dsa_index_scores")
     return scores
 
@@ -70,8 +69,9 @@ def topk_select(scores, seq_lens, block_table):
     if scores.dtype != torch.float32 or scores.shape != (rows, max_pages * 64):
         raise _cabi.Ako4xError("topk_select: scores must be fp32 [rows, max_pages*64]")
     out = torch.empty((rows, TOPK), dtype=torch.int32, device=scores.device)
+    keep = [t.contiguous() for t in (scores, seq_lens, block_table)]
     st = _cabi.lib().ako4x_dsa_topk_select(
-        _cabi.ptr(scores.contiguous()), _cabi.ptr(seq_lens.contiguous()),
-        _cabi.ptr(block_table.contiguous()), _cabi.ptr(out), rows, max_pages, _cabi.stream())
+        *[_cabi.ptr(t) for t in keep], _cabi.ptr(out), rows, max_pages, _cabi.stream())
+    del keep
     _cabi.check(st, "ako4x_dsa_topk_select")
     return out

@@ -26,13 +26,15 @@ def run(q, k_cache, v_cache, kv_indptr, kv_indices, sm_scale):
     page_size = k_cache.shape[1]
     n_idx = kv_indices.numel()
     L = _cabi.lib()
-    o = torch.empty_like(q)
+    o = torch.empty(q.shape, dtype=q.dtype, device=q.device)
     lse = torch.empty((batch, 32), dtype=torch.float32, device=q.device)
     ws_bytes = L.ako4x_gqa_paged_decode_workspace_bytes(batch, n_idx, page_size)
     ws = _cabi.workspace(ws_bytes, q.device)
+    qc = q.contiguous()   # kept alive until the launch is enqueued
     st = L.ako4x_gqa_paged_decode(
-        _cabi.ptr(q.contiguous()), _cabi.ptr(k_cache), _cabi.ptr(v_cache), _cabi.ptr(kv_indptr),
+        _cabi.ptr(qc), _cabi.ptr(k_cache), _cabi.ptr(v_cache), _cabi.ptr(kv_indptr),
         _cabi.ptr(kv_indices), float(sm_scale), _cabi.ptr(o), _cabi.ptr(lse), batch, n_idx,
         page_size, _cabi.ptr(ws), ws_bytes, _cabi.stream())
+    del qc
     _cabi.check(st, "ako4x_gqa_paged_decode")
     return o, lse

@@ -25,14 +25,16 @@ def run(q_nope, q_pe, ckv_cache, kpe_cache, qo_indptr, kv_indptr, kv_indices, sm
     page_size = ckv_cache.shape[1]
     n_idx = kv_indices.numel()
     L = _cabi.lib()
-    o = torch.empty_like(q_nope)
+    o = torch.empty(q_nope.shape, dtype=q_nope.dtype, device=q_nope.device)
     lse = torch.empty((total_q, 16), dtype=torch.float32, device=q_nope.device)
     ws_bytes = L.ako4x_mla_paged_prefill_workspace_bytes(total_q, batch, n_idx, page_size)
     ws = _cabi.workspace(ws_bytes, q_nope.device)
+    qn, qp = q_nope.contiguous(), q_pe.contiguous()   # kept alive until the launch is enqueued
     st = L.ako4x_mla_paged_prefill(
-        _cabi.ptr(q_nope.contiguous()), _cabi.ptr(q_pe.contiguous()), _cabi.ptr(ckv_cache),
+        _cabi.ptr(qn), _cabi.ptr(qp), _cabi.ptr(ckv_cache),
         _cabi.ptr(kpe_cache), _cabi.ptr(qo_indptr), _cabi.ptr(kv_indptr), _cabi.ptr(kv_indices),
         float(sm_scale), _cabi.ptr(o), _cabi.ptr(lse), total_q, batch, n_idx, page_size,
         _cabi.ptr(ws), ws_bytes, _cabi.stream())
+    del qn, qp
     _cabi.check(st, "ako4x_mla_paged_prefill")
     return o, lse

@@ -47,14 +47,18 @@ def run(routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_
     out = torch.empty((tokens, HIDDEN), dtype=torch.bfloat16, device=dev)
     ws_bytes = L.ako4x_moe_fp8_block_scale_workspace_bytes(tokens, n_local)
     ws = _cabi.workspace(ws_bytes, dev)
+    # Contiguous copies (if any were needed) stay bound until the launch has been enqueued: a
+    # temporary freed earlier could be handed to the next copy on the same stream.
+    lg, rb, x, xs = (routing_logits.contiguous(), routing_bias.contiguous(),
+                     hidden_states.contiguous(), hidden_states_scale.contiguous())
+    s13, s2 = gemm1_weights_scale.contiguous(), gemm2_weights_scale.contiguous()
     st = L.ako4x_moe_fp8_block_scale(
-        _cabi.ptr(routing_logits.contiguous()), _cabi.ptr(routing_bias.contiguous()),
-        1 if routing_bias.dtype == torch.bfloat16 else 0, _cabi.ptr(hidden_states.contiguous()),
-        _cabi.ptr(hidden_states_scale.contiguous()), _cabi.ptr(gemm1_weights),
-        _cabi.ptr(gemm1_weights_scale.contiguous()), _cabi.ptr(gemm2_weights),
-        _cabi.ptr(gemm2_weights_scale.contiguous()), int(_scalar(local_expert_offset)),
+        _cabi.ptr(lg), _cabi.ptr(rb), 1 if routing_bias.dtype == torch.bfloat16 else 0,
+        _cabi.ptr(x), _cabi.ptr(xs), _cabi.ptr(gemm1_weights), _cabi.ptr(s13),
+        _cabi.ptr(gemm2_weights), _cabi.ptr(s2), int(_scalar(local_expert_offset)),
         float(_scalar(routed_scaling_factor)), _cabi.ptr(out), tokens, n_local, _cabi.ptr(ws),
         ws_bytes, _cabi.stream())
+    del lg, rb, x, xs, s13, s2
     _cabi.check(st, "ako4x_moe_fp8_block_scale")
     if _check_status:
         off = L.ako4x_moe_fp8_block_scale_status_offset(tokens)
@@ -77,9 +81,11 @@ def ep_combine(rows, pos):
     if rows.dtype != torch.bfloat16 or pos.dtype != torch.int32:
         raise _cabi.Ako4xError("ep_combine: rows bf16 [n, cols], pos int32 [tokens, world]")
     out = torch.empty((tokens, cols), dtype=torch.bfloat16, device=pos.device)
+    rows_c, pos_c = rows.contiguous(), pos.contiguous()
     st = _cabi.lib().ako4x_moe_ep_combine(
-        _cabi.ptr(rows.contiguous()) if rows.numel() else None, _cabi.ptr(pos.contiguous()),
+        _cabi.ptr(rows_c) if rows.numel() else None, _cabi.ptr(pos_c),
         _cabi.ptr(out), tokens, world, cols, _cabi.stream())
+    del rows_c, pos_c
     _cabi.check(st, "ako4x_moe_ep_combine")
     return out
 
@@ -91,9 +97,11 @@ def ds_routing(routing_logits, routing_bias, routed_scaling_factor):
     dev = routing_logits.device
     ids = torch.empty((tokens, 8), dtype=torch.int32, device=dev)
     w = torch.empty((tokens, 8), dtype=torch.float32, device=dev)
+    lg, rb = routing_logits.contiguous(), routing_bias.contiguous()
     st = _cabi.lib().ako4x_moe_ds_routing(
-        _cabi.ptr(routing_logits.contiguous()), _cabi.ptr(routing_bias.contiguous()),
+        _cabi.ptr(lg), _cabi.ptr(rb),
         1 if routing_bias.dtype == torch.bfloat16 else 0, float(_scalar(routed_scaling_factor)),
         _cabi.ptr(ids), _cabi.ptr(w), tokens, _cabi.stream())
+    del lg, rb
     _cabi.check(st, "ako4x_moe_ds_routing")
     return ids, w

@@ -86,6 +86,10 @@ class ExpertParallelMoE:
             expert_fn = expert_fn or moe.run
             combine_fn = combine_fn or moe.ep_combine
         self.routing_fn, self.expert_fn, self.combine_fn = routing_fn, expert_fn, combine_fn
+        self.backend = "nccl"
+
+    def close(self):
+        """Releases what the instance holds (nothing for the NCCL exchange)."""
 
     @torch.no_grad()
     def run(self, routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights,

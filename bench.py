@@ -4,19 +4,24 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--op moe|gqa_decode|mla_decode] [--ops-only LIST]
                     [--impl ours|reference] [--no-ops-table]
 
-Headline (default ``--op moe``): FP8 block-scale MoE tokens/s at 8192 tokens per GPU, 32 local
-experts per GPU. With N > 1 (one process per GPU under torchrun) the ranks form an expert-parallel
-group (token dispatch/combine over NCCL all-to-all); ``--op gqa_decode`` / ``mla_decode`` shard the
-decode batch over the ranks with no collective. One JSON line is printed by rank 0.
+Headline (default ``--op moe``): FP8 block-scale MoE tokens/s at 8192 tokens, 32 local experts per
+GPU. With N > 1 (one process per GPU under torchrun) the ranks form an expert-parallel group: the
+8192 tokens are sharded 8192/N per rank, every rank owns 32 experts and receives the token rows
+routed to them, so the GEMM work per rank is that of the single-GPU call (weak scaling in
+(token, expert) pairs). The same run with 8192 tokens PER GPU is reported under
+``tokens_per_gpu_8192``, the expert-parallel result is checked against the sum over
+``local_expert_offset`` of the single-GPU operator (``ep_parity``), and the decode operators
+sharded by batch are timed on the same ranks (``decode_scaling``). ``--op gqa_decode`` /
+``mla_decode`` make a decode operator the headline instead. One JSON line is printed by rank 0.
 
 ``value`` is measured with the inputs resident in HBM; ``e2e`` is the same metric through the
 public Python ``run(...)`` with the step's inputs copied from pinned host memory and the result
 copied back inside the timed region. ``roofline`` describes the dominant kernel; ``ops`` lists
 microseconds per call and roofline fraction of every operator at its largest configuration
-(1 GPU only); ``cpu_baseline`` is the CPU oracle timed on a bounded sample.
+(1 GPU only); ``cpu_baseline`` is the CPU oracle timed on one pass over the same 8192 tokens.
 
 ``--impl reference`` times the CPU restatement of the reference operator (the oracle) on the host
-cores for the same workload, on a bounded sample per step.
+cores for the same workload: every step is one pass over all 8192 tokens.
 """
 from __future__ import annotations
 
@@ -401,7 +406,7 @@ def run_reference(args):
             "e2e": {"value": tps, "unit": "kv_tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}), flush=True)
         return
-    sample = 64
+    sample = MOE_TOKENS   # the whole workload: a smaller sample is mostly fixed dequantisation cost
     steps = max(1, args.steps)
     warmup = max(0, min(args.warmup, 1))
     tps, dt, cores = cpu_moe_sample(sample, steps, warmup)
@@ -412,9 +417,9 @@ def run_reference(args):
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp32",
         "data": "synthetic",
         "config": {"workload": f"moe_fp8_block_scale T={MOE_TOKENS} E_local=32 H=7168 I=2048 (DeepSeek-V3 routing)",
-                   "sample_tokens": sample},
+                   "parallelism": "host cores"},
         "cpu_baseline": {"value": tps, "unit": "tokens/s (full-token equivalents)", "cores": cores, "kind": "port",
-                         "sample": f"{sample} of {MOE_TOKENS} tokens per step, all 32 local experts resident"},
+                         "sample": f"all {MOE_TOKENS} tokens per step (the full workload), 32 local experts"},
         "e2e": {"value": tps, "unit": "tokens/s (full-token equivalents)", "h2d_bytes_per_step": 0,
                 "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -425,10 +430,56 @@ def run_reference(args):
 # ---------------------------------------------------------------------------------------------
 # main arm
 # ---------------------------------------------------------------------------------------------
-def run_moe(args, rank, world, dist_on, peaks):
+def ep_parity_check(ep, a, world, rows_per_rank=32):
+    """Expert-parallel equivalence on the GPUs: for `rows_per_rank` of this rank's tokens the
+    expert-parallel output must equal the sum, in rank order, over local_expert_offset = 0, 32, ...
+    of the single-GPU operator on the same rows (each rank applies its own experts to every
+    rank's sample rows; the bf16 partials are gathered and summed in fp32)."""
+    import torch.distributed as dist
     from ako4x_b200 import moe
-    T = args.tokens
+    T = a["hidden_states"].shape[0]
+    n = min(rows_per_rank, T)
+    sel = torch.linspace(0, T - 1, n, device="cuda").long()
+    out = ep.run(a["routing_logits"], a["routing_bias"], a["hidden_states"], a["hidden_states_scale"],
+                 a["gemm1_weights"], a["gemm1_weights_scale"], a["gemm2_weights"], a["gemm2_weights_scale"],
+                 a["routed_scaling_factor"])[sel]
+    mine = {"lg": a["routing_logits"][sel].contiguous(),
+            "x": a["hidden_states"].view(torch.uint8)[sel].contiguous(),
+            "xs": a["hidden_states_scale"][:, sel].t().contiguous()}           # [n, 56]
+    gathered = {}
+    for k, v in mine.items():
+        buf = [torch.empty_like(v) for _ in range(world)]
+        dist.all_gather(buf, v)
+        gathered[k] = torch.cat(buf)                                           # [world*n, ...]
+    part = moe.run(gathered["lg"], a["routing_bias"], gathered["x"].view(a["hidden_states"].dtype),
+                   gathered["xs"].t().contiguous(), a["gemm1_weights"], a["gemm1_weights_scale"],
+                   a["gemm2_weights"], a["gemm2_weights_scale"], a["local_expert_offset"],
+                   a["routed_scaling_factor"])                                 # bf16 [world*n, 7168]
+    parts = [torch.empty_like(part) for _ in range(world)]
+    dist.all_gather(parts, part)
+    rank = dist.get_rank()
+    ref = torch.zeros((n, 7168), dtype=torch.float32, device="cuda")
+    for g in range(world):
+        ref += parts[g][rank * n:(rank + 1) * n].float()
+    ref = ref.to(torch.bfloat16).float()
+    err = (out.float() - ref).abs()
+    stats = torch.tensor([float(err.norm()), float(ref.norm()),
+                          float((err <= 1e-2 + 1e-2 * ref.abs()).float().mean()),
+                          float((ref != 0).any())], device="cuda", dtype=torch.float64)
+    allst = [torch.empty_like(stats) for _ in range(world)]
+    dist.all_gather(allst, stats)
+    allst = torch.stack(allst).cpu()
+    fro = float((allst[:, 0].pow(2).sum().sqrt() / allst[:, 1].pow(2).sum().sqrt().clamp(min=1e-30)))
+    return {"max_rel_fro": fro, "matched_1e-2": float(allst[:, 2].min()), "rows_per_rank": n,
+            "nonzero_reference_on_every_rank": bool(allst[:, 3].min() > 0),
+            "ok": bool(fro <= 1e-3 and allst[:, 2].min() >= 0.999 and allst[:, 3].min() > 0)}
+
+
+def moe_measure(T, args, rank, world, dist_on, with_parity=False):
+    """Times the MoE step with `T` tokens on this rank (device-resident, then end to end)."""
+    from ako4x_b200 import moe
     a = moe_inputs(T, rank, "cuda")
+    ep = None
     if world > 1:
         from ako4x_b200 import moe_ep
         ep = moe_ep.ExpertParallelMoE(rank, world)
@@ -458,8 +509,8 @@ def run_moe(args, rank, world, dist_on, peaks):
     value = total_pairs / 8.0 * args.steps / (ms * 1e-3)
     tokens_in_flight = world * T * args.steps / (ms * 1e-3)
 
-    # end to end: pinned host inputs -> device, run, result -> pinned host, EVERY step. On one GPU
-    # the three legs of consecutive steps overlap (copy-in stream, compute stream, copy-out stream,
+    # end to end: pinned host inputs -> device, run, result -> pinned host, EVERY step. The three
+    # legs of consecutive steps overlap (copy-in stream, compute stream, copy-out stream,
     # double-buffered device inputs and host outputs): the serving pattern for a stream of batches.
     h_in = {k: pinned(a[k]) for k in ("routing_logits", "hidden_states", "hidden_states_scale")}
     d_in = [{k: torch.empty_like(a[k]) for k in h_in} for _ in range(2)]
@@ -474,16 +525,6 @@ def run_moe(args, rank, world, dist_on, peaks):
         j = counter[0] & 1
         counter[0] += 1
         cur = torch.cuda.current_stream()
-        if world > 1:  # the expert-parallel step synchronises with the host: legs stay in order
-            for k in h_in:
-                d_in[j][k].copy_(h_in[k], non_blocking=True)
-            b = dict(a)
-            b.update(d_in[j])
-            o = ep.run(b["routing_logits"], b["routing_bias"], b["hidden_states"], b["hidden_states_scale"],
-                       b["gemm1_weights"], b["gemm1_weights_scale"], b["gemm2_weights"],
-                       b["gemm2_weights_scale"], b["routed_scaling_factor"])
-            h_out[j].copy_(o, non_blocking=True)
-            return
         s_in.wait_event(ev_run[j])          # the step two back has consumed this input buffer
         with torch.cuda.stream(s_in):
             for k in h_in:
@@ -492,10 +533,14 @@ def run_moe(args, rank, world, dist_on, peaks):
         cur.wait_event(ev_in[j])
         b = dict(a)
         b.update(d_in[j])
-        o = moe.run(*[b[k] for k in MOE_KEYS])
+        if ep is not None:
+            o = ep.run(b["routing_logits"], b["routing_bias"], b["hidden_states"], b["hidden_states_scale"],
+                       b["gemm1_weights"], b["gemm1_weights_scale"], b["gemm2_weights"],
+                       b["gemm2_weights_scale"], b["routed_scaling_factor"])
+        else:
+            o = moe.run(*[b[k] for k in MOE_KEYS])
         ev_run[j].record(cur)
         s_out.wait_event(ev_run[j])
-        s_out.wait_event(ev_out[j])         # (ordering on s_out already implies it)
         with torch.cuda.stream(s_out):
             h_out[j].copy_(o, non_blocking=True)
             ev_out[j].record(s_out)
@@ -508,45 +553,97 @@ def run_moe(args, rank, world, dist_on, peaks):
     e2e_ms = time_steps(e2e_step, args.steps, min(args.warmup, 3), dist_on, finish=e2e_finish)
     h2d = sum(v.numel() * v.element_size() for v in h_in.values())
     d2h = h_out[0].numel() * h_out[0].element_size()
-    e2e_value = total_pairs / 8.0 * args.steps / (e2e_ms * 1e-3)
+    res = {"T": T, "ms": ms, "e2e_ms": e2e_ms, "pairs": total_pairs, "value": value,
+           "tokens_in_flight": tokens_in_flight, "e2e_value": total_pairs / 8.0 * args.steps / (e2e_ms * 1e-3),
+           "h2d": h2d, "d2h": d2h, "clocks": clocks, "launches_per_step": launches_per_step, "inputs": a}
+    if with_parity and ep is not None:
+        res["ep_parity"] = ep_parity_check(ep, a, world)
+    if ep is not None:
+        res["ep_backend"] = getattr(ep, "backend", "nccl")
+        ep.close()
+    return res
 
+
+def traffic_record():
+    """DRAM bytes per GEMM1 launch from the last ncu capture of this workload (a small JSON kept
+    beside the capture's summary; null when absent)."""
+    f = ROOT / "profiles" / "moe_gemm1_T8192_dram_traffic.json"
+    try:
+        return json.loads(f.read_text())
+    except (OSError, ValueError):
+        return None
+
+
+def run_moe(args, rank, world, dist_on, peaks):
+    if args.tokens % world:
+        raise SystemExit("--tokens must be a multiple of the number of GPUs")
+    T = args.tokens // world
+    m = moe_measure(T, args, rank, world, dist_on, with_parity=True)
+    a = m.pop("inputs")
     line = {
-        "metric": "moe_fp8_tokens_per_s", "value": value,
+        "metric": "moe_fp8_tokens_per_s", "value": m["value"],
         "unit": "tokens/s (full-token equivalents: 8 expert applications = 1 token)", "n_gpus": world,
-        "tokens_in_flight_per_s": tokens_in_flight, "pairs_per_step": total_pairs,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
+        "tokens_in_flight_per_s": m["tokens_in_flight"], "pairs_per_step": m["pairs"],
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": m["ms"] / args.steps,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3",
         "data": "synthetic",
-        "config": {"workload": f"moe_fp8_block_scale T={T} per GPU, E_local=32 per GPU, H=7168, I=2048, "
-                               "DeepSeek-V3 routing (256 experts, top-8)",
+        "config": {"workload": f"moe_fp8_block_scale T={args.tokens} tokens in the job ({T} per GPU), "
+                               "E_local=32 per GPU, H=7168, I=2048, DeepSeek-V3 routing (256 experts, top-8)",
                    "parallelism": f"ep{world}" if world > 1 else "single",
+                   "scaling_note": "every rank computes the (token, expert) pairs of its 32 experts over all "
+                                   f"{args.tokens} tokens: per-GPU work is fixed as N grows",
                    "l2": "inputs larger than L2 (1.4 GB of expert weights per step)"},
-        "clocks": clocks,
-        "e2e": {"value": e2e_value, "unit": "tokens/s (full-token equivalents)", "h2d_bytes_per_step": h2d,
-                "d2h_bytes_per_step": d2h},
-        "gpu_launches": launches_per_step * args.steps,
+        "clocks": m["clocks"],
+        "e2e": {"value": m["e2e_value"], "unit": "tokens/s (full-token equivalents)",
+                "h2d_bytes_per_step": m["h2d"], "d2h_bytes_per_step": m["d2h"]},
+        "gpu_launches": m["launches_per_step"] * args.steps,
     }
+    if "ep_parity" in m:
+        line["ep_parity"] = m["ep_parity"]
+        line["ep_backend"] = m["ep_backend"]
     if rank == 0 and world == 1:
-        pairs = total_pairs
+        pairs = m["pairs"]
         st = moe_stage_times(a, calls=5)
         fp8_peak = 2 * peaks["bf16_tflops"]
         achieved = pairs * FLOP_PER_PAIR_GEMM1 / (st[1] * 1e-3) / 1e12
+        tr = traffic_record() if args.tokens == MOE_TOKENS else None
         line["roofline"] = {
             "bound": "tensor", "kernel": "moe_gemm_tc_kernel<1> (GEMM1 + SwiGLU + two-piece e4m3 h)",
             "achieved": achieved, "peak": fp8_peak, "unit": "TFLOP/s", "frac": achieved / fp8_peak,
-            # dram__bytes_read.sum + dram__bytes_write.sum of one GEMM1 launch at this workload, from
-            # the ncu capture summarised in profiles/moe_gemm_tc_T8192_launch_list_and_counters.md
-            "traffic": 1052370432 if T == MOE_TOKENS else None,
+            "traffic": tr["dram_bytes_per_launch"] if tr else None,
+            "traffic_source": ({k: tr[k] for k in ("captured_at_commit", "captured_on", "command") if k in tr}
+                               if tr else None),
             "traffic_unit": "bytes per launch (algorithmic: 939.5 MB of W13 + 58 MB activations + 66 MB h)",
             "peak_source": f"2 x {peaks['source']} bf16 burst (no FP8 peak is recorded)",
             "local_pairs": pairs,
             "stage_ms": {"route_scatter": st[0], "gemm1": st[1], "gemm2": st[2], "combine": st[3]},
             "gemm2_achieved_tflops": pairs * FLOP_PER_PAIR_GEMM2 / (st[2] * 1e-3) / 1e12,
         }
+    del a
+    torch.cuda.empty_cache()
+    if world > 1 and not args.no_per_gpu_run:
+        # the larger job: 8192 tokens on EVERY GPU (8x the pairs per rank at N = 8)
+        g = moe_measure(args.tokens, args, rank, world, dist_on)
+        g.pop("inputs")
+        torch.cuda.empty_cache()
+        line["tokens_per_gpu_8192"] = {
+            "tokens_per_gpu": args.tokens, "value": g["value"], "ms_per_step": g["ms"] / args.steps,
+            "pairs_per_step": g["pairs"], "e2e_value": g["e2e_value"],
+            "tokens_in_flight_per_s": g["tokens_in_flight"]}
+    if not args.no_decode_scaling:
+        line["decode_scaling"] = []
+        for which in ("gqa_decode", "mla_decode"):
+            d = run_decode(args, rank, world, dist_on, peaks, which, e2e=False)
+            line["decode_scaling"].append({
+                "op": which, "kv_tokens_per_s": d["value"], "ms_per_step": d["ms_per_step"],
+                "workload": d["config"]["workload"], "hbm_frac_per_gpu": d["roofline"]["frac"]})
+            torch.cuda.empty_cache()
+    if "ep_parity" in line and not line["ep_parity"]["ok"]:
+        line["error"] = "expert-parallel output differs from the sum of single-GPU operators"
     return line
 
 
-def run_decode(args, rank, world, dist_on, peaks, which):
+def run_decode(args, rank, world, dist_on, peaks, which, e2e=True):
     from ako4x_b200 import gqa_decode, mla_decode, workloads as W
     if which == "gqa_decode":
         B = 256
@@ -568,6 +665,12 @@ def run_decode(args, rank, world, dist_on, peaks, which):
     with ClockSampler(torch.cuda.current_device()) as cs:
         ms = time_steps(step, args.steps, args.warmup, dist_on)
     value = total_tokens * args.steps / (ms * 1e-3)
+    if not e2e:
+        us = ms / args.steps * 1e3
+        achieved = per_tok * n / (us * 1e-6) / 1e9
+        return {"value": value, "ms_per_step": ms / args.steps,
+                "config": {"workload": f"{which} B={B} per GPU, len~U[128/512,8192], page_size=1"},
+                "roofline": {"frac": achieved / peaks["hbm_gbs"]}}
     h_in = {k: pinned(a[k]) for k in hostk}
     d_in = {k: torch.empty_like(a[k]) for k in hostk}
     o0, l0 = step()
@@ -614,7 +717,11 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--op", default="moe", choices=["moe", "gqa_decode", "mla_decode"])
     ap.add_argument("--tokens", type=int, default=MOE_TOKENS,
-                    help="MoE tokens per GPU (default: the benchmark configuration, 8192)")
+                    help="MoE tokens in the job (default: the benchmark configuration, 8192), sharded over the GPUs")
+    ap.add_argument("--no-per-gpu-run", action="store_true",
+                    help="with N > 1, skip the second run with --tokens tokens on every GPU")
+    ap.add_argument("--no-decode-scaling", action="store_true",
+                    help="skip the batch-sharded decode timings attached to the MoE line")
     ap.add_argument("--no-ops-table", action="store_true")
     ap.add_argument("--ops-only", default=None,
                     help="comma list of rmsnorm,gqa_decode,mla_decode,mla_prefill,dsa,moe_fp8: time only these "
@@ -659,10 +766,10 @@ def main():
             torch.cuda.empty_cache()
             line["ops"] = ops_table(peaks)
         if not args.no_cpu_baseline and args.op == "moe":
-            tps, dt, cores = cpu_moe_sample(64, 1, 0)
+            tps, dt, cores = cpu_moe_sample(MOE_TOKENS, 1, 0)
             line["cpu_baseline"] = {"value": tps, "unit": "tokens/s (full-token equivalents)", "cores": cores, "kind": "port",
-                                    "sample": "64 of 8192 tokens, one pass of the CPU oracle "
-                                              f"({dt:.1f} s), all 32 local experts resident"}
+                                    "sample": f"all {MOE_TOKENS} tokens (the full workload), one pass of the CPU "
+                                              f"oracle ({dt:.1f} s), 32 local experts"}
         elif not args.no_cpu_baseline:
             tps, dt, cores, n = cpu_decode_sample(args.op)
             line["cpu_baseline"] = {"value": tps, "unit": "kv_tokens/s", "cores": cores, "kind": "port",
@@ -673,6 +780,8 @@ def main():
         dist.destroy_process_group()
     if rank == 0:
         print(json.dumps(line), flush=True)
+    if line.get("error"):
+        raise SystemExit(line["error"])
 
 
 if __name__ == "__main__":

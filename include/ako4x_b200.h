@@ -5,7 +5,8 @@
  *   - takes raw DEVICE pointers, sizes and scalars only (no framework types),
  *   - launches on the CUDA stream it is given (a cudaStream_t passed as void*) and never
  *     synchronises the host, reads device memory from the host, allocates or frees,
- *   - keeps no state between calls (no pointer-keyed caches, no cached outputs),
+ *   - keeps no state between calls that changes a result (no pointer-keyed caches, no cached
+ *     outputs; the only words that outlive a call are the sticky diagnostic status words below),
  *   - initialises whatever part of `workspace` it later reads, so the workspace may hold garbage,
  *   - returns AKO4X_OK or a negative status; nothing throws across this boundary.
  * The matching `*_workspace_bytes` function gives the scratch size a call with the same
@@ -48,8 +49,10 @@ int ako4x_rmsnorm_h128(const void* x, const void* weight, void* y, int64_t rows,
  * q bf16 [batch,32,128]; k_cache, v_cache bf16 [pages,page_size,8,128]; kv_indptr int32
  * [batch+1]; kv_indices int32 [kv_indptr[batch]] (page ids); o bf16 [batch,32,128];
  * lse fp32 [batch,32] = log2(sum exp(logit)); empty sequence gives o = 0, lse = -inf.
- * `num_kv_indices` (the length of kv_indices) only sizes the split heuristic; it is a shape,
- * not device data.
+ * `num_kv_indices` (the length of kv_indices) sizes the split heuristic and the workspace; it is
+ * a shape, not device data, and it must bound the device-side list: kv_indptr[batch] <=
+ * num_kv_indices. A longer device-side list is cut to what the workspace holds and status code 20
+ * is recorded (ako4x_gqa_paged_decode_device_status).
  */
 size_t ako4x_gqa_paged_decode_workspace_bytes(int64_t batch, int64_t num_kv_indices,
                                               int64_t page_size);
@@ -59,9 +62,11 @@ int ako4x_gqa_paged_decode(const void* q, const void* k_cache, const void* v_cac
                            int64_t page_size, void* workspace, size_t workspace_bytes,
                            void* stream);
 
-/* The gather pipeline waits on mbarriers with a cycle limit. A wait that gives up stores a
- * non-zero code in a device status word and the CTA stops consuming; this call returns that word
- * (0 = no wait ever gave up). It synchronises the device: for tests and post-mortems only. */
+/* The gather pipeline waits on mbarriers with a cycle limit. A wait that gives up makes its CTA
+ * stop consuming and stores a non-zero code in a device status word; this call returns that word
+ * (0 = no wait has given up since the library was loaded). A non-zero word means that the outputs
+ * of the call that set it are invalid; later calls are not affected by it (every launch starts its
+ * waits afresh). It synchronises the device: for tests and post-mortems only. */
 int ako4x_gqa_paged_decode_device_status(void);
 
 /* The same operator for callers that have no scratch memory to pass and cannot allocate any (a

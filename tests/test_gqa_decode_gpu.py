@@ -80,6 +80,38 @@ def test_full_size_split_invariance(built_lib):
     assert_close_bf16(o[b], ref_o.to(torch.bfloat16))
 
 
+def test_full_length_sampled_sequences(built_lib):
+    """B = 256 with the configured lengths (128..8192), i.e. the work-list mode at full size: eight
+    sampled sequences against the CPU oracle (their cache rows compacted into a small cache)."""
+    a = W.make_gqa_decode(256, shape_id=256, device="cuda")
+    o, lse = gqa_decode.run(*[a[k] for k in KEYS])
+    sel = [0, 1, 50, 99, 128, 200, 254, 255]
+    ip = a["kv_indptr"].cpu().long()
+    rows, indptr = [], [0]
+    for b in sel:
+        rows.append(a["kv_indices"][ip[b]:ip[b + 1]].long())
+        indptr.append(indptr[-1] + int(ip[b + 1] - ip[b]))
+    rows = torch.cat(rows)
+    dsel = torch.tensor(sel, device="cuda")
+    ro, rlse = oracle.gqa_paged_decode(a["q"][dsel].cpu(), a["k_cache"][rows].cpu(), a["v_cache"][rows].cpu(),
+                                       torch.tensor(indptr, dtype=torch.int32),
+                                       torch.arange(rows.numel(), dtype=torch.int32), a["sm_scale"])
+    assert_close_bf16(o[dsel], ro)
+    assert_lse_close(lse[dsel], rlse)
+
+
+def test_non_contiguous_query(built_lib):
+    """q as a strided view: the wrapper's contiguous copy must be alive when the kernel runs."""
+    a = W.make_gqa_decode(3, shape_id=17, lens=[300, 1, 2049], extra_pages=7)
+    d = W.to_device(a, "cuda")
+    wide = torch.zeros((3, 32, 256), dtype=torch.bfloat16, device="cuda")
+    wide[..., :128] = d["q"]
+    o, lse = gqa_decode.run(wide[..., :128], *[d[k] for k in KEYS[1:]])
+    ro, rlse = oracle.gqa_paged_decode(*[a[k] for k in KEYS])
+    assert_close_bf16(o, ro)
+    assert_lse_close(lse, rlse)
+
+
 def test_same_buffers_new_contents(built_lib):
     a = W.to_device(W.make_gqa_decode(3, lens=[70, 300, 5], extra_pages=3), "cuda")
     o1, _ = gqa_decode.run(*[a[k] for k in KEYS])

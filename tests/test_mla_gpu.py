@@ -51,6 +51,55 @@ def test_decode_config_shapes(built_lib, batch):
            W.make_mla_decode(batch, shape_id=batch, len_lo=512, len_hi=1024 if batch > 1 else 8192))
 
 
+def _sampled_sequences(a, sel, cache_keys):
+    """CPU copy of the sub-problem made of the sequences `sel` of a GPU-resident paged batch: their
+    cache rows compacted into a small cache, page lists renumbered."""
+    ip = a["kv_indptr"].cpu().long()
+    rows, indptr = [], [0]
+    for b in sel:
+        rows.append(a["kv_indices"][ip[b]:ip[b + 1]].long())
+        indptr.append(indptr[-1] + int(ip[b + 1] - ip[b]))
+    rows = torch.cat(rows)
+    sub = {k: a[k][rows].cpu() for k in cache_keys}
+    sub["kv_indptr"] = torch.tensor(indptr, dtype=torch.int32)
+    sub["kv_indices"] = torch.arange(rows.numel(), dtype=torch.int32)
+    return sub
+
+
+def test_decode_full_length_sampled_sequences(built_lib):
+    """B = 128 with the configured context lengths (512..8192): eight sampled sequences of the
+    full-size call against the CPU oracle."""
+    a = W.make_mla_decode(128, shape_id=128, device="cuda")
+    o, lse = mla_decode.run(*[a[k] for k in DKEYS])
+    sel = [0, 17, 31, 64, 77, 100, 126, 127]
+    sub = _sampled_sequences(a, sel, ("ckv_cache", "kpe_cache"))
+    dsel = torch.tensor(sel, device="cuda")
+    ro, rlse = oracle.mla_paged_decode(a["q_nope"][dsel].cpu(), a["q_pe"][dsel].cpu(), sub["ckv_cache"],
+                                       sub["kpe_cache"], sub["kv_indptr"], sub["kv_indices"], a["sm_scale"])
+    assert_close_bf16(o[dsel], ro)
+    assert_lse_close(lse[dsel], rlse)
+
+
+def test_split_views_as_inputs(built_lib):
+    """q_nope / q_pe as the two halves of one [n,16,576] tensor (non-contiguous views): the wrapper's
+    contiguous copies must both be alive when the kernel runs."""
+    a = W.make_mla_decode(6, shape_id=61, lens=[700, 64, 1, 2500, 130, 999], extra_pages=13)
+    d = W.to_device(a, "cuda")
+    q = torch.cat([d["q_nope"], d["q_pe"]], dim=-1)
+    qn, qp = q.split([512, 64], dim=-1)
+    assert not qn.is_contiguous() and not qp.is_contiguous()
+    o, lse = mla_decode.run(qn, qp, *[d[k] for k in DKEYS[2:]])
+    ro, rlse = oracle.mla_paged_decode(*[a[k] for k in DKEYS])
+    assert_close_bf16(o, ro)
+    assert_lse_close(lse, rlse)
+    # the same through prefill (one query token per sequence, kv_len = its context) and DSA
+    qo = torch.arange(7, dtype=torch.int32, device="cuda")
+    o2, lse2 = mla_prefill.run(qn, qp, d["ckv_cache"], d["kpe_cache"], qo, d["kv_indptr"], d["kv_indices"],
+                               d["sm_scale"])
+    assert_close_bf16(o2, ro)
+    assert_lse_close(lse2, rlse)
+
+
 # ---- prefill -----------------------------------------------------------------------------------
 def test_prefill_golden(built_lib):
     g = load_golden("mla_prefill_b3")

@@ -20,7 +20,7 @@ KEYS = ["routing_logits", "routing_bias", "hidden_states", "hidden_states_scale"
         "routed_scaling_factor"]
 
 REL_FROBENIUS_MAX = 4e-3
-STRICT_MATCH_MIN = 0.93       # share of elements within atol = rtol = 1e-2
+STRICT_MATCH_MIN = 0.97       # share of elements within atol = rtol = 1e-2
 HARNESS_MATCH_MIN = 0.999     # share within atol 1, rtol 0.3 (the reference requires 0.9)
 
 
@@ -107,7 +107,9 @@ def test_skewed_routing(built_lib, weights):
     a = _case(weights, 512, shape_id=3, offset=0, skew=3.0)
     out = moe.run_checked(*[a[k] for k in KEYS])
     fro, strict, harness = _report(out, _oracle(a))
+    print(f"skewed: rel_fro={fro:.2e} strict={strict:.4f} harness={harness:.5f}")
     assert fro <= REL_FROBENIUS_MAX and harness >= HARNESS_MATCH_MIN
+    assert strict >= STRICT_MATCH_MIN
 
 
 def test_deterministic_and_no_stale_state(built_lib, weights):
@@ -118,6 +120,45 @@ def test_deterministic_and_no_stale_state(built_lib, weights):
     a["routing_logits"].copy_(a["routing_logits"].flip(0))
     o3 = moe.run_checked(*[a[k] for k in KEYS])
     assert not torch.equal(o1, o3), "refilled buffers must be recomputed"
+
+
+@pytest.mark.parametrize("offset", [0, 64])
+def test_full_size_sampled_rows_against_oracle(built_lib, weights, offset):
+    """T = 8192 (the headline shape: about 254 rows per expert, i.e. full 128-row tiles, m-tiles
+    that share a weight tile and a partial last tile). The operator treats every token
+    independently, so the oracle is run on 64 sampled tokens' own inputs and compared with the
+    same rows of the full call."""
+    a = _case(weights, 8192, shape_id=9 + offset, offset=offset)
+    out = moe.run_checked(*[a[k] for k in KEYS])
+    g = torch.Generator().manual_seed(1234 + offset)
+    sel = torch.randperm(8192, generator=g)[:64].sort().values
+    sub = dict(a)
+    dsel = sel.cuda()
+    sub["routing_logits"] = a["routing_logits"][dsel]
+    sub["hidden_states"] = a["hidden_states"].view(torch.uint8)[dsel].view(torch.float8_e4m3fn)
+    sub["hidden_states_scale"] = a["hidden_states_scale"][:, dsel].contiguous()
+    ref = _oracle(sub)
+    assert float(ref.float().abs().max()) > 0
+    fro, strict, harness = _report(out[dsel], ref)
+    print(f"T=8192 offset={offset}, 64 sampled rows: rel_fro={fro:.2e} strict={strict:.4f} harness={harness:.5f}")
+    assert fro <= REL_FROBENIUS_MAX
+    assert harness >= HARNESS_MATCH_MIN
+    assert strict >= STRICT_MATCH_MIN
+
+
+def test_non_contiguous_inputs(built_lib, weights):
+    """A transposed scale matrix and strided logits make the wrapper take contiguous copies; the
+    copies must stay alive until the launch (result equal to the contiguous call)."""
+    a = _case(weights, 96, shape_id=12)
+    ref = moe.run_checked(*[a[k] for k in KEYS]).clone()
+    b = dict(a)
+    b["hidden_states_scale"] = a["hidden_states_scale"].t().contiguous().t()          # [56,T] view of [T,56]
+    wide = torch.zeros((96, 512), dtype=torch.float32, device="cuda")
+    wide[:, ::2] = a["routing_logits"]
+    b["routing_logits"] = wide[:, ::2]
+    assert not b["hidden_states_scale"].is_contiguous() and not b["routing_logits"].is_contiguous()
+    out = moe.run_checked(*[b[k] for k in KEYS])
+    assert torch.equal(out, ref)
 
 
 def test_expert_partition_linearity_full_size(built_lib, weights):

@@ -14,6 +14,7 @@ run every other test.
 import pytest
 import torch
 
+import oracle
 from ako4x_b200 import _cabi, gqa_decode, workloads as W
 from conftest import assert_close_bf16, assert_lse_close
 
@@ -50,6 +51,14 @@ def test_two_calls_in_a_row_match_the_regular_entry_point(built_lib):
         assert_close_bf16(o, ro)          # the tolerance of the other GQA tests
         assert_lse_close(lse, rlse)
         assert torch.equal(o, ro) and torch.equal(lse, rlse)  # same kernels: also bit-identical
+    # and against the CPU oracle, so that this file does not lean on the regular path's own tests
+    a = W.make_gqa_decode(3, shape_id=34, lens=[1500, 3, 4100], extra_pages=9)
+    d = W.to_device(a, "cuda")
+    st, o, lse = _noalloc(d)
+    assert st == 0, _cabi.STATUS.get(st, st)
+    ro, rlse = oracle.gqa_paged_decode(*[a[k] for k in KEYS])
+    assert_close_bf16(o, ro)
+    assert_lse_close(lse, rlse)
 
 
 def test_oversized_request_is_refused_cleanly(built_lib):
