@@ -9,9 +9,12 @@ bf16-rounded scores, :541-546, which is lossy; fp32 ranking is the stricter rule
 global slots page*64+slot (:436-448) in ascending token position then -1; seq_len <= 2048 lists
 every token (:311-320).
 
-Parity unpinned: neither the reference nor flashinfer-python holds a definition or golden vector
-for this operator; the fixtures under tests/golden for it are produced by this oracle itself and
-only guard against regressions.
+Pinned against outputs of the reference's own GPU kernel (v8_radix_bt256/kernel.py::run, run on a
+B200 by tests/golden/make_indexer_reference_golden.py; fixture tests/golden/
+dsa_indexer_reference_v8.pt): rows of at most 2048 tokens are identical, longer rows differ from the
+reference's set only in slots whose score is a bf16 tie of the 2048-th score (the reference ranks
+bf16-rounded scores). tests/golden/dsa_indexer_t3.pt is this oracle's own output and only guards
+against regressions.
 """
 import torch
 

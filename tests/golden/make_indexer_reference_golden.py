@@ -67,7 +67,7 @@ def main():
                       "topk_indices": idx.detach().clone().cpu()})
         print(f"rows={rows} ctx={ctx}: valid per row {(idx >= 0).sum(dim=1).tolist()}")
     torch.save({"source": "reference/dsa-topk-indexer/variants/v8_radix_bt256/kernel.py::run (DSA_NO_GRAPH=1)",
-                "torch": torch.__version__, "cases": cases}, out_path)
+                "torch": str(torch.__version__), "cases": cases}, out_path)
     print("wrote", out_path)
 
     # the reference's latency on the benchmark shapes, same box, same inputs as bench.py's table

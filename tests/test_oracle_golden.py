@@ -4,7 +4,7 @@ import pytest
 import torch
 
 import oracle
-from conftest import assert_close_bf16, assert_lse_close, load_golden
+from conftest import GOLDEN, assert_close_bf16, assert_lse_close, load_golden
 
 
 @pytest.mark.parametrize("rows", [1, 7, 64])
@@ -100,3 +100,57 @@ def test_indexer_selection_rules():
     out = oracle.dsa_topk_select(scores, torch.tensor([70], dtype=torch.int32), bt)
     assert out[0, :70].tolist() == [int(bt[0, p // 64]) * 64 + p % 64 for p in range(70)]
     assert (out[0, 70:] == -1).all()
+
+
+def _bf16_ordinal(x: torch.Tensor) -> torch.Tensor:
+    """Monotone integer image of the bf16 rounding of fp32 values (adjacent bf16 values differ by 1)."""
+    bits = x.to(torch.bfloat16).view(torch.int16).to(torch.int32) & 0xFFFF
+    return torch.where(bits >= 0x8000, 0x8000 - bits, bits)   # negative values below positive ones
+
+
+def test_indexer_oracle_against_the_reference_kernel_outputs():
+    """Pins oracle/indexer.py to outputs of the reference's own GPU kernel
+    (reference/dsa-topk-indexer/variants/v8_radix_bt256/kernel.py::run), recorded on a B200 by
+    tests/golden/make_indexer_reference_golden.py on inputs this test redraws from the same seeds.
+
+    The reference ranks bf16-rounded scores and emits an unordered set, so the comparison is per
+    row and by set: rows of at most 2048 tokens must be identical (the listing rule, order
+    included); for longer rows every slot that only one side selected must have an oracle score
+    whose bf16 rounding is the bf16 rounding of the 2048-th best score, give or take one bf16 step
+    (the reference's fp32 sums run in another order before they are rounded)."""
+    import hashlib
+    from ako4x_b200 import workloads as W
+    g = torch.load(GOLDEN / "dsa_indexer_reference_v8.pt", weights_only=True)
+    keys = ["q_index_fp8", "k_index_cache_fp8", "weights", "seq_lens", "block_table"]
+    checked_long_rows = 0
+    for case in g["cases"]:
+        a = W.make_dsa_indexer(case["rows"], case["ctx"], shape_id=case["shape_id"], device="cpu")
+        h = hashlib.sha256()
+        for k in keys:
+            h.update(a[k].contiguous().view(torch.uint8).numpy().tobytes())
+        assert h.hexdigest() == case["input_sha256"], "the seeded inputs are not the recorded ones"
+        scores = oracle.dsa_index_scores(*[a[k] for k in keys])
+        mine = oracle.dsa_topk_select(scores, a["seq_lens"], a["block_table"])
+        ref = case["topk_indices"]
+        assert ref.shape == mine.shape
+        # global slot -> token position of this sequence (one block table for all rows)
+        bt = a["block_table"][0].long()
+        pos_of_slot = {int(bt[p]) * 64 + s: p * 64 + s for p in range(bt.numel()) for s in range(64)}
+        for r in range(case["rows"]):
+            sl = int(a["seq_lens"][r])
+            if sl <= 2048:
+                assert torch.equal(ref[r], mine[r]), f"ctx {case['ctx']} row {r}: listing differs"
+                continue
+            checked_long_rows += 1
+            rs, ms = set(ref[r].tolist()), set(mine[r].tolist())
+            assert -1 not in rs and len(rs) == 2048 and len(ms) == 2048
+            diff = rs ^ ms
+            row = scores[r, :sl]
+            kth = torch.sort(row, descending=True).values[2047]
+            kth_ord = int(_bf16_ordinal(kth.reshape(1)))
+            for slot in diff:
+                o = int(_bf16_ordinal(row[pos_of_slot[slot]].reshape(1)))
+                assert abs(o - kth_ord) <= 1, (f"ctx {case['ctx']} row {r}: slot {slot} differs from the "
+                                               f"reference and is not a bf16 tie of the 2048-th score")
+            assert len(diff) <= 2 * 64, f"ctx {case['ctx']} row {r}: {len(diff)} slots differ"
+    assert checked_long_rows >= 9
