@@ -372,6 +372,28 @@ __global__ void __launch_bounds__(THREADS, 1) mla_attention_kernel(Params p) {
   }
 }
 
+// The tensor-core form of the decode / sparse kernels (128-token tiles, tcgen05 + TMEM).
+#include "mla_gather_tc.cuh"
+
+// Calls with fewer 128-token tiles than this keep the 64-token mma.sync kernel: its CTAs are half
+// the size, so a call that cannot fill the GPU twice spreads over more SMs and has a shorter tail.
+constexpr int64_t kTcMinTiles = 296;
+
+bool use_tc(int64_t rows, int64_t avg_keys) {
+  return rows * ako::cdiv(avg_keys > 0 ? avg_keys : 1, tcg::TOK) >= kTcMinTiles;
+}
+
+// Splits for the tensor-core kernel: about six waves of CTAs (ragged rows make unequal CTAs; many
+// short ones keep the tail short), at least two tiles per CTA on average.
+int pick_splits_tc(int64_t rows, int64_t avg_keys) {
+  const int64_t tiles = ako::cdiv(avg_keys > 0 ? avg_keys : 1, tcg::TOK);
+  int64_t s = (148 * 6 + rows / 2) / rows;
+  if (s > tiles / 2) s = tiles / 2;
+  if (s < 1) s = 1;
+  if (s > MAX_SPLITS) s = MAX_SPLITS;
+  return (int)s;
+}
+
 int pick_splits(int64_t rows, int64_t avg_keys) {
   if (rows <= 0) return 1;
   int64_t want = ako::cdiv(592, rows);       // ~4 waves of 148 single-CTA SMs
@@ -404,14 +426,23 @@ size_t workspace_for(int64_t rows, int splits) {
 }
 
 template <int MODE>
-int launch(Params& p, int64_t rows, int splits, void* workspace, cudaStream_t st) {
+int launch(Params& p, int64_t rows, int splits, void* workspace, cudaStream_t st, bool tc = false) {
   p.num_splits = splits;
   p.part_acc = (float*)workspace;
   p.part_ml = workspace ? p.part_acc + (size_t)rows * H * splits * DC : nullptr;
-  if (!ako::ensure_dynamic_smem<mla_attention_kernel<MODE>>(SMEM_BYTES)) return AKO4X_ELAUNCH;
   const int64_t grid = rows * splits;
   if (grid > 0x7fffffffLL) return AKO4X_EINVAL;
-  mla_attention_kernel<MODE><<<(unsigned)grid, THREADS, SMEM_BYTES, st>>>(p);
+  if (tc) {
+    if constexpr (MODE == kPrefill) {
+      return AKO4X_EINVAL;
+    } else {
+      if (!ako::ensure_dynamic_smem<tcg::mla_gather_tc_kernel<MODE>>(tcg::SMEM)) return AKO4X_ELAUNCH;
+      tcg::mla_gather_tc_kernel<MODE><<<(unsigned)grid, tcg::THREADS, tcg::SMEM, st>>>(p);
+    }
+  } else {
+    if (!ako::ensure_dynamic_smem<mla_attention_kernel<MODE>>(SMEM_BYTES)) return AKO4X_ELAUNCH;
+    mla_attention_kernel<MODE><<<(unsigned)grid, THREADS, SMEM_BYTES, st>>>(p);
+  }
   AKO_CHECK_LAUNCH();
   if (splits > 1) {
     cudaLaunchConfig_t cfg = {};
@@ -455,7 +486,8 @@ void fill_common(Params& p, const void* q_nope, const void* q_pe, const void* ck
 extern "C" size_t ako4x_mla_paged_decode_workspace_bytes(int64_t batch, int64_t num_kv_indices,
                                                          int64_t page_size) {
   if (batch <= 0) return 0;
-  return workspace_for(batch, pick_splits(batch, num_kv_indices * page_size / batch));
+  const int64_t avg = num_kv_indices * page_size / batch;
+  return workspace_for(batch, use_tc(batch, avg) ? pick_splits_tc(batch, avg) : pick_splits(batch, avg));
 }
 
 extern "C" int ako4x_mla_paged_decode(const void* q_nope, const void* q_pe, const void* ckv_cache,
@@ -468,7 +500,9 @@ extern "C" int ako4x_mla_paged_decode(const void* q_nope, const void* q_pe, cons
   if (!q_nope || !q_pe || !ckv_cache || !kpe_cache || !kv_indptr || !o || !lse) return AKO4X_EINVAL;
   if (num_kv_indices > 0 && !kv_indices) return AKO4X_EINVAL;
   if (misaligned(q_nope, q_pe, ckv_cache, kpe_cache, o)) return AKO4X_EINVAL;
-  const int splits = pick_splits(batch, num_kv_indices * page_size / batch);
+  const int64_t avg = num_kv_indices * page_size / batch;
+  const bool tc = use_tc(batch, avg);
+  const int splits = tc ? pick_splits_tc(batch, avg) : pick_splits(batch, avg);
   const size_t need = workspace_for(batch, splits);
   if (need > 0 && (!workspace || workspace_bytes < need)) return AKO4X_EWORKSPACE;
   Params p = {};
@@ -476,13 +510,13 @@ extern "C" int ako4x_mla_paged_decode(const void* q_nope, const void* q_pe, cons
   p.kv_indptr = kv_indptr;
   p.indices = kv_indices;
   p.page_size = (int)page_size;
-  return launch<kDecode>(p, batch, splits, workspace, (cudaStream_t)stream);
+  return launch<kDecode>(p, batch, splits, workspace, (cudaStream_t)stream, tc);
 }
 
 // ---- DSA sparse attention ------------------------------------------------------------------------
 extern "C" size_t ako4x_dsa_sparse_attention_workspace_bytes(int64_t tokens, int64_t topk) {
   if (tokens <= 0) return 0;
-  return workspace_for(tokens, pick_splits(tokens, topk));
+  return workspace_for(tokens, use_tc(tokens, topk) ? pick_splits_tc(tokens, topk) : pick_splits(tokens, topk));
 }
 
 extern "C" int ako4x_dsa_sparse_attention(const void* q_nope, const void* q_pe, const void* ckv_cache,
@@ -496,7 +530,8 @@ extern "C" int ako4x_dsa_sparse_attention(const void* q_nope, const void* q_pe, 
   if (!q_nope || !q_pe || !ckv_cache || !kpe_cache || !o || !lse) return AKO4X_EINVAL;
   if (topk > 0 && !sparse_indices) return AKO4X_EINVAL;
   if (misaligned(q_nope, q_pe, ckv_cache, kpe_cache, o)) return AKO4X_EINVAL;
-  const int splits = pick_splits(tokens, topk);
+  const bool tc = use_tc(tokens, topk);
+  const int splits = tc ? pick_splits_tc(tokens, topk) : pick_splits(tokens, topk);
   const size_t need = workspace_for(tokens, splits);
   if (need > 0 && (!workspace || workspace_bytes < need)) return AKO4X_EWORKSPACE;
   Params p = {};
@@ -504,7 +539,7 @@ extern "C" int ako4x_dsa_sparse_attention(const void* q_nope, const void* q_pe, 
   p.indices = sparse_indices;
   p.page_size = 1;
   p.topk = (int)topk;
-  return launch<kSparse>(p, tokens, splits, workspace, (cudaStream_t)stream);
+  return launch<kSparse>(p, tokens, splits, workspace, (cudaStream_t)stream, tc);
 }
 
 // ---- causal paged MLA prefill --------------------------------------------------------------------

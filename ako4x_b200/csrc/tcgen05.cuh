@@ -55,6 +55,13 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* er
   }
 }
 
+// The same wait made warp-uniform: every lane of the (converged) warp polls, and the warp goes on
+// only if all lanes saw the phase. Roles that shuffle or __syncwarp after a wait use this form, so
+// that an error path cannot split the warp.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, int* err, int code) {
+  return __all_sync(0xffffffffu, mbar_wait(bar, parity, err, code) ? 1 : 0) != 0;
+}
+
 // ---- TMA (bulk tensor copy global -> shared, completion counted in bytes on an mbarrier) ------
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
@@ -148,6 +155,17 @@ __host__ __device__ constexpr uint32_t idesc_bf16_f32(int m, int n) {
   return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) |
          (static_cast<uint32_t>(m >> 4) << 24);
 }
+// The same fields for an operand stored with its M (or N) dimension contiguous ("MN-major"), 128-byte
+// swizzle: 64 elements of 16 bits along M are one 128-byte row, 8 consecutive reduction indices
+// are the 8 rows of a 1024-byte group. The low word then carries the byte distance between
+// successive 64-element blocks along M (LBO), the high word the distance between successive
+// 8-index groups along the reduction (SBO, 1024 bytes in kSmemDescHiSw128). A tile that was staged
+// as K-major rows of 128 bytes for one product can so be read transposed by another.
+__device__ __forceinline__ uint32_t smem_desc_lo_mn(uint32_t saddr, uint32_t lbo_bytes) {
+  return ((saddr >> 4) & 0x3FFFu) | (((lbo_bytes >> 4) & 0x3FFFu) << 16);
+}
+// Instruction descriptor bit that declares the A operand MN-major.
+constexpr uint32_t kIdescAMnMajor = 1u << 15;
 __device__ __forceinline__ void mma_bf16_lohi(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc,
                                               uint32_t accumulate) {
   asm volatile(
@@ -192,6 +210,28 @@ __device__ __forceinline__ void tmem_ld_wait_regs(float (&v)[32]) {
         "+r"(r[15]), "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]),
         "+r"(r[22]), "+r"(r[23]), "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]),
         "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+      :
+      : "memory");
+}
+
+// 32 lanes x 16 consecutive fp32 columns (same addressing as tmem_ld32).
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
+  uint32_t* r = reinterpret_cast<uint32_t*>(v);
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),
+        "=r"(r[15])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait_regs16(float (&v)[16]) {
+  uint32_t* r = reinterpret_cast<uint32_t*>(v);
+  asm volatile(
+      "tcgen05.wait::ld.sync.aligned;\n"
+      : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+        "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]),
+        "+r"(r[15])
       :
       : "memory");
 }

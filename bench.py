@@ -192,6 +192,10 @@ MOE_KEYS = ["routing_logits", "routing_bias", "hidden_states", "hidden_states_sc
 def moe_inputs(tokens, rank, device):
     from ako4x_b200 import workloads as W
     a = W.make_moe(tokens, shape_id=rank, device=device, local_expert_offset=32 * rank)
+    # the router bias is a model parameter: identical on every rank
+    g = torch.Generator(device=device)
+    g.manual_seed(W.BASE_SEED + 6999)
+    a["routing_bias"] = 0.01 * torch.randn(256, generator=g, device=device, dtype=torch.float32)
     return a
 
 
