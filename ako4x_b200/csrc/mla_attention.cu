@@ -380,18 +380,57 @@ __global__ void __launch_bounds__(THREADS, 1) mla_attention_kernel(Params p) {
 constexpr int64_t kTcMinTiles = 296;
 
 bool use_tc(int64_t rows, int64_t avg_keys) {
-  return rows * ako::cdiv(avg_keys > 0 ? avg_keys : 1, tcg::TOK) >= kTcMinTiles;
+  return rows <= tcg::MAX_ROWS && rows * ako::cdiv(avg_keys > 0 ? avg_keys : 1, tcg::TOK) >= kTcMinTiles;
 }
 
-// Splits for the tensor-core kernel: about six waves of CTAs (ragged rows make unequal CTAs; many
-// short ones keep the tail short), at least two tiles per CTA on average.
-int pick_splits_tc(int64_t rows, int64_t avg_keys) {
-  const int64_t tiles = ako::cdiv(avg_keys > 0 ? avg_keys : 1, tcg::TOK);
-  int64_t s = (148 * 6 + rows / 2) / rows;
-  if (s > tiles / 2) s = tiles / 2;
-  if (s < 1) s = 1;
-  if (s > MAX_SPLITS) s = MAX_SPLITS;
-  return (int)s;
+// Workspace of the tensor-core path: the tile prefix table (rows + 1 ints, padded), then one partial
+// slot per (row + CTA) sum: fp32 O [16][512] and (m, l) [16][2].
+struct TcWorkspace {
+  int* pref;
+  float* part_acc;
+  float* part_ml;
+  size_t total;
+};
+TcWorkspace tc_carve(void* base, int64_t rows, int ctas) {
+  const size_t slots = (size_t)rows + (size_t)ctas;
+  const size_t pref_bytes = (((size_t)rows + 1) * sizeof(int) + 255) & ~(size_t)255;
+  TcWorkspace w;
+  w.pref = (int*)base;
+  w.part_acc = (float*)((unsigned char*)base + pref_bytes);
+  w.part_ml = w.part_acc + slots * H * DC;
+  w.total = pref_bytes + slots * H * (DC + 2) * sizeof(float);
+  return w;
+}
+
+template <int MODE>
+int launch_tc(Params& p, int64_t rows, void* workspace, cudaStream_t st) {
+  const int ctas = ako::sm_count();
+  const TcWorkspace w = tc_carve(workspace, rows, ctas);
+  p.part_acc = w.part_acc;
+  p.part_ml = w.part_ml;
+  p.num_splits = 0;
+  if (!ako::ensure_dynamic_smem<tcg::mla_gather_tc_kernel<MODE>>(tcg::SMEM)) return AKO4X_ELAUNCH;
+  tcg::mla_gather_tc_kernel<MODE><<<ctas, tcg::THREADS, tcg::SMEM, st>>>(p, (int)rows, w.pref);
+  AKO_CHECK_LAUNCH();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(rows * H));
+  cfg.blockDim = dim3(DC / 4);
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const float* pacc = w.part_acc;
+  const float* pml = w.part_ml;
+  const int* pref = w.pref;
+  int nrows = (int)rows, tpr = (MODE == kSparse) ? (p.topk + tcg::TOK - 1) / tcg::TOK : 0, nctas = ctas;
+  __nv_bfloat16* op = p.o;
+  float* lp = p.lse;
+  if (cudaLaunchKernelEx(&cfg, tcg::mla_gather_tc_merge_kernel<MODE>, pacc, pml, pref, nrows, tpr, nctas, op, lp) !=
+      cudaSuccess)
+    return AKO4X_ELAUNCH;
+  return AKO4X_OK;
 }
 
 int pick_splits(int64_t rows, int64_t avg_keys) {
@@ -426,23 +465,14 @@ size_t workspace_for(int64_t rows, int splits) {
 }
 
 template <int MODE>
-int launch(Params& p, int64_t rows, int splits, void* workspace, cudaStream_t st, bool tc = false) {
+int launch(Params& p, int64_t rows, int splits, void* workspace, cudaStream_t st) {
   p.num_splits = splits;
   p.part_acc = (float*)workspace;
   p.part_ml = workspace ? p.part_acc + (size_t)rows * H * splits * DC : nullptr;
   const int64_t grid = rows * splits;
   if (grid > 0x7fffffffLL) return AKO4X_EINVAL;
-  if (tc) {
-    if constexpr (MODE == kPrefill) {
-      return AKO4X_EINVAL;
-    } else {
-      if (!ako::ensure_dynamic_smem<tcg::mla_gather_tc_kernel<MODE>>(tcg::SMEM)) return AKO4X_ELAUNCH;
-      tcg::mla_gather_tc_kernel<MODE><<<(unsigned)grid, tcg::THREADS, tcg::SMEM, st>>>(p);
-    }
-  } else {
-    if (!ako::ensure_dynamic_smem<mla_attention_kernel<MODE>>(SMEM_BYTES)) return AKO4X_ELAUNCH;
-    mla_attention_kernel<MODE><<<(unsigned)grid, THREADS, SMEM_BYTES, st>>>(p);
-  }
+  if (!ako::ensure_dynamic_smem<mla_attention_kernel<MODE>>(SMEM_BYTES)) return AKO4X_ELAUNCH;
+  mla_attention_kernel<MODE><<<(unsigned)grid, THREADS, SMEM_BYTES, st>>>(p);
   AKO_CHECK_LAUNCH();
   if (splits > 1) {
     cudaLaunchConfig_t cfg = {};
@@ -487,7 +517,8 @@ extern "C" size_t ako4x_mla_paged_decode_workspace_bytes(int64_t batch, int64_t 
                                                          int64_t page_size) {
   if (batch <= 0) return 0;
   const int64_t avg = num_kv_indices * page_size / batch;
-  return workspace_for(batch, use_tc(batch, avg) ? pick_splits_tc(batch, avg) : pick_splits(batch, avg));
+  if (use_tc(batch, avg)) return tc_carve(nullptr, batch, ako::sm_count()).total;
+  return workspace_for(batch, pick_splits(batch, avg));
 }
 
 extern "C" int ako4x_mla_paged_decode(const void* q_nope, const void* q_pe, const void* ckv_cache,
@@ -502,21 +533,23 @@ extern "C" int ako4x_mla_paged_decode(const void* q_nope, const void* q_pe, cons
   if (misaligned(q_nope, q_pe, ckv_cache, kpe_cache, o)) return AKO4X_EINVAL;
   const int64_t avg = num_kv_indices * page_size / batch;
   const bool tc = use_tc(batch, avg);
-  const int splits = tc ? pick_splits_tc(batch, avg) : pick_splits(batch, avg);
-  const size_t need = workspace_for(batch, splits);
-  if (need > 0 && (!workspace || workspace_bytes < need)) return AKO4X_EWORKSPACE;
+  const int splits = tc ? 0 : pick_splits(batch, avg);
+  const size_t need = tc ? tc_carve(nullptr, batch, ako::sm_count()).total : workspace_for(batch, splits);
+  if (need > 0 && (!workspace || workspace_bytes < need || ((uintptr_t)workspace & 15))) return AKO4X_EWORKSPACE;
   Params p = {};
   fill_common(p, q_nope, q_pe, ckv_cache, kpe_cache, o, lse, sm_scale);
   p.kv_indptr = kv_indptr;
   p.indices = kv_indices;
   p.page_size = (int)page_size;
-  return launch<kDecode>(p, batch, splits, workspace, (cudaStream_t)stream, tc);
+  if (tc) return launch_tc<kDecode>(p, batch, workspace, (cudaStream_t)stream);
+  return launch<kDecode>(p, batch, splits, workspace, (cudaStream_t)stream);
 }
 
 // ---- DSA sparse attention ------------------------------------------------------------------------
 extern "C" size_t ako4x_dsa_sparse_attention_workspace_bytes(int64_t tokens, int64_t topk) {
   if (tokens <= 0) return 0;
-  return workspace_for(tokens, use_tc(tokens, topk) ? pick_splits_tc(tokens, topk) : pick_splits(tokens, topk));
+  if (use_tc(tokens, topk)) return tc_carve(nullptr, tokens, ako::sm_count()).total;
+  return workspace_for(tokens, pick_splits(tokens, topk));
 }
 
 extern "C" int ako4x_dsa_sparse_attention(const void* q_nope, const void* q_pe, const void* ckv_cache,
@@ -531,15 +564,16 @@ extern "C" int ako4x_dsa_sparse_attention(const void* q_nope, const void* q_pe, 
   if (topk > 0 && !sparse_indices) return AKO4X_EINVAL;
   if (misaligned(q_nope, q_pe, ckv_cache, kpe_cache, o)) return AKO4X_EINVAL;
   const bool tc = use_tc(tokens, topk);
-  const int splits = tc ? pick_splits_tc(tokens, topk) : pick_splits(tokens, topk);
-  const size_t need = workspace_for(tokens, splits);
-  if (need > 0 && (!workspace || workspace_bytes < need)) return AKO4X_EWORKSPACE;
+  const int splits = tc ? 0 : pick_splits(tokens, topk);
+  const size_t need = tc ? tc_carve(nullptr, tokens, ako::sm_count()).total : workspace_for(tokens, splits);
+  if (need > 0 && (!workspace || workspace_bytes < need || ((uintptr_t)workspace & 15))) return AKO4X_EWORKSPACE;
   Params p = {};
   fill_common(p, q_nope, q_pe, ckv_cache, kpe_cache, o, lse, sm_scale);
   p.indices = sparse_indices;
   p.page_size = 1;
   p.topk = (int)topk;
-  return launch<kSparse>(p, tokens, splits, workspace, (cudaStream_t)stream, tc);
+  if (tc) return launch_tc<kSparse>(p, tokens, workspace, (cudaStream_t)stream);
+  return launch<kSparse>(p, tokens, splits, workspace, (cudaStream_t)stream);
 }
 
 // ---- causal paged MLA prefill --------------------------------------------------------------------

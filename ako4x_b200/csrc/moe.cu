@@ -42,7 +42,8 @@ struct Workspace {
   int32_t* topk_ids;      // [T,8]
   float* topk_w;          // [T,8]
   int32_t* pair_pos;      // [T,8] row of the pair in expert-sorted order, -1 if not local
-  int32_t* counts;        // [MAX_LOCAL]
+  int32_t* counts;        // [MAX_LOCAL] pairs routed to each local expert
+  int32_t* counts_fit;    // [MAX_LOCAL] the same, cut to the workspace capacity (what the GEMMs see)
   int32_t* offsets;       // [MAX_LOCAL+1]
   int32_t* sorted_token;  // [cap]
   float* h_scale;         // [16][cap]
@@ -53,8 +54,11 @@ struct Workspace {
   size_t total;
 };
 
-Workspace carve(void* base, int64_t tokens) {
-  const size_t cap = (size_t)tokens * TOPK;
+// `tokens` rows of routing lists; room for `cap` (token, local expert) pairs. The single-GPU operator
+// uses the worst case cap = 8 * tokens; the expert-parallel form passes a smaller bound.
+Workspace carve(void* base, int64_t tokens, int64_t cap_pairs) {
+  const size_t cap = (size_t)cap_pairs;
+  const size_t lists = (size_t)tokens * TOPK;
   uintptr_t p = (uintptr_t)base;
   auto take = [&](size_t bytes) {
     uintptr_t r = p;
@@ -62,10 +66,11 @@ Workspace carve(void* base, int64_t tokens) {
     return r;
   };
   Workspace w;
-  w.topk_ids = (int32_t*)take(cap * 4);
-  w.topk_w = (float*)take(cap * 4);
-  w.pair_pos = (int32_t*)take(cap * 4);
+  w.topk_ids = (int32_t*)take(lists * 4);
+  w.topk_w = (float*)take(lists * 4);
+  w.pair_pos = (int32_t*)take(lists * 4);
   w.counts = (int32_t*)take((MAX_LOCAL + 64) * 4);  // counts, then the error word (zeroed together)
+  w.counts_fit = (int32_t*)take(MAX_LOCAL * 4);
   w.offsets = (int32_t*)take((MAX_LOCAL + 1) * 4);
   w.sorted_token = (int32_t*)take(cap * 4);
   w.h_scale = (float*)take(16 * cap * 4);
@@ -191,11 +196,12 @@ __global__ void __launch_bounds__(128) moe_routing_kernel(
 __global__ void __launch_bounds__(1024) moe_scatter_kernel(
     const int32_t* __restrict__ topk_ids, const int32_t* __restrict__ counts,
     int32_t* __restrict__ offsets, int32_t* __restrict__ sorted_token, int32_t* __restrict__ pair_pos,
-    int tokens, int local_off, int n_local) {
+    int tokens, int local_off, int n_local, int cap, int32_t* __restrict__ counts_fit, int* __restrict__ error) {
   __shared__ int warp_tot[32];
   __shared__ int s_base;   // pairs of this expert placed by earlier chunks
   __shared__ int s_off;    // first row of this expert's segment
   __shared__ int s_chunk;  // pairs found in the current chunk
+  __shared__ int s_fit;    // pairs of this expert that fit into the workspace
   const int le = blockIdx.x;
   const int ge = local_off + le;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -205,15 +211,22 @@ __global__ void __launch_bounds__(1024) moe_scatter_kernel(
 #pragma unroll
     for (int off = 16; off >= 1; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
     if (lane == 0) {
-      s_off = acc;
+      // A workspace smaller than the worst case (expert-parallel callers) holds `cap` pairs: what
+      // does not fit is dropped (its pair_pos stays -1) and the status word says so.
+      const int fit = max(0, min(counts[le], cap - acc));
+      if (fit < counts[le]) atomicCAS(error, 0, 9);
+      s_off = min(acc, cap);
       s_base = 0;
-      offsets[le] = acc;
-      if (le == n_local - 1) offsets[n_local] = acc + counts[le];
+      s_fit = fit;
+      offsets[le] = min(acc, cap);
+      counts_fit[le] = fit;
+      if (le == n_local - 1) offsets[n_local] = min(acc, cap) + fit;
     }
   }
   __syncthreads();
   const int off_e = s_off;
-  if (counts[le] == 0) return;
+  const int fit = s_fit;
+  if (fit == 0) return;
   for (int t0 = 0; t0 < tokens; t0 += 1024) {
     const int t = t0 + tid;
     int slot = -1;
@@ -239,9 +252,11 @@ __global__ void __launch_bounds__(1024) moe_scatter_kernel(
     }
     __syncthreads();
     if (slot >= 0) {
-      const int pos = off_e + s_base + warp_tot[warp] + __popc(bal & ((1u << lane) - 1u));
-      sorted_token[pos] = t;
-      pair_pos[(int64_t)t * TOPK + slot] = pos;
+      const int k = s_base + warp_tot[warp] + __popc(bal & ((1u << lane) - 1u));
+      if (k < fit) {
+        sorted_token[off_e + k] = t;
+        pair_pos[(int64_t)t * TOPK + slot] = off_e + k;
+      }
     }
     __syncthreads();
     if (tid == 0) s_base += s_chunk;
@@ -376,12 +391,12 @@ int launch_gemms_tc(const GemmParams& p1, const GemmParams& p2, int64_t cap, int
 extern "C" size_t ako4x_moe_fp8_block_scale_workspace_bytes(int64_t tokens, int64_t num_local_experts) {
   (void)num_local_experts;
   if (tokens <= 0) return 0;
-  return carve(nullptr, tokens).total;
+  return carve(nullptr, tokens, tokens * TOPK).total;
 }
 
 extern "C" size_t ako4x_moe_fp8_block_scale_status_offset(int64_t tokens) {
   if (tokens <= 0) return 0;
-  const Workspace w = carve(nullptr, tokens);
+  const Workspace w = carve(nullptr, tokens, tokens * TOPK);
   return (size_t)((uintptr_t)(w.counts + MAX_LOCAL));
 }
 
@@ -420,7 +435,7 @@ extern "C" int ako4x_moe_fp8_block_scale_staged(
   const size_t need = ako4x_moe_fp8_block_scale_workspace_bytes(tokens, num_local_experts);
   if (!workspace || workspace_bytes < need || ((uintptr_t)workspace & 255)) return AKO4X_EWORKSPACE;
   cudaStream_t st = (cudaStream_t)stream;
-  Workspace w = carve(workspace, tokens);
+  Workspace w = carve(workspace, tokens, tokens * TOPK);
   const int n_local = (int)num_local_experts;
   const int64_t cap = tokens * TOPK;
 
@@ -430,8 +445,9 @@ extern "C" int ako4x_moe_fp8_block_scale_staged(
       routing_logits, routing_bias, bias_is_bf16, routed_scaling_factor, (int)tokens, w.topk_ids,
       w.topk_w, w.pair_pos, w.counts, local_expert_offset, n_local);
   AKO_CHECK_LAUNCH();
-  moe_scatter_kernel<<<n_local, 1024, 0, st>>>(w.topk_ids, w.counts, w.offsets, w.sorted_token,
-                                                w.pair_pos, (int)tokens, local_expert_offset, n_local);
+  moe_scatter_kernel<<<n_local, 1024, 0, st>>>(w.topk_ids, w.counts, w.offsets, w.sorted_token, w.pair_pos,
+                                                (int)tokens, local_expert_offset, n_local, (int)cap, w.counts_fit,
+                                                w.counts + MAX_LOCAL);
   AKO_CHECK_LAUNCH();
 
   GemmParams p1 = {};
@@ -439,7 +455,7 @@ extern "C" int ako4x_moe_fp8_block_scale_staged(
   p1.a_scale = hidden_states_scale;
   p1.w = (const uint8_t*)gemm1_weights;
   p1.w_scale = gemm1_weights_scale;
-  p1.counts = w.counts;
+  p1.counts = w.counts_fit;
   p1.offsets = w.offsets;
   p1.sorted_token = w.sorted_token;
   p1.hq = w.hq;
