@@ -379,8 +379,10 @@ __global__ void __launch_bounds__(THREADS, 1) mla_attention_kernel(Params p) {
 // the size, so a call that cannot fill the GPU twice spreads over more SMs and has a shorter tail.
 constexpr int64_t kTcMinTiles = 296;
 
-bool use_tc(int64_t rows, int64_t avg_keys) {
-  return rows <= tcg::MAX_ROWS && rows * ako::cdiv(avg_keys > 0 ? avg_keys : 1, tcg::TOK) >= kTcMinTiles;
+// `ragged`: rows have their own lengths (decode), which needs the per-row tile table in shared memory.
+bool use_tc(int64_t rows, int64_t avg_keys, bool ragged) {
+  if (ragged && rows > tcg::MAX_ROWS) return false;
+  return rows <= 0x7fffffffLL / 4096 && rows * ako::cdiv(avg_keys > 0 ? avg_keys : 1, tcg::TOK) >= kTcMinTiles;
 }
 
 // Workspace of the tensor-core path: the tile prefix table (rows + 1 ints, padded), then one partial
@@ -517,7 +519,7 @@ extern "C" size_t ako4x_mla_paged_decode_workspace_bytes(int64_t batch, int64_t 
                                                          int64_t page_size) {
   if (batch <= 0) return 0;
   const int64_t avg = num_kv_indices * page_size / batch;
-  if (use_tc(batch, avg)) return tc_carve(nullptr, batch, ako::sm_count()).total;
+  if (use_tc(batch, avg, true)) return tc_carve(nullptr, batch, ako::sm_count()).total;
   return workspace_for(batch, pick_splits(batch, avg));
 }
 
@@ -532,7 +534,7 @@ extern "C" int ako4x_mla_paged_decode(const void* q_nope, const void* q_pe, cons
   if (num_kv_indices > 0 && !kv_indices) return AKO4X_EINVAL;
   if (misaligned(q_nope, q_pe, ckv_cache, kpe_cache, o)) return AKO4X_EINVAL;
   const int64_t avg = num_kv_indices * page_size / batch;
-  const bool tc = use_tc(batch, avg);
+  const bool tc = use_tc(batch, avg, true);
   const int splits = tc ? 0 : pick_splits(batch, avg);
   const size_t need = tc ? tc_carve(nullptr, batch, ako::sm_count()).total : workspace_for(batch, splits);
   if (need > 0 && (!workspace || workspace_bytes < need || ((uintptr_t)workspace & 15))) return AKO4X_EWORKSPACE;
@@ -548,7 +550,7 @@ extern "C" int ako4x_mla_paged_decode(const void* q_nope, const void* q_pe, cons
 // ---- DSA sparse attention ------------------------------------------------------------------------
 extern "C" size_t ako4x_dsa_sparse_attention_workspace_bytes(int64_t tokens, int64_t topk) {
   if (tokens <= 0) return 0;
-  if (use_tc(tokens, topk)) return tc_carve(nullptr, tokens, ako::sm_count()).total;
+  if (use_tc(tokens, topk, false)) return tc_carve(nullptr, tokens, ako::sm_count()).total;
   return workspace_for(tokens, pick_splits(tokens, topk));
 }
 
@@ -563,7 +565,7 @@ extern "C" int ako4x_dsa_sparse_attention(const void* q_nope, const void* q_pe, 
   if (!q_nope || !q_pe || !ckv_cache || !kpe_cache || !o || !lse) return AKO4X_EINVAL;
   if (topk > 0 && !sparse_indices) return AKO4X_EINVAL;
   if (misaligned(q_nope, q_pe, ckv_cache, kpe_cache, o)) return AKO4X_EINVAL;
-  const bool tc = use_tc(tokens, topk);
+  const bool tc = use_tc(tokens, topk, false);
   const int splits = tc ? 0 : pick_splits(tokens, topk);
   const size_t need = tc ? tc_carve(nullptr, tokens, ako::sm_count()).total : workspace_for(tokens, splits);
   if (need > 0 && (!workspace || workspace_bytes < need || ((uintptr_t)workspace & 15))) return AKO4X_EWORKSPACE;
