@@ -86,6 +86,11 @@ _SIGNATURES = {
     "ako4x_moe_fp8_block_scale_status_offset": (_SZ, [_I64]),
     "ako4x_moe_ds_routing": (_INT, [_P, _P, _INT, _F32, _P, _P, _I64, _P]),
     "ako4x_moe_ep_combine": (_INT, [_P, _P, _P, _I64, _I64, _I64, _P]),
+    "ako4x_moe_ep_buffer_bytes": (_SZ, [_I64, _I64]),
+    "ako4x_moe_ep_workspace_bytes": (_SZ, [_I64, _I64, _I64, _I64]),
+    "ako4x_moe_fp8_block_scale_ep": (_INT, [_P, _P, _INT, _P, _P, _P, _P, _P, _P, _F32, _P, _I64, _I64, _I64, _I64,
+                                             _I64, _I32, _P, _P, _SZ, _P]),
+    "ako4x_moe_ep_status": (_INT, [_P]),
 }
 
 

@@ -386,7 +386,151 @@ int launch_gemms_tc(const GemmParams& p1, const GemmParams& p2, int64_t cap, int
   return AKO4X_OK;
 }
 
+// Expert-parallel exchange over peer memory (kernels).
+#include "moe_ep.cuh"
+
+// Private workspace of one expert-parallel rank: the rank's own routing lists and dispatch plan,
+// then the operator's workspace for the rows it receives (world * cap_rows virtual tokens,
+// `pair_capacity` (token, expert) pairs).
+struct EpWorkspace {
+  int32_t* ids;         // [tokens, 8]
+  float* wts;           // [tokens, 8]
+  int32_t* pos;         // [tokens, world] row inside the destination's block, or -1
+  int32_t* send_count;  // [8]
+  void* expert;         // carve(world * cap_rows, pair_capacity)
+  size_t total;
+};
+EpWorkspace ep_carve(void* base, int64_t tokens, int64_t world, int64_t cap_rows, int64_t pair_capacity) {
+  uintptr_t p = (uintptr_t)base;
+  auto take = [&](size_t bytes) {
+    uintptr_t r = p;
+    p += (bytes + 255) & ~(size_t)255;
+    return r;
+  };
+  EpWorkspace w;
+  w.ids = (int32_t*)take((size_t)tokens * TOPK * 4);
+  w.wts = (float*)take((size_t)tokens * TOPK * 4);
+  w.pos = (int32_t*)take((size_t)tokens * world * 4);
+  w.send_count = (int32_t*)take(ep::MAX_WORLD * 4);
+  w.expert = (void*)take(carve(nullptr, world * cap_rows, pair_capacity).total);
+  w.total = p - (uintptr_t)base;
+  return w;
+}
+
 }  // namespace
+
+extern "C" size_t ako4x_moe_ep_buffer_bytes(int64_t world, int64_t cap_rows) {
+  if (world < 1 || world > ep::MAX_WORLD || cap_rows < 1) return 0;
+  return ep::buffer_bytes((int)world, cap_rows);
+}
+
+extern "C" size_t ako4x_moe_ep_workspace_bytes(int64_t tokens, int64_t world, int64_t cap_rows,
+                                               int64_t pair_capacity) {
+  if (tokens < 0 || world < 1 || world > ep::MAX_WORLD || cap_rows < 1 || pair_capacity < 1) return 0;
+  return ep_carve(nullptr, tokens, world, cap_rows, pair_capacity).total;
+}
+
+extern "C" int ako4x_moe_fp8_block_scale_ep(
+    const float* routing_logits, const void* routing_bias, int bias_is_bf16, const void* hidden_states,
+    const float* hidden_states_scale, const void* gemm1_weights, const float* gemm1_weights_scale,
+    const void* gemm2_weights, const float* gemm2_weights_scale, float routed_scaling_factor, void* out,
+    int64_t tokens, int64_t world, int64_t rank, int64_t cap_rows, int64_t pair_capacity, int32_t step,
+    void* const* peer_buffers, void* workspace, size_t workspace_bytes, void* stream) {
+  if (world < 1 || world > ep::MAX_WORLD || rank < 0 || rank >= world || cap_rows < 1 || pair_capacity < 1 ||
+      step < 1 || tokens < 0 || tokens > cap_rows || world * cap_rows > (1 << 24) ||
+      pair_capacity > world * cap_rows * TOPK)
+    return AKO4X_EINVAL;
+  if (!routing_logits || !routing_bias || !hidden_states || !hidden_states_scale || !gemm1_weights ||
+      !gemm1_weights_scale || !gemm2_weights || !gemm2_weights_scale || !out || !peer_buffers)
+    return AKO4X_EINVAL;
+  if (((uintptr_t)routing_logits | (uintptr_t)routing_bias | (uintptr_t)hidden_states |
+       (uintptr_t)gemm1_weights | (uintptr_t)gemm2_weights | (uintptr_t)out) & 15)
+    return AKO4X_EINVAL;
+  ep::Peers peers = {};
+  for (int g = 0; g < world; ++g) {
+    if (!peer_buffers[g] || ((uintptr_t)peer_buffers[g] & 255)) return AKO4X_EINVAL;
+    peers.buf[g] = (unsigned char*)peer_buffers[g];
+  }
+  const size_t need = ako4x_moe_ep_workspace_bytes(tokens, world, cap_rows, pair_capacity);
+  if (!workspace || workspace_bytes < need || ((uintptr_t)workspace & 255)) return AKO4X_EWORKSPACE;
+  cudaStream_t st = (cudaStream_t)stream;
+  const EpWorkspace ew = ep_carve(workspace, tokens, world, cap_rows, pair_capacity);
+  const int n_local = 32;
+  const int local_off = 32 * (int)rank;
+  unsigned char* mybuf = peers.buf[rank];
+
+  // ---- dispatch: route my tokens, plan, store rows into the destinations' receive areas ----
+  if (tokens > 0) {
+    moe_routing_kernel<<<(unsigned)ako::cdiv(tokens, 4), 128, 0, st>>>(
+        routing_logits, routing_bias, bias_is_bf16, routed_scaling_factor, (int)tokens, ew.ids, ew.wts, nullptr,
+        nullptr, 0, 0);
+    AKO_CHECK_LAUNCH();
+  }
+  ep::ep_plan_kernel<<<(unsigned)world, 1024, 0, st>>>(ew.ids, (int)tokens, (int)world, ew.pos, ew.send_count);
+  AKO_CHECK_LAUNCH();
+  ep::ep_send_kernel<<<(unsigned)ako::cdiv(tokens * world > 0 ? tokens * world : 1, 8), 256, 0, st>>>(
+      (const uint8_t*)hidden_states, hidden_states_scale, ew.ids, ew.wts, ew.pos, ew.send_count, (int)tokens,
+      (int)world, (int)rank, cap_rows, step, peers);
+  AKO_CHECK_LAUNCH();
+
+  // ---- experts: the operator on the rows every rank sent me ----
+  const int64_t vtokens = world * cap_rows;
+  Workspace w = carve(ew.expert, vtokens, pair_capacity);
+  if (cudaMemsetAsync(w.counts, 0, (MAX_LOCAL + 64) * sizeof(int32_t), st) != cudaSuccess) return AKO4X_ELAUNCH;
+  ep::ep_recv_route_kernel<<<(unsigned)ako::cdiv(vtokens, 32), 256, 0, st>>>(
+      mybuf, (int)world, cap_rows, step, w.topk_ids, w.topk_w, w.pair_pos, w.counts, local_off, n_local);
+  AKO_CHECK_LAUNCH();
+  moe_scatter_kernel<<<n_local, 1024, 0, st>>>(w.topk_ids, w.counts, w.offsets, w.sorted_token, w.pair_pos,
+                                                (int)vtokens, local_off, n_local, (int)pair_capacity, w.counts_fit,
+                                                w.counts + MAX_LOCAL);
+  AKO_CHECK_LAUNCH();
+  ep::ep_permute_kernel<<<(unsigned)ako::cdiv(vtokens * TOPK, 8), 256, 0, st>>>(
+      mybuf + ep::recv_offset(), w.pair_pos, w.xs, w.xs_scale, vtokens, pair_capacity);
+  AKO_CHECK_LAUNCH();
+  GemmParams p1 = {};
+  p1.a = w.xs;
+  p1.a_scale = w.xs_scale;
+  p1.w = (const uint8_t*)gemm1_weights;
+  p1.w_scale = gemm1_weights_scale;
+  p1.counts = w.counts_fit;
+  p1.offsets = w.offsets;
+  p1.sorted_token = w.sorted_token;
+  p1.hq = w.hq;
+  p1.h_scale = w.h_scale;
+  p1.a_scale_stride = pair_capacity;
+  p1.h_scale_stride = pair_capacity;
+  p1.error = w.counts + MAX_LOCAL;
+  p1.n_local = n_local;
+  GemmParams p2 = p1;
+  p2.a = w.hq;
+  p2.a_scale = w.h_scale;
+  p2.w = (const uint8_t*)gemm2_weights;
+  p2.w_scale = gemm2_weights_scale;
+  p2.y = w.y;
+  const int rc = launch_gemms_tc(p1, p2, pair_capacity, n_local, ako::sm_count(), st, [](int) {});
+  if (rc != AKO4X_OK) return rc;
+  ep::ep_return_kernel<<<(unsigned)vtokens, 256, 0, st>>>(w.y, w.pair_pos, w.topk_w, w.topk_ids, (int)world, (int)rank,
+                                                           cap_rows, step, peers);
+  AKO_CHECK_LAUNCH();
+
+  // ---- finish: my tokens' partial rows, summed in rank order ----
+  if (tokens > 0) {
+    ep::ep_finish_kernel<<<(unsigned)tokens, 256, 0, st>>>(mybuf, ew.pos, (__nv_bfloat16*)out, (int)world, cap_rows,
+                                                           step);
+    AKO_CHECK_LAUNCH();
+  }
+  return AKO4X_OK;
+}
+
+// Status of the expert-parallel exchange on this rank: 0, or the code of a bounded wait on a peer
+// that gave up (50 + source rank: rows never arrived; 60 + expert rank: results never arrived), or
+// the GEMM status word (see ako4x_moe_fp8_block_scale_status_offset). Synchronises the device.
+extern "C" int ako4x_moe_ep_status(const void* my_buffer) {
+  if (!my_buffer) return AKO4X_EINVAL;
+  ep::Flags f;
+  if (cudaMemcpy(&f, my_buffer, sizeof(f), cudaMemcpyDeviceToHost) != cudaSuccess) return AKO4X_ELAUNCH;
+  return f.error;
+}
 
 extern "C" size_t ako4x_moe_fp8_block_scale_workspace_bytes(int64_t tokens, int64_t num_local_experts) {
   (void)num_local_experts;

@@ -68,6 +68,7 @@ __device__ __forceinline__ bool wait_step(const int32_t* flag, int step, int32_t
   const long long t0 = clock64();
   while (true) {
     if (ld_acquire_sys(flag) >= step) return true;
+    if (*reinterpret_cast<volatile int32_t*>(error) != 0) return false;  // another wait already gave up
     if (clock64() - t0 > kPeerWaitCycles) {
       atomicCAS(error, 0, code);
       return false;

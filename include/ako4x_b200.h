@@ -215,6 +215,40 @@ int ako4x_moe_ds_routing(const float* routing_logits, const void* routing_bias, 
 int ako4x_moe_ep_combine(const void* rows, const int32_t* pos, void* out, int64_t tokens,
                          int64_t world, int64_t cols, void* stream);
 
+/* ---- Expert-parallel form of a7 over NVLink peer memory (no counterpart in the reference, which is
+ * single-GPU) ---------------------------------------------------------------------------------
+ * One process per GPU; rank r owns experts [32r, 32r+32) (routing group r). Every rank allocates
+ * one buffer of ako4x_moe_ep_buffer_bytes(world, cap_rows) bytes that all ranks can address (CUDA
+ * peer / IPC / fabric mapping; the Python side uses torch symmetric memory), zero-fills its first
+ * 4096 bytes once, and passes the `world` mapped addresses, in rank order, as `peer_buffers` (a HOST
+ * array). `cap_rows` bounds the tokens any rank contributes to a step; `pair_capacity` bounds the
+ * (token, expert) pairs this rank computes (about world * cap_rows for uniform routing; pairs beyond
+ * it are dropped and status 9 is recorded in the workspace status word); `step` is 1, 2, 3, ... and
+ * must be the same on every rank for the same step. The call routes this rank's `tokens` tokens,
+ * stores one copy of each token row into the receive area of every rank that owns one of its eight
+ * experts, runs the operator on the rows it received, stores each row's bf16 partial back into the
+ * sender's return area and sums, in rank order and in fp32, the partial rows of its own tokens into
+ * `out` (bf16 [tokens, 7168]). Everything runs on `stream`; there is no host synchronisation and no
+ * collective library call. Waits on peers are bounded (about two seconds): a rank that never
+ * arrives leaves a code in the buffer's status word (ako4x_moe_ep_status) instead of a hang.
+ * Experts that no participating rank owns (world < 8) are dropped, as the single-GPU operator
+ * drops non-local experts. */
+size_t ako4x_moe_ep_buffer_bytes(int64_t world, int64_t cap_rows);
+size_t ako4x_moe_ep_workspace_bytes(int64_t tokens, int64_t world, int64_t cap_rows,
+                                    int64_t pair_capacity);
+int ako4x_moe_fp8_block_scale_ep(const float* routing_logits, const void* routing_bias,
+                                 int bias_is_bf16, const void* hidden_states,
+                                 const float* hidden_states_scale, const void* gemm1_weights,
+                                 const float* gemm1_weights_scale, const void* gemm2_weights,
+                                 const float* gemm2_weights_scale, float routed_scaling_factor,
+                                 void* out, int64_t tokens, int64_t world, int64_t rank,
+                                 int64_t cap_rows, int64_t pair_capacity, int32_t step,
+                                 void* const* peer_buffers, void* workspace, size_t workspace_bytes,
+                                 void* stream);
+/* 0, or the code of a bounded wait on a peer that gave up (50 + source rank: its rows never arrived;
+ * 60 + expert rank: its results never arrived). Synchronises the device. */
+int ako4x_moe_ep_status(const void* my_buffer);
+
 #ifdef __cplusplus
 }
 #endif
