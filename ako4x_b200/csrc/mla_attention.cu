@@ -578,6 +578,32 @@ extern "C" int ako4x_dsa_sparse_attention(const void* q_nope, const void* q_pe, 
   return launch<kSparse>(p, tokens, splits, workspace, (cudaStream_t)stream);
 }
 
+// ---- DSA indexer followed by sparse attention, the top-k list staying on the device ---------------
+extern "C" size_t ako4x_dsa_indexer_attention_workspace_bytes(int64_t rows, int64_t max_pages) {
+  const size_t a = (ako4x_dsa_topk_indexer_workspace_bytes(rows, max_pages) + 255) & ~(size_t)255;
+  return a + ako4x_dsa_sparse_attention_workspace_bytes(rows, 2048);
+}
+
+extern "C" int ako4x_dsa_indexer_attention(const void* q_index_fp8, const void* k_index_cache,
+                                           const float* weights, const int32_t* seq_lens,
+                                           const int32_t* block_table, const void* q_nope, const void* q_pe,
+                                           const void* ckv_cache, const void* kpe_cache, float sm_scale,
+                                           int32_t* topk_indices, void* o, float* lse, int64_t rows,
+                                           int64_t max_pages, int64_t num_cache_pages, void* workspace,
+                                           size_t workspace_bytes, void* stream) {
+  if (rows < 0 || max_pages < 0 || num_cache_pages < 0) return AKO4X_EINVAL;
+  if (rows == 0) return AKO4X_OK;
+  const size_t a = (ako4x_dsa_topk_indexer_workspace_bytes(rows, max_pages) + 255) & ~(size_t)255;
+  const size_t b = ako4x_dsa_sparse_attention_workspace_bytes(rows, 2048);
+  if (a + b > 0 && (!workspace || workspace_bytes < a + b || ((uintptr_t)workspace & 255))) return AKO4X_EWORKSPACE;
+  int rc = ako4x_dsa_topk_indexer(q_index_fp8, k_index_cache, weights, seq_lens, block_table, topk_indices, rows,
+                                  max_pages, num_cache_pages, workspace, a, stream);
+  if (rc != AKO4X_OK) return rc;
+  // the index space of the top-k list is the flattened cache: num_cache_pages * 64 rows
+  return ako4x_dsa_sparse_attention(q_nope, q_pe, ckv_cache, kpe_cache, topk_indices, sm_scale, o, lse, rows, 2048,
+                                    num_cache_pages * 64, (unsigned char*)workspace + a, b, stream);
+}
+
 // ---- causal paged MLA prefill --------------------------------------------------------------------
 extern "C" size_t ako4x_mla_paged_prefill_workspace_bytes(int64_t total_q, int64_t batch,
                                                           int64_t num_kv_indices, int64_t page_size) {

@@ -468,7 +468,10 @@ extern "C" int ako4x_moe_fp8_block_scale_ep(
   }
   ep::ep_plan_kernel<<<(unsigned)world, 1024, 0, st>>>(ew.ids, (int)tokens, (int)world, ew.pos, ew.send_count);
   AKO_CHECK_LAUNCH();
-  ep::ep_send_kernel<<<(unsigned)ako::cdiv(tokens * world > 0 ? tokens * world : 1, 8), 256, 0, st>>>(
+  const int64_t comm_ctas = (int64_t)ako::sm_count() * 4;   // persistent, grid-stride
+  int64_t send_ctas = ako::cdiv(tokens * world > 0 ? tokens * world : 1, 8);
+  if (send_ctas > comm_ctas) send_ctas = comm_ctas;
+  ep::ep_send_kernel<<<(unsigned)send_ctas, 256, 0, st>>>(
       (const uint8_t*)hidden_states, hidden_states_scale, ew.ids, ew.wts, ew.pos, ew.send_count, (int)tokens,
       (int)world, (int)rank, cap_rows, step, peers);
   AKO_CHECK_LAUNCH();
@@ -509,7 +512,7 @@ extern "C" int ako4x_moe_fp8_block_scale_ep(
   p2.y = w.y;
   const int rc = launch_gemms_tc(p1, p2, pair_capacity, n_local, ako::sm_count(), st, [](int) {});
   if (rc != AKO4X_OK) return rc;
-  ep::ep_return_kernel<<<(unsigned)vtokens, 256, 0, st>>>(w.y, w.pair_pos, w.topk_w, w.topk_ids, (int)world, (int)rank,
+  ep::ep_return_kernel<<<(unsigned)(vtokens < comm_ctas ? vtokens : comm_ctas), 256, 0, st>>>(w.y, w.pair_pos, w.topk_w, w.topk_ids, (int)world, (int)rank,
                                                            cap_rows, step, peers);
   AKO_CHECK_LAUNCH();
 

@@ -125,8 +125,11 @@ __global__ void __launch_bounds__(256) ep_send_kernel(
     const float* __restrict__ topk_w, const int32_t* __restrict__ pos, const int32_t* __restrict__ send_count,
     int tokens, int world, int rank, int64_t cap, int step, Peers peers) {
   const int lane = threadIdx.x & 31;
-  const int64_t pair = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);  // token * world + dest
-  if (pair < (int64_t)tokens * world) {
+  const int64_t npairs = (int64_t)tokens * world;
+  // grid-stride: a CTA fences once, after all of its rows (a system-scope fence after remote stores
+  // costs a round trip over NVLink)
+  for (int64_t pair = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); pair < npairs;
+       pair += (int64_t)gridDim.x * (blockDim.x >> 5)) {  // pair = token * world + dest
     const int p = pos[pair];
     if (p >= 0) {
       const int64_t t = pair / world;
@@ -217,7 +220,7 @@ __global__ void __launch_bounds__(256) ep_permute_kernel(
 __global__ void __launch_bounds__(256) ep_return_kernel(
     const float* __restrict__ y, const int32_t* __restrict__ pair_pos, const float* __restrict__ topk_w,
     const int32_t* __restrict__ topk_ids, int world, int rank, int64_t cap, int step, Peers peers) {
-  const int64_t v = blockIdx.x;
+  for (int64_t v = blockIdx.x; v < (int64_t)world * cap; v += gridDim.x) {
   const int s = (int)(v / cap);
   const int64_t i = v - (int64_t)s * cap;
   if (topk_ids[v * TOPK] >= 0) {  // the row exists (ids of missing rows are all -1)
@@ -244,6 +247,7 @@ __global__ void __launch_bounds__(256) ep_return_kernel(
       pk.y = ako::pack_bf16x2(a.z, a.w);
       *reinterpret_cast<uint2*>(out + c) = pk;
     }
+  }
   }
   __threadfence_system();
   __syncthreads();

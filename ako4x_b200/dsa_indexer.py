@@ -75,3 +75,31 @@ def topk_select(scores, seq_lens, block_table):
     del keep
     _cabi.check(st, "ako4x_dsa_topk_select")
     return out
+
+
+@torch.no_grad()
+def run_with_attention(q_index_fp8, k_index_cache_fp8, weights, seq_lens, block_table, q_nope, q_pe, ckv_cache,
+                       kpe_cache, sm_scale):
+    """Indexer followed by sparse MLA attention in one call, the top-k list staying on the device
+    (the pair of reference plug-ins dsa-topk-indexer / dsa-sparse-attention run back to back).
+    Returns (o, lse, topk_indices)."""
+    from .mla_decode import check_mla_inputs
+    rows, npages, max_pages = _check(q_index_fp8, k_index_cache_fp8, weights, seq_lens, block_table)
+    check_mla_inputs("dsa_indexer_attention", q_nope, q_pe, ckv_cache, kpe_cache)
+    if q_nope.shape[0] != rows or ckv_cache.shape[0] != npages or ckv_cache.shape[1] != 64:
+        raise _cabi.Ako4xError("dsa_indexer_attention: one query row per indexer row, caches of [pages, 64, .]")
+    L = _cabi.lib()
+    dev = q_index_fp8.device
+    topk = torch.empty((rows, TOPK), dtype=torch.int32, device=dev)
+    o = torch.empty(q_nope.shape, dtype=q_nope.dtype, device=dev)
+    lse = torch.empty((rows, 16), dtype=torch.float32, device=dev)
+    ws_bytes = L.ako4x_dsa_indexer_attention_workspace_bytes(rows, max_pages)
+    ws = _cabi.workspace(ws_bytes, dev)
+    keep = [t.contiguous() for t in (q_index_fp8, k_index_cache_fp8, weights, seq_lens, block_table, q_nope, q_pe)]
+    st = L.ako4x_dsa_indexer_attention(
+        *[_cabi.ptr(t) for t in keep], _cabi.ptr(ckv_cache), _cabi.ptr(kpe_cache), float(sm_scale),
+        _cabi.ptr(topk), _cabi.ptr(o), _cabi.ptr(lse), rows, max_pages, npages, _cabi.ptr(ws), ws_bytes,
+        _cabi.stream())
+    del keep
+    _cabi.check(st, "ako4x_dsa_indexer_attention")
+    return o, lse, topk

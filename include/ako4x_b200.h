@@ -215,6 +215,32 @@ int ako4x_moe_ds_routing(const float* routing_logits, const void* routing_bias, 
 int ako4x_moe_ep_combine(const void* rows, const int32_t* pos, void* out, int64_t tokens,
                          int64_t world, int64_t cols, void* stream);
 
+/* ---- The producers in front of the operator set (same layer, one step earlier) ---------------
+ * FP8 activation quantiser: x bf16 [rows, cols] (cols a multiple of 128) -> q e4m3 [rows, cols] and
+ * scale fp32 [cols/128, rows] (block-major, the layout a7 takes as hidden_states_scale). Per 128
+ * consecutive values: scale = amax / 448 (1.0 when amax <= 1e-10), q = e4m3(x / scale), the rule
+ * of reference/moe-fp8-block-scale/variants/fused_routing_v2/kernel.py:495-503. */
+int ako4x_fp8_quantize_1x128(const void* x, void* q, float* scale, int64_t rows, int64_t cols,
+                             void* stream);
+/* Index-K cache writer: k bf16 [tokens, 128] -> the paged cache a5 reads (8448 bytes per page: 64 x
+ * 128 e4m3 values, then 64 fp32 scales; reference/dsa-topk-indexer/variants/v8_radix_bt256/
+ * kernel.py:562, 621-625). slot_mapping int32 [tokens] = page * 64 + slot of every token, -1 to skip
+ * it. Per token: scale = amax / 448 (1.0 when amax <= 1e-10), values e4m3(k / scale). */
+int ako4x_dsa_index_k_cache_write(const void* k, const int32_t* slot_mapping, void* k_index_cache,
+                                  int64_t tokens, int64_t num_cache_pages, void* stream);
+/* a5 followed by a6 on one stream, the top-k list staying on the device: the arguments of both
+ * operators, `topk_indices` int32 [rows, 2048] as the hand-over buffer (an output as well), one
+ * workspace of ako4x_dsa_indexer_attention_workspace_bytes bytes. The attention kernels are
+ * launched with programmatic dependent launch so that their prologue overlaps the selection's
+ * tail. References as for a5 and a6. */
+size_t ako4x_dsa_indexer_attention_workspace_bytes(int64_t rows, int64_t max_pages);
+int ako4x_dsa_indexer_attention(const void* q_index_fp8, const void* k_index_cache, const float* weights,
+                                const int32_t* seq_lens, const int32_t* block_table,
+                                const void* q_nope, const void* q_pe, const void* ckv_cache,
+                                const void* kpe_cache, float sm_scale, int32_t* topk_indices, void* o,
+                                float* lse, int64_t rows, int64_t max_pages, int64_t num_cache_pages,
+                                void* workspace, size_t workspace_bytes, void* stream);
+
 /* ---- Expert-parallel form of a7 over NVLink peer memory (no counterpart in the reference, which is
  * single-GPU) ---------------------------------------------------------------------------------
  * One process per GPU; rank r owns experts [32r, 32r+32) (routing group r). Every rank allocates

@@ -9,3 +9,4 @@ from .attention import (  # noqa: F401
     gqa_paged_decode, mla_paged_decode, mla_paged_prefill, dsa_sparse_attention)
 from .indexer import dsa_index_scores, dsa_topk_select, dsa_topk_indexer, unpack_index_cache  # noqa: F401
 from .moe import ds_routing, moe_fp8_block_scale  # noqa: F401
+from .quantize import fp8_quantize_1x128, index_k_cache_write  # noqa: F401
