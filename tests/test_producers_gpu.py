@@ -25,7 +25,7 @@ def test_quantiser_bit_exact(built_lib, rows, cols):
     # first-principles check of the rule itself: dequantised values within half an e4m3 step
     deq = q.cpu().float().reshape(rows, cols // 128, 128) * rs.t().unsqueeze(-1)
     err = (deq - x.float().reshape(rows, cols // 128, 128)).abs()
-    assert (err <= rs.t().unsqueeze(-1) * 16.0 + 1e-30).all()    # 448 has 3 mantissa bits: step <= 32 at the top
+    assert (err <= rs.t().unsqueeze(-1) * 16.0 * 1.001 + 1e-30).all()   # 3 mantissa bits: step <= 32 at the top (ties land exactly on 16)
 
 
 def test_quantiser_feeds_the_moe(built_lib):
@@ -61,7 +61,7 @@ def test_index_k_cache_writer_bit_exact_and_readable(built_lib):
     t = 7
     page, s = divmod(int(slots[t]), 64)
     deq = vals[page, s] * scales[page, s]
-    assert (deq - k[t].float()).abs().max() <= scales[page, s] * 16.0
+    assert (deq - k[t].float()).abs().max() <= scales[page, s] * 16.0 * 1.001
 
 
 @pytest.mark.parametrize("tokens,ctx", [(3, 1500), (24, 6000)])
