@@ -96,6 +96,25 @@ __device__ __forceinline__ float fast_exp2(float x) {
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;\n" ::); }
 
+// Launch with programmatic dependent launch allowed: the kernel may be scheduled while its
+// predecessor on the stream is still running; it must execute pdl_wait() before it touches anything
+// the predecessor wrote (the wait returns when the predecessor grid has completed).
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                              Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 // Opts a kernel into `bytes` of dynamic shared memory once per device. The kernel is a template
 // argument so that every kernel gets its own flags; a race between host threads only repeats
 // the call.

@@ -205,6 +205,8 @@ __global__ void __launch_bounds__(1024) moe_scatter_kernel(
   const int le = blockIdx.x;
   const int ge = local_off + le;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  ako::pdl_wait();      // the routing lists and counts come from the previous kernel
+  ako::pdl_trigger();
   if (warp == 0) {
     int acc = 0;
     for (int i = lane; i < le; i += 32) acc += counts[i];
@@ -294,6 +296,8 @@ __global__ void __launch_bounds__(256) moe_permute_kernel(
     uint8_t* __restrict__ xs, float* __restrict__ xs_scale, int tokens, int64_t cap) {
   const int lane = threadIdx.x & 31;
   const int64_t slot = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);  // token*8 + k
+  ako::pdl_wait();
+  ako::pdl_trigger();
   if (slot >= (int64_t)tokens * TOPK) return;
   const int pos = pair_pos[slot];
   if (pos < 0) return;
@@ -317,6 +321,8 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(
   const int64_t tkn = blockIdx.x;
   int pos[TOPK];
   float w[TOPK];
+  ako::pdl_wait();
+  ako::pdl_trigger();
 #pragma unroll
   for (int s = 0; s < TOPK; ++s) {
     pos[s] = pair_pos[tkn * TOPK + s];
@@ -378,11 +384,11 @@ int launch_gemms_tc(const GemmParams& p1, const GemmParams& p2, int64_t cap, int
       !ako::tma::byte_matrix_map(&a2, p2.a, (uint64_t)cap, 2 * INTER, TC_BM) ||
       !ako::tma::byte_matrix_map(&b2, p2.w, (uint64_t)n_local * HID, INTER, TC_BN))
     return AKO4X_ELAUNCH;
-  moe_gemm_tc_kernel<1><<<sms, TC_THREADS, TC_SMEM, st>>>(p1, a1, b1);
-  AKO_CHECK_LAUNCH();
+  if (ako::launch_pdl(moe_gemm_tc_kernel<1>, dim3(sms), dim3(TC_THREADS), TC_SMEM, st, p1, a1, b1) != cudaSuccess)
+    return AKO4X_ELAUNCH;
   mark(2);
-  moe_gemm_tc_kernel<2><<<sms, TC_THREADS, TC_SMEM, st>>>(p2, a2, b2);
-  AKO_CHECK_LAUNCH();
+  if (ako::launch_pdl(moe_gemm_tc_kernel<2>, dim3(sms), dim3(TC_THREADS), TC_SMEM, st, p2, a2, b2) != cudaSuccess)
+    return AKO4X_ELAUNCH;
   return AKO4X_OK;
 }
 
@@ -592,10 +598,10 @@ extern "C" int ako4x_moe_fp8_block_scale_staged(
       routing_logits, routing_bias, bias_is_bf16, routed_scaling_factor, (int)tokens, w.topk_ids,
       w.topk_w, w.pair_pos, w.counts, local_expert_offset, n_local);
   AKO_CHECK_LAUNCH();
-  moe_scatter_kernel<<<n_local, 1024, 0, st>>>(w.topk_ids, w.counts, w.offsets, w.sorted_token, w.pair_pos,
-                                                (int)tokens, local_expert_offset, n_local, (int)cap, w.counts_fit,
-                                                w.counts + MAX_LOCAL);
-  AKO_CHECK_LAUNCH();
+  if (ako::launch_pdl(moe_scatter_kernel, dim3(n_local), dim3(1024), 0, st, w.topk_ids, w.counts, w.offsets,
+                      w.sorted_token, w.pair_pos, (int)tokens, (int)local_expert_offset, n_local, (int)cap,
+                      w.counts_fit, w.counts + MAX_LOCAL) != cudaSuccess)
+    return AKO4X_ELAUNCH;
 
   GemmParams p1 = {};
   p1.a = (const uint8_t*)hidden_states;
@@ -621,9 +627,10 @@ extern "C" int ako4x_moe_fp8_block_scale_staged(
   const int sms = ako::sm_count();
   mark(1);
   int rc;
-  moe_permute_kernel<<<(unsigned)ako::cdiv(tokens * TOPK, 8), 256, 0, st>>>(
-      (const uint8_t*)hidden_states, hidden_states_scale, w.pair_pos, w.xs, w.xs_scale, (int)tokens, cap);
-  AKO_CHECK_LAUNCH();
+  if (ako::launch_pdl(moe_permute_kernel, dim3((unsigned)ako::cdiv(tokens * TOPK, 8)), dim3(256), 0, st,
+                      (const uint8_t*)hidden_states, hidden_states_scale, w.pair_pos, w.xs, w.xs_scale, (int)tokens,
+                      cap) != cudaSuccess)
+    return AKO4X_ELAUNCH;
   GemmParams t1 = p1;
   t1.a = w.xs;
   t1.a_scale = w.xs_scale;
@@ -631,8 +638,9 @@ extern "C" int ako4x_moe_fp8_block_scale_staged(
   rc = launch_gemms_tc(t1, p2, cap, n_local, sms, st, mark);
   if (rc != AKO4X_OK) return rc;
   mark(3);
-  moe_combine_kernel<<<(unsigned)tokens, 256, 0, st>>>(w.y, w.pair_pos, w.topk_w, (__nv_bfloat16*)out);
-  AKO_CHECK_LAUNCH();
+  if (ako::launch_pdl(moe_combine_kernel, dim3((unsigned)tokens), dim3(256), 0, st, (const float*)w.y,
+                      (const int32_t*)w.pair_pos, (const float*)w.topk_w, (__nv_bfloat16*)out) != cudaSuccess)
+    return AKO4X_ELAUNCH;
   mark(4);
   return AKO4X_OK;
 }
