@@ -194,7 +194,6 @@ moe_gemm_tc_kernel(GemmParams p, const __grid_constant__ CUtensorMap tm_a, const
       const TileInfo ti = tc_tile_info<NT_TILES>(p, s_cum, tile);
       const int tile_par = tcount & 1;
       const bool live = r < ti.rows;
-      const bool warp_live = 32 * q < ti.rows;
       const float* asp = p.a_scale + (live ? ti.row0 + r : 0);
       const float* bsp0;
       const float* bsp1;
@@ -224,13 +223,6 @@ moe_gemm_tc_kernel(GemmParams p, const __grid_constant__ CUtensorMap tm_a, const
         const int buf = g & 1;
         const uint32_t aph = (g >> 1) & 1;
         if (!ako::tc::mbar_wait(ako::smem_u32(&s_acc_full[buf]), aph, p.error, kErrEpilogue)) { ok = false; break; }
-        if (!warp_live) {
-          // none of this warp's 32 rows belongs to the tile (few rows per expert): it only keeps the
-          // barrier protocol (one arrival per warp and K block, after the accumulator is complete)
-          // and leaves the issue slots to the warps that have rows
-          if (lane == 0) ako::tc::mbar_arrive(ako::smem_u32(&s_acc_empty[buf]));
-          continue;
-        }
         ako::tc::fence_after_thread_sync();
         const uint32_t taddr = tmem_base + ((uint32_t)(32 * q) << 16) + buf * TC_BN + half * 128;
         float v0[32], v1[32];
@@ -259,7 +251,6 @@ moe_gemm_tc_kernel(GemmParams p, const __grid_constant__ CUtensorMap tm_a, const
       if (!ok) break;
 
       if (WHICH == 2) {
-        if (!warp_live) continue;   // no row of this warp belongs to the tile: nothing to store
         // A thread holds 128 columns of ONE row; stored directly, a warp's instruction would touch
         // 32 rows with 16 bytes each. Each warp transposes 32-column chunks through its own 4 KB
         // of shared memory (16-byte groups XOR-swizzled by row: conflict-free both ways) so that an
