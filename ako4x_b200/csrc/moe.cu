@@ -311,6 +311,8 @@ __global__ void __launch_bounds__(256) moe_permute_kernel(
 
 // The tcgen05 / TMEM form of the grouped GEMM (same GemmParams, same tile-list convention).
 #include "moe_gemm_tc.cuh"
+// The same GEMM as a CTA pair sharing a 256 x 256 tile (cta_group::2).
+#include "moe_gemm_tc2.cuh"
 
 // ---------------------------------------------------------------------------------------------
 // 5. combine
@@ -372,18 +374,99 @@ __global__ void __launch_bounds__(256) moe_ep_combine_kernel(
 }
 
 
-// p1 / p2 are the GEMM1 / GEMM2 parameters with the expert-sorted activation copy as A.
+// Launch of a kernel as clusters of two CTAs (optionally with programmatic dependent launch).
+// Whether the grouped GEMMs run as CTA pairs (moe_gemm_tc2.cuh). Off unless AKO4X_MOE_PAIRS=1 is set
+// in the environment: the pair kernel is parity-green and its K loop is shorter in cycles (1 040 per
+// 256 x 256 x 128 block against 2 x 1 250 for two one-CTA tiles), but at the benchmark shape it
+// measured slower end to end (GEMM1 430 us against 359 us): with about 254 rows per expert, 14 of
+// 32 experts need a second pair for a handful of rows (46 pair tiles where 39 would do), and the
+// busier tensor pipe pulls the SM clock from 1 965 to about 1 740 MHz under the power cap.
+bool use_pairs(int64_t tokens, int n_local) {
+  (void)tokens;
+  (void)n_local;
+  static const bool forced = [] {
+    const char* e = std::getenv("AKO4X_MOE_PAIRS");
+    return e != nullptr && e[0] == '1';
+  }();
+  return forced;
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pairs(bool overlap, void (*kernel)(KArgs...), int ctas, int threads, size_t smem,
+                                cudaStream_t st, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)ctas);
+  cfg.blockDim = dim3((unsigned)threads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = overlap ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 2;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
+// CTAs of the pair kernels that can be resident at once (2 x the co-resident clusters), per device.
+int pair_grid() {
+  static std::atomic<int> cached[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+  int n = cached[dev].load(std::memory_order_relaxed);
+  if (n == 0) {
+    if (!ako::ensure_dynamic_smem<moe_gemm_tc2_kernel<1>>(T2_SMEM) ||
+        !ako::ensure_dynamic_smem<moe_gemm_tc2_kernel<2>>(T2_SMEM))
+      return 0;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(ako::sm_count() & ~1));
+    cfg.blockDim = dim3(TC_THREADS);
+    cfg.dynamicSmemBytes = T2_SMEM;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int clusters = 0;
+    if (cudaOccupancyMaxActiveClusters(&clusters, moe_gemm_tc2_kernel<1>, &cfg) != cudaSuccess || clusters <= 0) {
+      (void)cudaGetLastError();
+      n = -1;   // pairs are not available on this device: the one-CTA kernel is used
+    } else {
+      n = 2 * clusters;
+      if (n > (ako::sm_count() & ~1)) n = ako::sm_count() & ~1;
+    }
+    cached[dev].store(n, std::memory_order_relaxed);
+  }
+  return n > 0 ? n : 0;
+}
+
+// p1 / p2 are the GEMM1 / GEMM2 parameters with the expert-sorted activation copy as A. `pairs`:
+// most experts have two or more 128-row tiles, so the CTA-pair kernel (256 x 256 tiles) pays.
 template <typename Mark>
 int launch_gemms_tc(const GemmParams& p1, const GemmParams& p2, int64_t cap, int n_local, int sms,
-                    cudaStream_t st, Mark mark, bool pdl) {
-  if (!ako::ensure_dynamic_smem<moe_gemm_tc_kernel<1>>(TC_SMEM)) return AKO4X_ELAUNCH;
-  if (!ako::ensure_dynamic_smem<moe_gemm_tc_kernel<2>>(TC_SMEM)) return AKO4X_ELAUNCH;
+                    cudaStream_t st, Mark mark, bool pdl, bool pairs) {
   CUtensorMap a1, b1, a2, b2;
+  const int pgrid = pairs ? pair_grid() : 0;
   if (!ako::tma::byte_matrix_map(&a1, p1.a, (uint64_t)cap, HID, TC_BM) ||
       !ako::tma::byte_matrix_map(&b1, p1.w, (uint64_t)n_local * 2 * INTER, HID, 64) ||
       !ako::tma::byte_matrix_map(&a2, p2.a, (uint64_t)cap, 2 * INTER, TC_BM) ||
-      !ako::tma::byte_matrix_map(&b2, p2.w, (uint64_t)n_local * HID, INTER, TC_BN))
+      !ako::tma::byte_matrix_map(&b2, p2.w, (uint64_t)n_local * HID, INTER, pgrid > 0 ? 128 : TC_BN))
     return AKO4X_ELAUNCH;
+  if (pgrid > 0) {
+    if (launch_pairs(pdl, moe_gemm_tc2_kernel<1>, pgrid, TC_THREADS, T2_SMEM, st, p1, a1, b1) != cudaSuccess)
+      return AKO4X_ELAUNCH;
+    mark(2);
+    if (launch_pairs(pdl, moe_gemm_tc2_kernel<2>, pgrid, TC_THREADS, T2_SMEM, st, p2, a2, b2) != cudaSuccess)
+      return AKO4X_ELAUNCH;
+    return AKO4X_OK;
+  }
+  if (!ako::ensure_dynamic_smem<moe_gemm_tc_kernel<1>>(TC_SMEM)) return AKO4X_ELAUNCH;
+  if (!ako::ensure_dynamic_smem<moe_gemm_tc_kernel<2>>(TC_SMEM)) return AKO4X_ELAUNCH;
   if (ako::launch_pdl(pdl, moe_gemm_tc_kernel<1>, dim3(sms), dim3(TC_THREADS), TC_SMEM, st, p1, a1, b1) != cudaSuccess)
     return AKO4X_ELAUNCH;
   mark(2);
@@ -516,7 +599,8 @@ extern "C" int ako4x_moe_fp8_block_scale_ep(
   p2.w = (const uint8_t*)gemm2_weights;
   p2.w_scale = gemm2_weights_scale;
   p2.y = w.y;
-  const int rc = launch_gemms_tc(p1, p2, pair_capacity, n_local, ako::sm_count(), st, [](int) {}, false);
+  const int rc = launch_gemms_tc(p1, p2, pair_capacity, n_local, ako::sm_count(), st, [](int) {}, false,
+                                 use_pairs(vtokens * 32 / NE, n_local));
   if (rc != AKO4X_OK) return rc;
   ep::ep_return_kernel<<<(unsigned)(vtokens < comm_ctas ? vtokens : comm_ctas), 256, 0, st>>>(w.y, w.pair_pos, w.topk_w, w.topk_ids, (int)world, (int)rank,
                                                            cap_rows, step, peers);
@@ -638,7 +722,7 @@ extern "C" int ako4x_moe_fp8_block_scale_staged(
   t1.a = w.xs;
   t1.a_scale = w.xs_scale;
   t1.a_scale_stride = cap;
-  rc = launch_gemms_tc(t1, p2, cap, n_local, sms, st, mark, pdl);
+  rc = launch_gemms_tc(t1, p2, cap, n_local, sms, st, mark, pdl, use_pairs(tokens, n_local));
   if (rc != AKO4X_OK) return rc;
   mark(3);
   if (ako::launch_pdl(pdl, moe_combine_kernel, dim3((unsigned)tokens), dim3(256), 0, st, (const float*)w.y,
