@@ -375,12 +375,14 @@ __global__ void __launch_bounds__(256) moe_ep_combine_kernel(
 
 
 // Launch of a kernel as clusters of two CTAs (optionally with programmatic dependent launch).
-// Whether the grouped GEMMs run as CTA pairs (moe_gemm_tc2.cuh). Off unless AKO4X_MOE_PAIRS=1 is set
-// in the environment: the pair kernel is parity-green and its K loop is shorter in cycles (1 040 per
-// 256 x 256 x 128 block against 2 x 1 250 for two one-CTA tiles), but at the benchmark shape it
-// measured slower end to end (GEMM1 430 us against 359 us): with about 254 rows per expert, 14 of
-// 32 experts need a second pair for a handful of rows (46 pair tiles where 39 would do), and the
-// busier tensor pipe pulls the SM clock from 1 965 to about 1 740 MHz under the power cap.
+// Whether the grouped GEMMs run as CTA pairs (moe_gemm_tc2.cuh): only when AKO4X_MOE_PAIRS=1 is set
+// in the environment. The pair kernel is parity-green and its K loop is shorter in cycles (1 040 per
+// 256 x 256 x 128 block against 2 x 1 250 for two one-CTA tiles), yet it measured slower in time at
+// every size tried: T = 8192: GEMM1 430 us against 359 us (about 254 rows per expert: 14 of 32
+// experts need a second pair tile for a handful of rows, 46 pair tiles where 39 would do);
+// T = 16384 / 32768 whole operator: 1 618 / 2 750 us against 1 436 / 2 566 us. The busier tensor
+// pipe pulls the SM clock from 1 965 to about 1 740 MHz and lower under the 1 kW power cap, which
+// costs more than the cycles saved.
 bool use_pairs(int64_t tokens, int n_local) {
   (void)tokens;
   (void)n_local;

@@ -146,6 +146,54 @@ def test_full_size_sampled_rows_against_oracle(built_lib, weights, offset):
     assert strict >= STRICT_MATCH_MIN
 
 
+def test_large_call_sampled_rows(built_lib, weights):
+    """T = 16384 (about 512 rows per expert, four and more m-tiles per expert): 64 sampled tokens
+    against the oracle."""
+    a = _case(weights, 16384, shape_id=21, offset=32)
+    out = moe.run_checked(*[a[k] for k in KEYS])
+    g = torch.Generator().manual_seed(77)
+    dsel = torch.randperm(16384, generator=g)[:64].sort().values.cuda()
+    sub = dict(a)
+    sub["routing_logits"] = a["routing_logits"][dsel]
+    sub["hidden_states"] = a["hidden_states"].view(torch.uint8)[dsel].view(torch.float8_e4m3fn)
+    sub["hidden_states_scale"] = a["hidden_states_scale"][:, dsel].contiguous()
+    ref = _oracle(sub)
+    assert float(ref.float().abs().max()) > 0
+    fro, strict, harness = _report(out[dsel], ref)
+    print(f"T=16384, 64 sampled rows: rel_fro={fro:.2e} strict={strict:.4f} harness={harness:.5f}")
+    assert fro <= REL_FROBENIUS_MAX and harness >= HARNESS_MATCH_MIN and strict >= STRICT_MATCH_MIN
+
+
+def test_cta_pair_gemm_matches_the_default_path(built_lib, weights):
+    """The opt-in CTA-pair form of the grouped GEMMs (AKO4X_MOE_PAIRS=1, read once per process) must
+    give the same result as the default kernel; it runs in a child process for that reason."""
+    import os
+    import subprocess
+    import sys
+    code = (
+        "import sys, torch; sys.path.insert(0, %r); sys.path.insert(0, %r)\n"
+        "import oracle\n"
+        "from ako4x_b200 import moe, workloads as W\n"
+        "KEYS = %r\n"
+        "a = W.make_moe(2048, shape_id=5, device='cuda', num_local_experts=4, local_expert_offset=0)\n"
+        "a['routing_logits'][:, :4] += 3.0\n"
+        "out = moe.run_checked(*[a[k] for k in KEYS])\n"
+        "c = {k: (v.cpu() if torch.is_tensor(v) else v) for k, v in a.items()}\n"
+        "sel = torch.arange(0, 2048, 37)\n"
+        "c['routing_logits'] = c['routing_logits'][sel]; c['hidden_states'] = c['hidden_states'].view(torch.uint8)[sel].view(torch.float8_e4m3fn)\n"
+        "c['hidden_states_scale'] = c['hidden_states_scale'][:, sel].contiguous()\n"
+        "ref = oracle.moe_fp8_block_scale(*[c[k] for k in KEYS])\n"
+        "err = (out.cpu()[sel].float() - ref.float())\n"
+        "print('REL', float(err.norm() / ref.float().norm()))\n"
+    ) % (str(__import__('pathlib').Path(__file__).resolve().parents[1]),
+         str(__import__('pathlib').Path(__file__).resolve().parent), KEYS)
+    env = dict(os.environ, AKO4X_MOE_PAIRS="1")
+    res = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=300, env=env)
+    assert res.returncode == 0, res.stderr[-2000:]
+    rel = float([ln for ln in res.stdout.splitlines() if ln.startswith("REL")][-1].split()[1])
+    assert rel <= REL_FROBENIUS_MAX, rel
+
+
 def test_non_contiguous_inputs(built_lib, weights):
     """A transposed scale matrix and strided logits make the wrapper take contiguous copies; the
     copies must stay alive until the launch (result equal to the contiguous call)."""
