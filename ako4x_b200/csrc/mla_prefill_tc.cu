@@ -54,7 +54,14 @@ constexpr int THREADS = 512;
 constexpr int REGS_O = 184, REGS_SOFTMAX = 104, REGS_OTHER = 40;  // 2*184 + 104 + 40 = 4*128
 constexpr float NEG = -1.0e30f;           // finite stand-in for -inf
 
+// Wait status of the CURRENT call (cleared by the gather kernel that starts every call, so a code
+// left by an earlier call cannot make this call's waits give up early) and the sticky word that
+// ako_mla_prefill_tc_status() reports. The per-call word stays in global memory on purpose: with
+// the word in shared memory, as in the other kernels, this kernel measured 18 % slower (1 463 ->
+// 1 725 us at the benchmark shape; the roles that run on 40 registers do not take the extra pointer
+// well).
 __device__ int g_pf_status = 0;
+__device__ int g_pf_sticky = 0;
 
 struct PfParams {
   const int32_t* qo_indptr;
@@ -83,6 +90,7 @@ __global__ void __launch_bounds__(256) mla_prefill_gather_kernel(
   __shared__ int64_t s_col[G_TOK];
   const int tid = threadIdx.x;
   const int64_t g0 = (int64_t)blockIdx.x * G_TOK;
+  if (blockIdx.x == 0 && tid == 0) g_pf_status = 0;  // this call's wait status starts clean
   if (tid < G_TOK) {
     const int64_t g = g0 + tid;
     int64_t row = 0, col = -1;
@@ -127,7 +135,7 @@ mla_prefill_tc_kernel(PfParams p, const __grid_constant__ CUtensorMap tm_qn, con
   const int half = blockIdx.y;  // which 256 output columns
   unsigned char* smem_al = smem_raw;
   if (ako::smem_u32(smem_raw) & 1023u) {  // the swizzled operand tiles need this; nothing is started yet
-    if (tid == 0) atomicCAS(&g_pf_status, 0, 13);
+    if (tid == 0) atomicCAS(&g_pf_sticky, 0, 13);
     return;
   }
   const uint32_t st_base = ako::smem_u32(smem_al);
@@ -147,7 +155,6 @@ mla_prefill_tc_kernel(PfParams p, const __grid_constant__ CUtensorMap tm_qn, con
   uint64_t& fin = bars[2 * NST + 9];
   uint32_t& s_tmem = *reinterpret_cast<uint32_t*>(bars + 2 * NST + 10);
   int* s_work = reinterpret_cast<int*>(bars + 2 * NST + 11);  // sequence, tile inside the sequence (or -1)
-  int* s_err = s_work + 2;  // code of a wait of this CTA that gave up (0 = none), published on exit
 
   if (tid == 0) {
     // reversed: within a sequence the later query tiles see more keys, so the long CTAs start
@@ -160,7 +167,6 @@ mla_prefill_tc_kernel(PfParams p, const __grid_constant__ CUtensorMap tm_qn, con
     }
     s_work[0] = b;
     s_work[1] = (b < p.batch) ? t : -1;
-    *s_err = 0;
     for (int s = 0; s < NST; ++s) {
       ako::tc::mbar_init(ako::smem_u32(&st_full[s]), 1);
       ako::tc::mbar_init(ako::smem_u32(&st_empty[s]), 1);
@@ -211,7 +217,7 @@ mla_prefill_tc_kernel(PfParams p, const __grid_constant__ CUtensorMap tm_qn, con
     for (int i = 0; i < 128; ++i) o[i] = 0.f;
     bool ok = true;
     for (int j = 0; j < ntk; ++j) {
-      if (!ako::tc::mbar_wait(ako::smem_u32(&pv_full), (uint32_t)(j & 1), s_err, 1)) { ok = false; break; }
+      if (!ako::tc::mbar_wait(ako::smem_u32(&pv_full), (uint32_t)(j & 1), &g_pf_status, 1)) { ok = false; break; }
       ako::tc::fence_after_thread_sync();
       const float a = alpha_s[(j & 3) * BM + r];
 #pragma unroll
@@ -228,7 +234,7 @@ mla_prefill_tc_kernel(PfParams p, const __grid_constant__ CUtensorMap tm_qn, con
         for (int i = 0; i < 32; ++i) o[32 * c + i] = fmaf(o[32 * c + i], a, v[i]);
       }
     }
-    if (ok && tile >= 0 && ako::tc::mbar_wait(ako::smem_u32(&fin), 0u, s_err, 2)) {
+    if (ok && tile >= 0 && ako::tc::mbar_wait(ako::smem_u32(&fin), 0u, &g_pf_status, 2)) {
       const int qtok = r >> 4;
       if (qtok < nq) {
         const float l = fin_l[r];
@@ -257,7 +263,7 @@ mla_prefill_tc_kernel(PfParams p, const __grid_constant__ CUtensorMap tm_qn, con
     bool ok = true;
     for (int j = 0; j < ntk; ++j) {
       const int buf = j & 1;
-      if (!ako::tc::mbar_wait(ako::smem_u32(&s_full[buf]), (uint32_t)((j >> 1) & 1), s_err, 3)) { ok = false; break; }
+      if (!ako::tc::mbar_wait(ako::smem_u32(&s_full[buf]), (uint32_t)((j >> 1) & 1), &g_pf_status, 3)) { ok = false; break; }
       ako::tc::fence_after_thread_sync();
       const uint32_t ts = tq + buf * BK;
       const int nvis = kv_lim - j * BK;  // visible keys of this tile for this row (may be <= 0 or > 128)
@@ -328,7 +334,7 @@ mla_prefill_tc_kernel(PfParams p, const __grid_constant__ CUtensorMap tm_qn, con
       // with masked rows does not), so it may finish tile j before a slow warp has finished tile
       // j-1; its arrival would then complete the phase of tile j-1 in the slow warp's place. Wait
       // until all four warps have arrived for tile j-1 before arriving for tile j.
-      if (j > 0 && !ako::tc::mbar_wait(ako::smem_u32(&p_full), (uint32_t)((j - 1) & 1), s_err, 4)) { ok = false; break; }
+      if (j > 0 && !ako::tc::mbar_wait(ako::smem_u32(&p_full), (uint32_t)((j - 1) & 1), &g_pf_status, 4)) { ok = false; break; }
       __syncwarp();
       if (lane == 0) ako::tc::mbar_arrive(ako::smem_u32(&p_full));
     }
@@ -351,7 +357,7 @@ mla_prefill_tc_kernel(PfParams p, const __grid_constant__ CUtensorMap tm_qn, con
         bool ok = true;
         for (int c = 0; c < NCH; ++c, ++g) {
           const int stage = g % NST;
-          if (!ako::tc::mbar_wait(ako::smem_u32(&st_empty[stage]), (uint32_t)(((g / NST) & 1) ^ 1), s_err, 5)) { ok = false; break; }
+          if (!ako::tc::mbar_wait(ako::smem_u32(&st_empty[stage]), (uint32_t)(((g / NST) & 1) ^ 1), &g_pf_status, 5)) { ok = false; break; }
           const uint32_t bar = ako::smem_u32(&st_full[stage]);
           const uint32_t dst = st_base + stage * ST_BYTES;
           ako::tc::mbar_arrive_expect_tx(bar, ST_BYTES);
@@ -365,7 +371,7 @@ mla_prefill_tc_kernel(PfParams p, const __grid_constant__ CUtensorMap tm_qn, con
       // ================================ V producer ==============================================
       ako::tc::tma_prefetch_desc(&tm_v);
       for (int j = 0; j < ntk; ++j) {
-        if (!ako::tc::mbar_wait(ako::smem_u32(&v_empty), (uint32_t)((j & 1) ^ 1), s_err, 6)) break;
+        if (!ako::tc::mbar_wait(ako::smem_u32(&v_empty), (uint32_t)((j & 1) ^ 1), &g_pf_status, 6)) break;
         const uint32_t bar = ako::smem_u32(&v_full);
         ako::tc::mbar_arrive_expect_tx(bar, V_BYTES);
         const int x = (int)(vbase + (int64_t)j * BK);
@@ -380,12 +386,12 @@ mla_prefill_tc_kernel(PfParams p, const __grid_constant__ CUtensorMap tm_qn, con
       for (int j = 0; j < ntk; ++j) {
         const int buf = j & 1;
         // the PV MMAs of tile j-2 have read P out of this buffer
-        if (!ako::tc::mbar_wait(ako::smem_u32(&s_empty[buf]), (uint32_t)(((j >> 1) & 1) ^ 1), s_err, 7)) break;
+        if (!ako::tc::mbar_wait(ako::smem_u32(&s_empty[buf]), (uint32_t)(((j >> 1) & 1) ^ 1), &g_pf_status, 7)) break;
         const uint32_t d = tmem + buf * BK;
         bool ok = true;
         for (int c = 0; c < NCH; ++c, ++g) {
           const int stage = g % NST;
-          if (!ako::tc::mbar_wait(ako::smem_u32(&st_full[stage]), (uint32_t)((g / NST) & 1), s_err, 8)) { ok = false; break; }
+          if (!ako::tc::mbar_wait(ako::smem_u32(&st_full[stage]), (uint32_t)((g / NST) & 1), &g_pf_status, 8)) { ok = false; break; }
           ako::tc::fence_after_thread_sync();
           const uint32_t a_lo = st_lo0 + stage * (ST_BYTES >> 4);
           const uint32_t b_lo = a_lo + (CH_BYTES >> 4);
@@ -404,9 +410,9 @@ mla_prefill_tc_kernel(PfParams p, const __grid_constant__ CUtensorMap tm_qn, con
       constexpr uint32_t IDESC_PV = ako::tc::idesc_bf16_f32(BM, 256);
       const uint32_t v_lo0 = ako::tc::smem_desc_lo(v_base);
       for (int j = 0; j < ntk; ++j) {
-        if (!ako::tc::mbar_wait(ako::smem_u32(&p_full), (uint32_t)(j & 1), s_err, 9)) break;
-        if (!ako::tc::mbar_wait(ako::smem_u32(&v_full), (uint32_t)(j & 1), s_err, 10)) break;
-        if (!ako::tc::mbar_wait(ako::smem_u32(&pv_empty), (uint32_t)((j & 1) ^ 1), s_err, 11)) break;
+        if (!ako::tc::mbar_wait(ako::smem_u32(&p_full), (uint32_t)(j & 1), &g_pf_status, 9)) break;
+        if (!ako::tc::mbar_wait(ako::smem_u32(&v_full), (uint32_t)(j & 1), &g_pf_status, 10)) break;
+        if (!ako::tc::mbar_wait(ako::smem_u32(&pv_empty), (uint32_t)((j & 1) ^ 1), &g_pf_status, 11)) break;
         ako::tc::fence_after_thread_sync();
         const uint32_t d = tmem + 256;
 #pragma unroll
@@ -424,7 +430,10 @@ mla_prefill_tc_kernel(PfParams p, const __grid_constant__ CUtensorMap tm_qn, con
 
   ako::tc::fence_before_thread_sync();
   __syncthreads();
-  if (tid == 0 && *s_err != 0) atomicCAS(&g_pf_status, 0, *s_err);
+  if (tid == 0) {
+    const int code = *reinterpret_cast<volatile int*>(&g_pf_status);
+    if (code != 0) atomicCAS(&g_pf_sticky, 0, code);
+  }
   if (warp == 13) {
     ako::tc::fence_after_thread_sync();
     ako::tc::tmem_dealloc(tmem, 512);
@@ -485,6 +494,6 @@ int ako_mla_prefill_tc_launch(const void* q_nope, const void* q_pe, const void* 
 
 int ako_mla_prefill_tc_status() {
   int v = 0;
-  if (cudaMemcpyFromSymbol(&v, g_pf_status, sizeof(int)) != cudaSuccess) return AKO4X_ELAUNCH;
+  if (cudaMemcpyFromSymbol(&v, g_pf_sticky, sizeof(int)) != cudaSuccess) return AKO4X_ELAUNCH;
   return v;
 }
