@@ -15,7 +15,7 @@ import torch
 
 BASE_SEED = 20260101
 OP_IDS = {"rmsnorm": 0, "gqa_decode": 1, "mla_decode": 2, "mla_prefill": 3, "dsa_indexer": 4,
-          "dsa_attention": 5, "moe": 6}
+          "dsa_attention": 5, "moe": 6, "gdn_decode": 7}
 
 FP8_MAX = 448.0
 
@@ -208,3 +208,24 @@ def make_moe(tokens: int, shape_id: int = 0, device="cpu", num_local_experts=32,
 
 def to_device(args: dict, device) -> dict:
     return {k: (v.to(device) if torch.is_tensor(v) else v) for k, v in args.items()}
+
+
+# ---- Gated Delta Net decode -----------------------------------------------------------------
+
+def make_gdn_decode(batch: int, shape_id: int = 0, device="cpu", with_state=True):
+    """q/k L2-normalised per head (as the model feeds them), decay A in [1, 16], state ~ N(0, 0.25)."""
+    g = _gen("gdn_decode", shape_id, device)
+
+    def unit(shape):
+        x = torch.randn(shape, generator=g, device=device)
+        return (x / x.norm(dim=-1, keepdim=True)).to(torch.bfloat16)
+
+    q, k = unit((batch, 1, 4, 128)), unit((batch, 1, 4, 128))
+    v = _randn_bf16((batch, 1, 8, 128), g, device)
+    state = 0.5 * torch.randn((batch, 8, 128, 128), generator=g, device=device) if with_state else None
+    A_log = torch.log(1.0 + 15.0 * torch.rand(8, generator=g, device=device))
+    a = _randn_bf16((batch, 1, 8), g, device)
+    dt_bias = torch.randn(8, generator=g, device=device)
+    b = _randn_bf16((batch, 1, 8), g, device)
+    return {"q": q, "k": k, "v": v, "state": state, "A_log": A_log, "a": a, "dt_bias": dt_bias, "b": b,
+            "scale": 1.0 / math.sqrt(128.0)}

@@ -241,7 +241,7 @@ def moe_stage_times(a, calls):
 # per-operator table (1 GPU)
 # ---------------------------------------------------------------------------------------------
 def ops_table(peaks, calls=15, only=None):
-    from ako4x_b200 import (dsa_attention, dsa_indexer, gqa_decode, mla_decode, mla_prefill, moe,
+    from ako4x_b200 import (dsa_attention, dsa_indexer, gdn_decode, gqa_decode, mla_decode, mla_prefill, moe,
                             rmsnorm, workloads as W)
     hbm = peaks["hbm_gbs"] * 1e9
     bf16 = peaks["bf16_tflops"] * 1e12
@@ -340,8 +340,17 @@ def ops_table(peaks, calls=15, only=None):
                 bytes_=active * (44040192 + 10752) + T * (7168 + 224 + 1024 + 14336),
                 flops=pairs * FLOP_PER_PAIR, bound="tensor_fp8" if T >= 1024 else "hbm")
 
+    def _gdn():
+        for B in (1, 16, 64):
+            a = W.make_gdn_decode(B, shape_id=B, device="cuda")
+            args = [a[k] for k in ("q", "k", "v", "state", "A_log", "a", "dt_bias", "b")]
+            us = time_calls_cold(lambda: gdn_decode.run(*args, a["scale"]), calls)
+            add("gdn_decode", f"B={B}", us, bytes_=B * (8 * 2 * 65536 + 2 * 1024 + 2 * 2048 + 32) + 64,
+                note="state read + state write")
+            del a
+
     for name, f in (("rmsnorm", _rms), ("gqa_decode", _gqa), ("mla_decode", _mla), ("mla_prefill", _prefill),
-                    ("dsa", _dsa), ("moe_fp8", _moe)):
+                    ("dsa", _dsa), ("moe_fp8", _moe), ("gdn_decode", _gdn)):
         if only is None or name in only:
             guarded(name, f)
     return rows
@@ -728,7 +737,7 @@ def main():
                     help="skip the batch-sharded decode timings attached to the MoE line")
     ap.add_argument("--no-ops-table", action="store_true")
     ap.add_argument("--ops-only", default=None,
-                    help="comma list of rmsnorm,gqa_decode,mla_decode,mla_prefill,dsa,moe_fp8: time only these "
+                    help="comma list of rmsnorm,gqa_decode,mla_decode,mla_prefill,dsa,moe_fp8,gdn_decode: time only these "
                          "operators (cold L2) and print their table; used for per-kernel profiles")
     ap.add_argument("--calls", type=int, default=15, help="timed calls per operator row of the table")
     ap.add_argument("--no-cpu-baseline", action="store_true")

@@ -275,6 +275,20 @@ int ako4x_moe_fp8_block_scale_ep(const float* routing_logits, const void* routin
  * 60 + expert rank: its results never arrived). Synchronises the device. */
 int ako4x_moe_ep_status(const void* my_buffer);
 
+/* ---- Gated Delta Net decode (definition gdn_decode_qk4_v8_d128_k_last) -------------------------
+ * Replaces run(q, k, v, state, A_log, a, dt_bias, b, scale) of
+ * reference/gdn-decode/variants/cuda_bv32_register_resident/kernel.py:456-523.
+ * q, k bf16 [batch, 1, 4, 128]; v bf16 [batch, 1, 8, 128]; state fp32 [batch, 8, 128 (v), 128 (k)] or
+ * NULL (zeros); A_log, dt_bias fp32 [8]; a, b bf16 [batch, 1, 8]; out bf16 [batch, 1, 8, 128];
+ * new_state fp32 like state (may not alias state). v head h reads q/k head h / 2.
+ *   g = exp(-exp(A_log) softplus(a + dt_bias)), beta = sigmoid(b), delta = beta (v - g S k),
+ *   new_state = g S + delta k^T, out = scale q . new_state.
+ * scale is used as given (the Python wrapper maps None / 0 to 1/sqrt(128)). q, k, state and
+ * new_state must be 16-byte aligned. One launch, no workspace. */
+int ako4x_gdn_decode(const void* q, const void* k, const void* v, const float* state,
+                     const float* A_log, const void* a, const float* dt_bias, const void* b,
+                     float scale, void* out, float* new_state, int64_t batch, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

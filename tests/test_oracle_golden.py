@@ -154,3 +154,23 @@ def test_indexer_oracle_against_the_reference_kernel_outputs():
                                                f"reference and is not a bf16 tie of the 2048-th score")
             assert len(diff) <= 2 * 64, f"ctx {case['ctx']} row {r}: {len(diff)} slots differ"
     assert checked_long_rows >= 9
+
+
+@pytest.mark.parametrize("name", ["gdn_decode_b2", "gdn_decode_b1_nostate"])
+def test_gdn_decode(name):
+    """oracle.gdn_decode against the FlashInfer-Bench definition's outputs. fp32 sums in another
+    order: state within 2e-6 relative to the row scale, bf16 output within one rounding step."""
+    from ako4x_b200 import workloads as W
+    g = load_golden(name)
+    i = g["inputs"]
+    a = W.make_gdn_decode(i["batch"], shape_id=i["shape_id"], with_state=i["with_state"])
+    for key in ("q", "k", "v", "A_log", "a", "dt_bias", "b"):
+        assert torch.equal(a[key], i[key]), key
+    if i["with_state"]:
+        assert a["state"].double().sum().item() == i["state_digest"]
+    o, s = oracle.gdn_decode(a["q"], a["k"], a["v"], a["state"], a["A_log"], a["a"], a["dt_bias"], a["b"], a["scale"])
+    ref_o, ref_s = g["outputs"]["output"], g["outputs"]["new_state"]
+    assert o.shape == ref_o.shape and o.dtype == torch.bfloat16 and s.shape == ref_s.shape
+    assert (s - ref_s).abs().max().item() <= 2e-6 * ref_s.abs().max().item() + 1e-7
+    assert_close_bf16(o, ref_o, atol=1e-4, rtol=1e-2)
+    assert (o == ref_o).float().mean().item() > 0.97
