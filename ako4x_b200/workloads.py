@@ -15,7 +15,7 @@ import torch
 
 BASE_SEED = 20260101
 OP_IDS = {"rmsnorm": 0, "gqa_decode": 1, "mla_decode": 2, "mla_prefill": 3, "dsa_indexer": 4,
-          "dsa_attention": 5, "moe": 6, "gdn_decode": 7}
+          "dsa_attention": 5, "moe": 6, "gdn_decode": 7, "gemm": 8}
 
 FP8_MAX = 448.0
 
@@ -229,3 +229,13 @@ def make_gdn_decode(batch: int, shape_id: int = 0, device="cpu", with_state=True
     b = _randn_bf16((batch, 1, 8), g, device)
     return {"q": q, "k": k, "v": v, "state": state, "A_log": A_log, "a": a, "dt_bias": dt_bias, "b": b,
             "scale": 1.0 / math.sqrt(128.0)}
+
+
+# ---- dense GEMM -----------------------------------------------------------------------------
+
+def make_gemm(m: int, shape_id: int = 0, device="cpu", n=2048, k=4096, dtype=torch.float16):
+    """A [m, k], B [n, k] ~ N(0, 1): C = A @ B.T has entries of size sqrt(k)."""
+    g = _gen("gemm", shape_id, device)
+    a = torch.randn((m, k), generator=g, device=device, dtype=torch.float32).to(dtype)
+    b = torch.randn((n, k), generator=g, device=device, dtype=torch.float32).to(dtype)
+    return {"A": a, "B": b}

@@ -241,7 +241,7 @@ def moe_stage_times(a, calls):
 # per-operator table (1 GPU)
 # ---------------------------------------------------------------------------------------------
 def ops_table(peaks, calls=15, only=None):
-    from ako4x_b200 import (dsa_attention, dsa_indexer, gdn_decode, gqa_decode, mla_decode, mla_prefill, moe,
+    from ako4x_b200 import (dsa_attention, dsa_indexer, gdn_decode, gemm, gqa_decode, mla_decode, mla_prefill, moe,
                             rmsnorm, workloads as W)
     hbm = peaks["hbm_gbs"] * 1e9
     bf16 = peaks["bf16_tflops"] * 1e12
@@ -349,8 +349,16 @@ def ops_table(peaks, calls=15, only=None):
                 note="state read + state write")
             del a
 
+    def _gemm():
+        for M in (16, 256, 969, 4096, 16294):
+            a = W.make_gemm(M, shape_id=M % 89, device="cuda")
+            us = time_calls_cold(lambda: gemm.run(a["A"], a["B"]), calls)
+            add("gemm_f16", f"M={M},N=2048,K=4096", us, bytes_=2 * (M * 4096 + 2048 * 4096 + M * 2048),
+                flops=2 * M * 2048 * 4096, bound="tensor_bf16" if M >= 969 else "hbm")
+            del a
+
     for name, f in (("rmsnorm", _rms), ("gqa_decode", _gqa), ("mla_decode", _mla), ("mla_prefill", _prefill),
-                    ("dsa", _dsa), ("moe_fp8", _moe), ("gdn_decode", _gdn)):
+                    ("dsa", _dsa), ("moe_fp8", _moe), ("gdn_decode", _gdn), ("gemm", _gemm)):
         if only is None or name in only:
             guarded(name, f)
     return rows
@@ -737,7 +745,7 @@ def main():
                     help="skip the batch-sharded decode timings attached to the MoE line")
     ap.add_argument("--no-ops-table", action="store_true")
     ap.add_argument("--ops-only", default=None,
-                    help="comma list of rmsnorm,gqa_decode,mla_decode,mla_prefill,dsa,moe_fp8,gdn_decode: time only these "
+                    help="comma list of rmsnorm,gqa_decode,mla_decode,mla_prefill,dsa,moe_fp8,gdn_decode,gemm: time only these "
                          "operators (cold L2) and print their table; used for per-kernel profiles")
     ap.add_argument("--calls", type=int, default=15, help="timed calls per operator row of the table")
     ap.add_argument("--no-cpu-baseline", action="store_true")

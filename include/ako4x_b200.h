@@ -289,6 +289,17 @@ int ako4x_gdn_decode(const void* q, const void* k, const void* v, const float* s
                      const float* A_log, const void* a, const float* dt_bias, const void* b,
                      float scale, void* out, float* new_state, int64_t batch, void* stream);
 
+/* ---- Dense GEMM (definition gemm_n2048_k4096) --------------------------------------------------
+ * C[m, n] = A[m, k] * B[n, k]^T with fp32 accumulation; A, B, C fp16 (is_bf16 = 0) or bf16 (1),
+ * row-major and contiguous, 16-byte aligned. Replaces the reference family's best implementation,
+ * torch.matmul(A, B.T) (reference/gemm-n2048-k4096/README.md: N = 2048, K = 4096, M = 1 ... 16 294).
+ * n must be a multiple of 256 and k of 64 (AKO4X_EUNSUPPORTED_SHAPE otherwise); any m >= 0. One
+ * launch, no workspace. */
+int ako4x_gemm_f16_nt(const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k,
+                      int is_bf16, void* stream);
+/* 0, or the code of a bounded wait of the GEMM kernels that gave up (71-74). Synchronises. */
+int ako4x_gemm_device_status(void);
+
 #ifdef __cplusplus
 }
 #endif

@@ -174,3 +174,19 @@ def test_gdn_decode(name):
     assert (s - ref_s).abs().max().item() <= 2e-6 * ref_s.abs().max().item() + 1e-7
     assert_close_bf16(o, ref_o, atol=1e-4, rtol=1e-2)
     assert (o == ref_o).float().mean().item() > 0.97
+
+
+@pytest.mark.parametrize("m", [1, 37, 200])
+def test_gemm(m):
+    """oracle.gemm_nt against torch.matmul(A, B.T) on fp16 tensors (the reference expression of the
+    family): fp32 sums in another order, so a value may round to the neighbouring fp16."""
+    from ako4x_b200 import workloads as W
+    g = load_golden(f"gemm_m{m}")
+    a = W.make_gemm(m, shape_id=g["inputs"]["shape_id"])
+    assert (a["A"].double().sum() + a["B"].double().sum()).item() == g["inputs"]["digest"]
+    c = oracle.gemm_nt(a["A"], a["B"])
+    ref = g["outputs"]["C"]
+    assert c.shape == ref.shape and c.dtype == torch.float16
+    err = (c.float() - ref.float()).abs()
+    assert (err <= 2e-3 * ref.float().abs() + 1e-2).all()
+    assert (c == ref).float().mean().item() > 0.97
