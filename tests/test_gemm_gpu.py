@@ -48,7 +48,8 @@ def test_bf16_and_other_shapes():
 
 def test_largest_benchmark_size_sampled_rows():
     """M = 16 294 (the largest recorded workload): 96 sampled rows against the oracle, and linearity
-    (A and 2A give C and 2C exactly: scaling by two is exact in fp16 away from overflow)."""
+    (A and 2A give C and 2C exactly: scaling by two is exact in fp32 and in fp16 away from overflow
+    and from the subnormal range, which a few results near zero fall into)."""
     a = W.make_gemm(16294, shape_id=0, device="cuda")
     a["A"].mul_(0.25)
     c = gemm.run(a["A"], a["B"])
@@ -56,7 +57,8 @@ def test_largest_benchmark_size_sampled_rows():
     ref = oracle.gemm_nt(a["A"][rows.cuda()].cpu(), a["B"].cpu())
     _check(c[rows.cuda()].cpu(), ref, 2e-3)
     c2 = gemm.run(a["A"] * 2, a["B"])
-    assert torch.equal(c2, c * 2)
+    normal = c.abs() > 1e-3
+    assert torch.equal(c2[normal], (c * 2)[normal]) and normal.float().mean().item() > 0.999
     assert _cabi.lib().ako4x_gemm_device_status() == 0
 
 
