@@ -7,5 +7,5 @@ from . import _cabi  # noqa: F401
 
 __all__ = [
     "rmsnorm", "gqa_decode", "mla_decode", "mla_prefill", "dsa_indexer", "dsa_attention", "moe",
-    "gdn_decode", "gemm",
+    "gdn_decode", "gdn_prefill", "gemm",
 ]

@@ -15,7 +15,7 @@ import torch
 
 BASE_SEED = 20260101
 OP_IDS = {"rmsnorm": 0, "gqa_decode": 1, "mla_decode": 2, "mla_prefill": 3, "dsa_indexer": 4,
-          "dsa_attention": 5, "moe": 6, "gdn_decode": 7, "gemm": 8}
+          "dsa_attention": 5, "moe": 6, "gdn_decode": 7, "gemm": 8, "gdn_prefill": 9}
 
 FP8_MAX = 448.0
 
@@ -239,3 +239,28 @@ def make_gemm(m: int, shape_id: int = 0, device="cpu", n=2048, k=4096, dtype=tor
     a = torch.randn((m, k), generator=g, device=device, dtype=torch.float32).to(dtype)
     b = torch.randn((n, k), generator=g, device=device, dtype=torch.float32).to(dtype)
     return {"A": a, "B": b}
+
+
+# ---- Gated Delta Net prefill ------------------------------------------------------------------
+
+def make_gdn_prefill(seq_lens, shape_id: int = 0, device="cpu", with_state=True):
+    """Packed sequences of the given lengths; value distributions as make_gdn_decode."""
+    g = _gen("gdn_prefill", shape_id, device)
+    lens = torch.as_tensor(seq_lens, dtype=torch.int64)
+    T, n = int(lens.sum()), lens.numel()
+
+    def unit(shape):
+        x = torch.randn(shape, generator=g, device=device)
+        return (x / x.norm(dim=-1, keepdim=True)).to(torch.bfloat16)
+
+    q, k = unit((T, 4, 128)), unit((T, 4, 128))
+    v = _randn_bf16((T, 8, 128), g, device)
+    state = 0.5 * torch.randn((n, 8, 128, 128), generator=g, device=device) if with_state else None
+    A_log = torch.log(1.0 + 15.0 * torch.rand(8, generator=g, device=device))
+    a = _randn_bf16((T, 8), g, device)
+    dt_bias = torch.randn(8, generator=g, device=device)
+    b = _randn_bf16((T, 8), g, device)
+    cu = torch.zeros(n + 1, dtype=torch.int64, device=device)
+    cu[1:] = torch.cumsum(lens, 0).to(device)
+    return {"q": q, "k": k, "v": v, "state": state, "A_log": A_log, "a": a, "dt_bias": dt_bias, "b": b,
+            "cu_seqlens": cu, "scale": 1.0 / math.sqrt(128.0)}

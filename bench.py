@@ -241,7 +241,7 @@ def moe_stage_times(a, calls):
 # per-operator table (1 GPU)
 # ---------------------------------------------------------------------------------------------
 def ops_table(peaks, calls=15, only=None):
-    from ako4x_b200 import (dsa_attention, dsa_indexer, gdn_decode, gemm, gqa_decode, mla_decode, mla_prefill, moe,
+    from ako4x_b200 import (dsa_attention, dsa_indexer, gdn_decode, gdn_prefill, gemm, gqa_decode, mla_decode, mla_prefill, moe,
                             rmsnorm, workloads as W)
     hbm = peaks["hbm_gbs"] * 1e9
     bf16 = peaks["bf16_tflops"] * 1e12
@@ -349,6 +349,17 @@ def ops_table(peaks, calls=15, only=None):
                 note="state read + state write")
             del a
 
+    def _gdnp():
+        for lens in ([8192], [1024] * 8, [128] * 64):
+            a = W.make_gdn_prefill(lens, shape_id=len(lens), device="cuda")
+            args = [a[k] for k in ("q", "k", "v", "state", "A_log", "a", "dt_bias", "b", "cu_seqlens")]
+            us = time_calls_cold(lambda: gdn_prefill.run(*args, a["scale"]), max(5, calls // 3))
+            T, n = sum(lens), len(lens)
+            add("gdn_prefill", f"seqs={n}x{lens[0]}", us, bytes_=T * (2 * 1024 + 2 * 2048 + 32) + n * 8 * 2 * 65536,
+                flops=T * 8 * 128 * 128 * 6, bound="latency",
+                note="token-sequential recurrence, rows in parallel; not the chunked form")
+            del a
+
     def _gemm():
         for M in (16, 256, 969, 4096, 16294):
             a = W.make_gemm(M, shape_id=M % 89, device="cuda")
@@ -358,7 +369,8 @@ def ops_table(peaks, calls=15, only=None):
             del a
 
     for name, f in (("rmsnorm", _rms), ("gqa_decode", _gqa), ("mla_decode", _mla), ("mla_prefill", _prefill),
-                    ("dsa", _dsa), ("moe_fp8", _moe), ("gdn_decode", _gdn), ("gemm", _gemm)):
+                    ("dsa", _dsa), ("moe_fp8", _moe), ("gdn_decode", _gdn), ("gdn_prefill", _gdnp),
+                    ("gemm", _gemm)):
         if only is None or name in only:
             guarded(name, f)
     return rows
@@ -745,7 +757,7 @@ def main():
                     help="skip the batch-sharded decode timings attached to the MoE line")
     ap.add_argument("--no-ops-table", action="store_true")
     ap.add_argument("--ops-only", default=None,
-                    help="comma list of rmsnorm,gqa_decode,mla_decode,mla_prefill,dsa,moe_fp8,gdn_decode,gemm: time only these "
+                    help="comma list of rmsnorm,gqa_decode,mla_decode,mla_prefill,dsa,moe_fp8,gdn_decode,gdn_prefill,gemm: time only these "
                          "operators (cold L2) and print their table; used for per-kernel profiles")
     ap.add_argument("--calls", type=int, default=15, help="timed calls per operator row of the table")
     ap.add_argument("--no-cpu-baseline", action="store_true")

@@ -300,6 +300,20 @@ int ako4x_gemm_f16_nt(const void* a, const void* b, void* c, int64_t m, int64_t 
 /* 0, or the code of a bounded wait of the GEMM kernels that gave up (71-74). Synchronises. */
 int ako4x_gemm_device_status(void);
 
+/* ---- Gated Delta Net prefill (definition gdn_prefill_qk4_v8_d128_k_last) ------------------------
+ * Replaces run(q, k, v, state, A_log, a, dt_bias, b, cu_seqlens, scale) of
+ * reference/gdn-prefill/variants/cuda_graph_v5/kernel.py:1333. q, k bf16 [tokens, 4, 128]; v bf16
+ * [tokens, 8, 128]; state fp32 [num_seqs, 8, 128 (v), 128 (k)] or NULL (zeros); A_log, dt_bias fp32
+ * [8]; a, b bf16 [tokens, 8]; cu_seqlens int64 [num_seqs + 1] (device memory, ascending; sequence s
+ * owns tokens cu_seqlens[s] .. cu_seqlens[s+1]); out bf16 [tokens, 8, 128]; new_state like state.
+ * The decode recurrence (ako4x_gdn_decode) applied to every token of a sequence in order, the
+ * output taken after each update. An empty sequence gets a zero new_state (as the definition
+ * does); tokens that belong to no sequence are not written. One launch, no workspace. */
+int ako4x_gdn_prefill(const void* q, const void* k, const void* v, const float* state,
+                      const float* A_log, const void* a, const float* dt_bias, const void* b,
+                      const int64_t* cu_seqlens, float scale, void* out, float* new_state,
+                      int64_t total_tokens, int64_t num_seqs, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

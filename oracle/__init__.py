@@ -10,5 +10,5 @@ from .attention import (  # noqa: F401
 from .indexer import dsa_index_scores, dsa_topk_select, dsa_topk_indexer, unpack_index_cache  # noqa: F401
 from .moe import ds_routing, moe_fp8_block_scale  # noqa: F401
 from .quantize import fp8_quantize_1x128, index_k_cache_write  # noqa: F401
-from .gdn import gdn_decode  # noqa: F401
+from .gdn import gdn_decode, gdn_prefill  # noqa: F401
 from .gemm import gemm_nt  # noqa: F401

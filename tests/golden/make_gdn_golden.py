@@ -33,6 +33,15 @@ def main():
         torch.save({"inputs": inputs, "outputs": {"output": o, "new_state": s}}, OUT / f"{name}.pt")
         print(name, (OUT / f"{name}.pt").stat().st_size // 1024, "KiB")
 
+    # prefill: three packed sequences, one of them empty; only outputs and new states are stored
+    lens = [5, 0, 21]
+    a = W.make_gdn_prefill(lens, shape_id=900)
+    o, s = G._gdn_prefill_reference(a["q"], a["k"], a["v"], a["state"], a["A_log"], a["a"], a["dt_bias"], a["b"],
+                                    a["cu_seqlens"], a["scale"])
+    torch.save({"inputs": {"seq_lens": lens, "shape_id": 900, "state_digest": a["state"].double().sum().item()},
+                "outputs": {"output": o, "new_state": s}}, OUT / "gdn_prefill_s3.pt")
+    print("gdn_prefill_s3", (OUT / "gdn_prefill_s3.pt").stat().st_size // 1024, "KiB")
+
 
 if __name__ == "__main__":
     main()

@@ -190,3 +190,19 @@ def test_gemm(m):
     err = (c.float() - ref.float()).abs()
     assert (err <= 2e-3 * ref.float().abs() + 1e-2).all()
     assert (c == ref).float().mean().item() > 0.97
+
+
+def test_gdn_prefill():
+    """oracle.gdn_prefill against the FlashInfer-Bench definition (three packed sequences, one
+    empty)."""
+    from ako4x_b200 import workloads as W
+    g = load_golden("gdn_prefill_s3")
+    a = W.make_gdn_prefill(g["inputs"]["seq_lens"], shape_id=g["inputs"]["shape_id"])
+    assert a["state"].double().sum().item() == g["inputs"]["state_digest"]
+    o, s = oracle.gdn_prefill(a["q"], a["k"], a["v"], a["state"], a["A_log"], a["a"], a["dt_bias"], a["b"],
+                              a["cu_seqlens"], a["scale"])
+    ref_o, ref_s = g["outputs"]["output"], g["outputs"]["new_state"]
+    assert (s - ref_s).abs().max().item() <= 1e-5 * ref_s.abs().max().item()
+    assert torch.all(ref_s[1] == 0) and torch.all(s[1] == 0)
+    assert_close_bf16(o, ref_o, atol=1e-3, rtol=1e-2)
+    assert (o == ref_o).float().mean().item() > 0.95

@@ -27,6 +27,7 @@ PARAMS = {
         "gemm1_weights_scale", "gemm2_weights", "gemm2_weights_scale", "local_expert_offset",
         "routed_scaling_factor"],
     "gemm_n2048_k4096": ["A", "B"],
+    "gdn_prefill_qk4_v8_d128_k_last": ["q", "k", "v", "state", "A_log", "a", "dt_bias", "b", "cu_seqlens", "scale"],
     "gdn_decode_qk4_v8_d128_k_last": ["q", "k", "v", "state", "A_log", "a", "dt_bias", "b", "scale"],
 }
 

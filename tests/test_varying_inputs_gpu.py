@@ -74,6 +74,8 @@ def _cases():
            [a[k] for k in ("routing_logits", "routing_bias", "hidden_states", "hidden_states_scale", "gemm1_weights",
                            "gemm1_weights_scale", "gemm2_weights", "gemm2_weights_scale", "local_expert_offset",
                            "routed_scaling_factor")])
+    a = W.make_gdn_prefill([50, 3, 120], shape_id=80, device="cuda")
+    yield "gdn_prefill_qk4_v8_d128_k_last", [a[k] for k in ("q", "k", "v", "state", "A_log", "a", "dt_bias", "b", "cu_seqlens", "scale")]
     a = W.make_gemm(333, shape_id=79, device="cuda")
     yield "gemm_n2048_k4096", [a["A"], a["B"]]
     a = W.make_gdn_decode(6, shape_id=78, device="cuda")
