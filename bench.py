@@ -175,6 +175,35 @@ def time_calls_cold(fn, calls=20, warmup=3):
     return statistics.median(us), statistics.fmean(us)
 
 
+def time_call_e2e(fn, step_inputs, calls=10, warmup=2):
+    """The same call timed end to end through the plug-in: the per-step inputs (device tensors in
+    `step_inputs`, which `fn` reads) are refilled from pinned host copies inside the timed region
+    and every output is copied back to pinned host memory. Caches, weights and recurrent states
+    stay resident, as they do in a serving engine. Returns (median us, h2d bytes, d2h bytes)."""
+    hosts = [pinned(t) for t in step_inputs]
+    out = fn()
+    outs = list(out) if isinstance(out, (tuple, list)) else [out]
+    host_outs = [torch.empty(o.shape, dtype=o.dtype, device="cpu", pin_memory=True) for o in outs]
+    us = []
+    for i in range(warmup + calls):
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for d, h in zip(step_inputs, hosts):
+            d.copy_(h, non_blocking=True)
+        out = fn()
+        outs = list(out) if isinstance(out, (tuple, list)) else [out]
+        for o, h in zip(outs, host_outs):
+            h.copy_(o, non_blocking=True)
+        e1.record()
+        torch.cuda.synchronize()
+        if i >= warmup:
+            us.append(e0.elapsed_time(e1) * 1e3)
+    h2d = sum(t.numel() * t.element_size() for t in step_inputs)
+    d2h = sum(t.numel() * t.element_size() for t in host_outs)
+    return statistics.median(us), h2d, d2h
+
+
 def pinned(t: torch.Tensor) -> torch.Tensor:
     h = torch.empty(t.shape, dtype=t.dtype, device="cpu", pin_memory=True)
     h.copy_(t)
@@ -248,8 +277,11 @@ def ops_table(peaks, calls=15, only=None):
     fp8 = 2 * bf16
     rows = []
 
-    def add(name, cfg, us, bytes_=None, flops=None, bound="hbm", note=None):
+    def add(name, cfg, us, bytes_=None, flops=None, bound="hbm", note=None, e2e=None):
         r = {"op": name, "config": cfg, "us_per_call": round(us[0], 2), "us_mean": round(us[1], 2)}
+        if e2e is not None:   # host inputs in, outputs back to the host, inside the timed region
+            r["e2e_us"] = round(e2e[0], 2)
+            r["e2e_h2d_bytes"], r["e2e_d2h_bytes"] = e2e[1], e2e[2]
         if bytes_ is not None:
             r["hbm_gbs"] = round(bytes_ / (us[0] * 1e-6) / 1e9, 1)
             r["hbm_frac"] = round(bytes_ / (us[0] * 1e-6) / hbm, 4)
@@ -272,26 +304,30 @@ def ops_table(peaks, calls=15, only=None):
     def _rms():
         for T in (4096, 520128):
             a = W.make_rmsnorm(T, device="cuda")
-            us = time_calls_cold(lambda: rmsnorm.run(a["hidden_states"], a["weight"]), calls)
-            add("rmsnorm", f"T={T}", us, bytes_=512 * T + 256)
+            f = lambda: rmsnorm.run(a["hidden_states"], a["weight"])
+            us = time_calls_cold(f, calls)
+            add("rmsnorm", f"T={T}", us, bytes_=512 * T + 256, e2e=time_call_e2e(f, [a["hidden_states"]]))
 
     def _gqa():
         for B in (1, 16, 64, 256):
             a = W.make_gqa_decode(B, shape_id=B, device="cuda")
             n = a["kv_indices"].numel()
-            us = time_calls_cold(lambda: gqa_decode.run(a["q"], a["k_cache"], a["v_cache"], a["kv_indptr"],
-                                                        a["kv_indices"], a["sm_scale"]), calls)
-            add("gqa_decode", f"B={B},sum_len={n}", us, bytes_=4100 * n + 16516 * B, flops=4 * 32 * 128 * n)
+            f = lambda: gqa_decode.run(a["q"], a["k_cache"], a["v_cache"], a["kv_indptr"], a["kv_indices"],
+                                       a["sm_scale"])
+            us = time_calls_cold(f, calls)
+            add("gqa_decode", f"B={B},sum_len={n}", us, bytes_=4100 * n + 16516 * B, flops=4 * 32 * 128 * n,
+                e2e=time_call_e2e(f, [a["q"], a["kv_indptr"], a["kv_indices"]]))
             del a
 
     def _mla():
         for B in (1, 32, 128):
             a = W.make_mla_decode(B, shape_id=B, device="cuda")
             n = a["kv_indices"].numel()
-            us = time_calls_cold(lambda: mla_decode.run(a["q_nope"], a["q_pe"], a["ckv_cache"], a["kpe_cache"],
-                                                        a["kv_indptr"], a["kv_indices"], a["sm_scale"]), calls)
+            f = lambda: mla_decode.run(a["q_nope"], a["q_pe"], a["ckv_cache"], a["kpe_cache"], a["kv_indptr"],
+                                       a["kv_indices"], a["sm_scale"])
+            us = time_calls_cold(f, calls)
             add("mla_decode", f"B={B},sum_ctx={n}", us, bytes_=1156 * n + B * (16 * 576 * 2 + 16 * 512 * 2 + 64),
-                flops=34816 * n)
+                flops=34816 * n, e2e=time_call_e2e(f, [a["q_nope"], a["q_pe"], a["kv_indptr"], a["kv_indices"]]))
             del a
 
     def _prefill():
@@ -299,12 +335,13 @@ def ops_table(peaks, calls=15, only=None):
         qo, kv = a["qo_indptr"].cpu().long(), a["kv_indptr"].cpu().long()
         ql, kl = qo[1:] - qo[:-1], kv[1:] - kv[:-1]
         pairs = int((ql * (kl - ql) + ql * (ql + 1) // 2).sum())
-        us = time_calls_cold(lambda: mla_prefill.run(a["q_nope"], a["q_pe"], a["ckv_cache"], a["kpe_cache"],
-                                                     a["qo_indptr"], a["kv_indptr"], a["kv_indices"],
-                                                     a["sm_scale"]), max(5, calls // 3))
+        f = lambda: mla_prefill.run(a["q_nope"], a["q_pe"], a["ckv_cache"], a["kpe_cache"], a["qo_indptr"],
+                                    a["kv_indptr"], a["kv_indices"], a["sm_scale"])
+        us = time_calls_cold(f, max(5, calls // 3))
         tq, tkv = int(ql.sum()), int(kl.sum())
         add("mla_prefill", f"batch=8,total_q={tq},total_kv={tkv}", us,
-            bytes_=tq * 16 * (576 + 512) * 2 + tkv * 1156, flops=34816 * pairs, bound="tensor_bf16")
+            bytes_=tq * 16 * (576 + 512) * 2 + tkv * 1156, flops=34816 * pairs, bound="tensor_bf16",
+            e2e=time_call_e2e(f, [a["q_nope"], a["q_pe"], a["qo_indptr"], a["kv_indptr"], a["kv_indices"]], calls=5))
 
     def _dsa():
         for T, ctx in ((1, 32768), (64, 32768), (512, 32768)):
@@ -315,16 +352,20 @@ def ops_table(peaks, calls=15, only=None):
             sl = int(a["seq_lens"].long().sum())
             add("dsa_indexer", f"T={T},ctx={ctx}", us,
                 bytes_=pages * 8448 + T * (64 * 128 + 64 * 4 + 4 * pages + 2048 * 4),
-                flops=2 * 64 * 128 * sl, bound="tensor_fp8")
+                flops=2 * 64 * 128 * sl, bound="tensor_fp8",
+                e2e=time_call_e2e(lambda: dsa_indexer.run(*args),
+                                  [a["q_index_fp8"], a["weights"], a["seq_lens"], a["block_table"]]))
             (idx,) = dsa_indexer.run(*args)
             npages = a["k_index_cache_fp8"].shape[0]
             b = W.make_dsa_attention(T, ctx, idx, npages, shape_id=T, device="cuda")
-            us = time_calls_cold(lambda: dsa_attention.run(b["q_nope"], b["q_pe"], b["ckv_cache"], b["kpe_cache"],
-                                                           b["sparse_indices"], b["sm_scale"]), calls)
+            f = lambda: dsa_attention.run(b["q_nope"], b["q_pe"], b["ckv_cache"], b["kpe_cache"],
+                                          b["sparse_indices"], b["sm_scale"])
+            us = time_calls_cold(f, calls)
             nvalid = int((idx >= 0).sum())
             add("dsa_attention", f"T={T},ctx={ctx}", us,
                 bytes_=nvalid * 1152 + T * (2048 * 4 + 16 * 1088 * 2 + 64), flops=34816 * nvalid,
-                note="gather bytes; served from L2 when rows repeat across tokens")
+                note="gather bytes; served from L2 when rows repeat across tokens",
+                e2e=time_call_e2e(f, [b["q_nope"], b["q_pe"], b["sparse_indices"]]))
             del a, b
 
     def _moe():
@@ -335,18 +376,23 @@ def ops_table(peaks, calls=15, only=None):
                 a[k] = base[k]
             pairs, ids = moe_local_pairs(a)
             active = int(torch.unique(ids[(ids >= 0) & (ids < 32)]).numel())
-            us = time_calls_cold(lambda: moe.run(*[a[k] for k in MOE_KEYS]), max(5, calls // 2))
+            f = lambda: moe.run(*[a[k] for k in MOE_KEYS])
+            us = time_calls_cold(f, max(5, calls // 2))
             add("moe_fp8", f"T={T},local_pairs={pairs},active_experts={active}", us,
                 bytes_=active * (44040192 + 10752) + T * (7168 + 224 + 1024 + 14336),
-                flops=pairs * FLOP_PER_PAIR, bound="tensor_fp8" if T >= 1024 else "hbm")
+                flops=pairs * FLOP_PER_PAIR, bound="tensor_fp8" if T >= 1024 else "hbm",
+                e2e=time_call_e2e(f, [a["routing_logits"], a["hidden_states"], a["hidden_states_scale"]], calls=5))
 
     def _gdn():
         for B in (1, 16, 64):
             a = W.make_gdn_decode(B, shape_id=B, device="cuda")
             args = [a[k] for k in ("q", "k", "v", "state", "A_log", "a", "dt_bias", "b")]
             us = time_calls_cold(lambda: gdn_decode.run(*args, a["scale"]), calls)
+            # end to end the new state stays on the device (it is the next step's input): only the
+            # token's output goes back
             add("gdn_decode", f"B={B}", us, bytes_=B * (8 * 2 * 65536 + 2 * 1024 + 2 * 2048 + 32) + 64,
-                note="state read + state write")
+                note="state read + state write",
+                e2e=time_call_e2e(lambda: gdn_decode.run(*args, a["scale"])[0], [a["q"], a["k"], a["v"], a["a"], a["b"]]))
             del a
 
     def _gdnp():
@@ -354,10 +400,12 @@ def ops_table(peaks, calls=15, only=None):
             a = W.make_gdn_prefill(lens, shape_id=len(lens), device="cuda")
             args = [a[k] for k in ("q", "k", "v", "state", "A_log", "a", "dt_bias", "b", "cu_seqlens")]
             us = time_calls_cold(lambda: gdn_prefill.run(*args, a["scale"]), max(5, calls // 3))
+            e2e = time_call_e2e(lambda: gdn_prefill.run(*args, a["scale"])[0],
+                                [a["q"], a["k"], a["v"], a["a"], a["b"], a["cu_seqlens"]], calls=5)
             T, n = sum(lens), len(lens)
             add("gdn_prefill", f"seqs={n}x{lens[0]}", us, bytes_=T * (2 * 1024 + 2 * 2048 + 32) + n * 8 * 2 * 65536,
                 flops=T * 8 * 128 * 128 * 6, bound="latency",
-                note="token-sequential recurrence, rows in parallel; not the chunked form")
+                note="token-sequential recurrence, rows in parallel; not the chunked form", e2e=e2e)
             del a
 
     def _gemm():
@@ -365,7 +413,8 @@ def ops_table(peaks, calls=15, only=None):
             a = W.make_gemm(M, shape_id=M % 89, device="cuda")
             us = time_calls_cold(lambda: gemm.run(a["A"], a["B"]), calls)
             add("gemm_f16", f"M={M},N=2048,K=4096", us, bytes_=2 * (M * 4096 + 2048 * 4096 + M * 2048),
-                flops=2 * M * 2048 * 4096, bound="tensor_bf16" if M >= 969 else "hbm")
+                flops=2 * M * 2048 * 4096, bound="tensor_bf16" if M >= 969 else "hbm",
+                e2e=time_call_e2e(lambda: gemm.run(a["A"], a["B"]), [a["A"]]))
             del a
 
     for name, f in (("rmsnorm", _rms), ("gqa_decode", _gqa), ("mla_decode", _mla), ("mla_prefill", _prefill),
