@@ -10,10 +10,10 @@
 //     the whole K dimension per tile, so no partial sums leave TMEM;
 //   * four epilogue warps drain the other accumulator (tcgen05.ld, cast, 64-byte stores per row)
 //     while the next tile's MMAs run.
-// Small M (up to a few hundred rows) is not where this kernel is good: a tile's K loop is 256
-// MMAs whatever its width, an M128 x N32 x K16 MMA takes about 80 cycles, so a CTA needs 11 us for
-// its one tile (measured 22-24 us per call; keeping 64 KB instead of 32 KB of B in flight per CTA
-// changed nothing). Splitting K over CTAs with a reduction is the way down and is not built.
+// Small M: a tile's K loop is 256 MMAs whatever its width and an M128 x N32 x K16 MMA takes about
+// 80 cycles, so one CTA per tile needs 11 us (22-24 us per call, and keeping 64 KB instead of 32 KB
+// of B in flight per CTA changed nothing). With a workspace the K dimension is split over up to 8
+// CTAs per tile and a second kernel sums the fp32 partial products (gemm_plan below).
 // Every wait is bounded; a wait that gives up records its code in the status word below and the
 // CTA unwinds through the common exit that frees TMEM.
 #include "common.cuh"
@@ -44,9 +44,10 @@ __host__ __device__ constexpr uint32_t idesc_f16(int m, int n, bool bf16) {
 
 struct GemmArgs {
   void* c;
+  float* partial;   // split-K: fp32 partial products [split][m][n]; unused when splits == 1
   int m, n, k;
   int a_box_rows;   // rows of A one TMA box brings (128, or fewer when M is small)
-  int bf16;
+  int splits;       // CTAs that share one output tile, each over k / splits of the reduction
 };
 
 template <int BN, bool BF16>
@@ -83,9 +84,10 @@ gemm_f16_tc_kernel(GemmArgs p, const __grid_constant__ CUtensorMap tm_a, const _
   ako::tc::fence_after_thread_sync();
   const uint32_t tmem_base = s_tmem_base;
 
+  // work item = (output tile, K split), the split fastest
   const int m_tiles = (p.m + G_BM - 1) / G_BM, n_tiles = p.n / BN;
-  const int total_tiles = m_tiles * n_tiles;
-  const int nkb = p.k / 64;
+  const int total_tiles = m_tiles * n_tiles * p.splits;
+  const int nkb = p.k / 64 / p.splits;
   // bytes one stage receives: A brings a_box_rows rows, B all BN
   const uint32_t stage_tx = (uint32_t)p.a_box_rows * G_BK_BYTES + (uint32_t)Cfg::B_BYTES;
 
@@ -97,8 +99,10 @@ gemm_f16_tc_kernel(GemmArgs p, const __grid_constant__ CUtensorMap tm_a, const _
       int g = 0;
       bool ok = true;
       for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-        const int mt = tile / n_tiles, nt = tile % n_tiles;
-        for (int kb = 0; kb < nkb; ++kb, ++g) {
+        const int ks = tile % p.splits, ot = tile / p.splits;
+        const int mt = ot / n_tiles, nt = ot % n_tiles;
+        for (int kb0 = 0; kb0 < nkb; ++kb0, ++g) {
+          const int kb = ks * nkb + kb0;
           const int stage = g % STAGES;
           const uint32_t ph = (uint32_t)((g / STAGES) & 1);
           if (!ako::tc::mbar_wait(ako::smem_u32(&s_empty[stage]), ph ^ 1u, &s_err, kErrGLoad)) { ok = false; break; }
@@ -141,19 +145,25 @@ gemm_f16_tc_kernel(GemmArgs p, const __grid_constant__ CUtensorMap tm_a, const _
     const int row_in_tile = 32 * warp + lane;   // TMEM lane = accumulator row
     int lt = 0;
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++lt) {
-      const int mt = tile / n_tiles, nt = tile % n_tiles;
+      const int ks = tile % p.splits, ot = tile / p.splits;
+      const int mt = ot / n_tiles, nt = ot % n_tiles;
       const int buf = lt & 1;
       if (!ako::tc::mbar_wait_warp(ako::smem_u32(&s_acc_full[buf]), (uint32_t)((lt >> 1) & 1), &s_err, kErrGEpi)) break;
       ako::tc::fence_after_thread_sync();
       const int row = mt * G_BM + row_in_tile;
       const uint32_t taddr = tmem_base + ((uint32_t)(32 * warp) << 16) + buf * BN;
       uint16_t* crow = reinterpret_cast<uint16_t*>(p.c) + (int64_t)row * p.n + nt * BN;
+      float* prow = p.partial + ((int64_t)ks * p.m + row) * p.n + nt * BN;
 #pragma unroll 1
       for (int c = 0; c < BN; c += 32) {
         float v[32];
         ako::tc::tmem_ld32(taddr + c, v);
         ako::tc::tmem_ld_wait_regs(v);
-        if (row < p.m) {
+        if (row < p.m && p.splits > 1) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 4)
+            *reinterpret_cast<float4*>(prow + c + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+        } else if (row < p.m) {
 #pragma unroll
           for (int j = 0; j < 32; j += 8) {
             uint32_t w[4];
@@ -187,8 +197,42 @@ gemm_f16_tc_kernel(GemmArgs p, const __grid_constant__ CUtensorMap tm_a, const _
   }
 }
 
+// Split-K second step: C = cast(sum over splits, in split order, of the fp32 partials). Eight
+// values per thread; launched with programmatic dependent launch behind the GEMM.
+template <bool BF16>
+__global__ void __launch_bounds__(256) gemm_splitk_reduce_kernel(const float* __restrict__ partial, void* __restrict__ c,
+                                                                 int64_t mn, int splits) {
+  ako::pdl_wait();
+  const int64_t i = ((int64_t)blockIdx.x * 256 + threadIdx.x) * 8;
+  if (i >= mn) return;
+  float acc[8];
+  {
+    const float4 x = __ldcs(reinterpret_cast<const float4*>(partial + i));
+    const float4 y = __ldcs(reinterpret_cast<const float4*>(partial + i + 4));
+    acc[0] = x.x; acc[1] = x.y; acc[2] = x.z; acc[3] = x.w; acc[4] = y.x; acc[5] = y.y; acc[6] = y.z; acc[7] = y.w;
+  }
+  for (int s = 1; s < splits; ++s) {
+    const float4 x = __ldcs(reinterpret_cast<const float4*>(partial + s * mn + i));
+    const float4 y = __ldcs(reinterpret_cast<const float4*>(partial + s * mn + i + 4));
+    acc[0] += x.x; acc[1] += x.y; acc[2] += x.z; acc[3] += x.w; acc[4] += y.x; acc[5] += y.y; acc[6] += y.z; acc[7] += y.w;
+  }
+  uint32_t w[4];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    if (BF16) {
+      const __nv_bfloat162 h = __floats2bfloat162_rn(acc[2 * k], acc[2 * k + 1]);
+      w[k] = *reinterpret_cast<const uint32_t*>(&h);
+    } else {
+      const __half2 h = __floats2half2_rn(acc[2 * k], acc[2 * k + 1]);
+      w[k] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+  }
+  *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(c) + i) = make_uint4(w[0], w[1], w[2], w[3]);
+}
+
 template <int BN, bool BF16>
-int launch_gemm(const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k, cudaStream_t st) {
+int launch_gemm(const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k, int splits, float* partial,
+                cudaStream_t st) {
   using Cfg = GemmCfg<BN>;
   const int a_box_rows = (m >= G_BM) ? G_BM : (int)((m + 7) / 8 * 8);
   CUtensorMap tm_a, tm_b;
@@ -202,37 +246,78 @@ int launch_gemm(const void* a, const void* b, void* c, int64_t m, int64_t n, int
   p.n = (int)n;
   p.k = (int)k;
   p.a_box_rows = a_box_rows;
-  p.bf16 = BF16 ? 1 : 0;
-  const int64_t tiles = ((m + G_BM - 1) / G_BM) * (n / BN);
+  p.splits = splits;
+  p.partial = partial;
+  const int64_t tiles = ((m + G_BM - 1) / G_BM) * (n / BN) * splits;
   const int grid = (int)std::min<int64_t>(tiles, ako::sm_count());
   gemm_f16_tc_kernel<BN, BF16><<<grid, G_THREADS, Cfg::SMEM, st>>>(p, tm_a, tm_b);
   AKO_CHECK_LAUNCH();
+  if (splits > 1) {
+    const int64_t mn = m * n;
+    const unsigned blocks = (unsigned)((mn / 8 + 255) / 256);
+    if (ako::launch_pdl(true, gemm_splitk_reduce_kernel<BF16>, dim3(blocks), dim3(256), 0, st, (const float*)partial, c,
+                        mn, splits) != cudaSuccess)
+      return AKO4X_ELAUNCH;
+  }
   return AKO4X_OK;
+}
+
+// Tile width and K split by how many work items the GPU gets. Full-width tiles (256 columns)
+// without a split once they fill three quarters of the SMs. Below that a tile's K loop (256 MMAs
+// whatever the tile width) is what a call waits for: tiles of 128 columns, and K cut into 2, 4 or 8
+// pieces handled by different CTAs (summed by a second kernel) until there are 128 work items.
+// Measured, whole call, cold L2: M = 16: 15.4 us (unsplit 26.6), M = 128: 17.4, M = 256: 19.5,
+// M = 512: 23.5, M = 969: 30.7 (no split; 256 columns x 2 splits: 29.7).
+struct GemmPlan {
+  int bn, splits;
+};
+inline GemmPlan gemm_plan(int64_t m, int64_t n, int64_t k, bool have_workspace) {
+  const int64_t mt = (m + G_BM - 1) / G_BM;
+  const int sms = ako::sm_count();
+  if (mt * (n / 256) * 4 >= 3 * sms) return {256, 1};
+  if (!have_workspace) return {(mt * (n / 128) * 4 >= 3 * sms) ? 128 : 32, 1};
+  int s = 1;
+  while (s < 8 && mt * (n / 128) * s < 128 && (k / 64) % (2 * s) == 0) s *= 2;
+  return {128, s};
 }
 
 }  // namespace
 
-extern "C" int ako4x_gemm_f16_nt(const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k,
-                                 int is_bf16, void* stream) {
+extern "C" size_t ako4x_gemm_workspace_bytes(int64_t m, int64_t n, int64_t k) {
+  if (m <= 0 || n <= 0 || k <= 0 || n % 256 != 0 || k % 64 != 0) return 0;
+  const GemmPlan pl = gemm_plan(m, n, k, true);
+  return pl.splits > 1 ? (size_t)pl.splits * (size_t)m * (size_t)n * sizeof(float) : 0;
+}
+
+static int gemm_entry(const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k, int is_bf16,
+                      void* workspace, size_t workspace_bytes, void* stream) {
   if (m < 0 || n <= 0 || k <= 0 || m > (1 << 24)) return AKO4X_EINVAL;
   if (n % 256 != 0 || k % 64 != 0) return AKO4X_EUNSUPPORTED_SHAPE;
   if (m == 0) return AKO4X_OK;
   if (!a || !b || !c) return AKO4X_EINVAL;
-  if (((uintptr_t)a | (uintptr_t)b | (uintptr_t)c) & 15) return AKO4X_EINVAL;
+  if (((uintptr_t)a | (uintptr_t)b | (uintptr_t)c | (uintptr_t)workspace) & 15) return AKO4X_EINVAL;
   cudaStream_t st = (cudaStream_t)stream;
-  // Tile width by how many tiles the GPU gets: 256 columns once that fills three quarters of the
-  // SMs, 128 for the sizes between, 32 for small M (64 or more CTAs stream B side by side).
-  const int64_t mt = (m + G_BM - 1) / G_BM;
-  const int sms = ako::sm_count();
-  const int bn = (mt * (n / 256) * 4 >= 3 * sms) ? 256 : (mt * (n / 128) * 4 >= 3 * sms) ? 128 : 32;
+  const GemmPlan pl = gemm_plan(m, n, k, workspace != nullptr);
+  if (pl.splits > 1 && workspace_bytes < (size_t)pl.splits * (size_t)m * (size_t)n * sizeof(float)) return AKO4X_EWORKSPACE;
+  float* part = (float*)workspace;
   if (is_bf16) {
-    if (bn == 256) return launch_gemm<256, true>(a, b, c, m, n, k, st);
-    if (bn == 128) return launch_gemm<128, true>(a, b, c, m, n, k, st);
-    return launch_gemm<32, true>(a, b, c, m, n, k, st);
+    if (pl.bn == 256) return launch_gemm<256, true>(a, b, c, m, n, k, pl.splits, part, st);
+    if (pl.bn == 128) return launch_gemm<128, true>(a, b, c, m, n, k, pl.splits, part, st);
+    return launch_gemm<32, true>(a, b, c, m, n, k, 1, part, st);
   }
-  if (bn == 256) return launch_gemm<256, false>(a, b, c, m, n, k, st);
-  if (bn == 128) return launch_gemm<128, false>(a, b, c, m, n, k, st);
-  return launch_gemm<32, false>(a, b, c, m, n, k, st);
+  if (pl.bn == 256) return launch_gemm<256, false>(a, b, c, m, n, k, pl.splits, part, st);
+  if (pl.bn == 128) return launch_gemm<128, false>(a, b, c, m, n, k, pl.splits, part, st);
+  return launch_gemm<32, false>(a, b, c, m, n, k, 1, part, st);
+}
+
+extern "C" int ako4x_gemm_f16_nt(const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k,
+                                 int is_bf16, void* stream) {
+  return gemm_entry(a, b, c, m, n, k, is_bf16, nullptr, 0, stream);
+}
+
+extern "C" int ako4x_gemm_f16_nt_ws(const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k,
+                                    int is_bf16, void* workspace, size_t workspace_bytes, void* stream) {
+  return gemm_entry(a, b, c, m, n, k, is_bf16, workspace, workspace_bytes, stream);
 }
 
 // Status word of the GEMM kernels: 0, or the code of the first bounded wait that gave up (71

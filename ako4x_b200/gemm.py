@@ -19,7 +19,12 @@ def run(A: torch.Tensor, B: torch.Tensor) -> torch.Tensor:
     n = B.shape[0]
     a, b = A.contiguous(), B.contiguous()
     c = torch.empty((m, n), dtype=A.dtype, device=A.device)
-    st = _cabi.lib().ako4x_gemm_f16_nt(_cabi.ptr(a), _cabi.ptr(b), _cabi.ptr(c), m, n, k,
-                                       1 if A.dtype == torch.bfloat16 else 0, _cabi.stream())
-    _cabi.check(st, "ako4x_gemm_f16_nt")
+    lib = _cabi.lib()
+    # small and medium M split K over CTAs; the fp32 partial products live in this workspace
+    ws_bytes = lib.ako4x_gemm_workspace_bytes(m, n, k)
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=A.device) if ws_bytes else None
+    st = lib.ako4x_gemm_f16_nt_ws(_cabi.ptr(a), _cabi.ptr(b), _cabi.ptr(c), m, n, k,
+                                  1 if A.dtype == torch.bfloat16 else 0,
+                                  _cabi.ptr(ws) if ws is not None else None, ws_bytes, _cabi.stream())
+    _cabi.check(st, "ako4x_gemm_f16_nt_ws")
     return c

@@ -297,6 +297,13 @@ int ako4x_gdn_decode(const void* q, const void* k, const void* v, const float* s
  * launch, no workspace. */
 int ako4x_gemm_f16_nt(const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k,
                       int is_bf16, void* stream);
+/* The same GEMM with a caller-owned workspace, which lets small and medium M split the K dimension
+ * over CTAs (partial products in fp32 in the workspace, summed in split order by a second kernel:
+ * deterministic). ako4x_gemm_workspace_bytes gives the size for a shape (0 when no split is used);
+ * a NULL workspace runs the unsplit kernel; a workspace that is too small is AKO4X_EWORKSPACE. */
+size_t ako4x_gemm_workspace_bytes(int64_t m, int64_t n, int64_t k);
+int ako4x_gemm_f16_nt_ws(const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k,
+                         int is_bf16, void* workspace, size_t workspace_bytes, void* stream);
 /* 0, or the code of a bounded wait of the GEMM kernels that gave up (71-74). Synchronises. */
 int ako4x_gemm_device_status(void);
 

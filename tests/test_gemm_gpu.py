@@ -37,6 +37,28 @@ def test_against_oracle(m):
     assert _cabi.lib().ako4x_gemm_device_status() == 0
 
 
+def test_unsplit_entry_point_agrees():
+    """The entry point without a workspace (no K split) against the oracle, and the split form
+    against it: same products, fp32 sums in another grouping."""
+    import ctypes
+    for m in (5, 200, 700):
+        a = W.make_gemm(m, shape_id=50 + m, device="cuda")
+        c0 = torch.empty((m, 2048), dtype=torch.float16, device="cuda")
+        st = _cabi.lib().ako4x_gemm_f16_nt(_cabi.ptr(a["A"]), _cabi.ptr(a["B"]), _cabi.ptr(c0), m, 2048, 4096, 0,
+                                           _cabi.stream())
+        assert st == 0
+        _check(c0.cpu(), oracle.gemm_nt(a["A"].cpu(), a["B"].cpu()), 2e-3)
+        c1 = gemm.run(a["A"], a["B"])
+        assert _cabi.lib().ako4x_gemm_workspace_bytes(m, 2048, 4096) > 0
+        _check(c1.cpu(), c0.cpu(), 2e-3)
+        # too small a workspace is refused before anything runs
+        ws = torch.empty(64, dtype=torch.uint8, device="cuda")
+        st = _cabi.lib().ako4x_gemm_f16_nt_ws(_cabi.ptr(a["A"]), _cabi.ptr(a["B"]), _cabi.ptr(c0), m, 2048, 4096, 0,
+                                              _cabi.ptr(ws), 64, _cabi.stream())
+        assert st == -4
+    assert _cabi.lib().ako4x_gemm_device_status() == 0
+
+
 def test_bf16_and_other_shapes():
     a = W.make_gemm(515, shape_id=3, n=1024, k=512, dtype=torch.bfloat16)
     c = gemm.run(a["A"].cuda(), a["B"].cuda()).cpu()
