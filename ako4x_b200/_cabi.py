@@ -95,7 +95,8 @@ _SIGNATURES = {
     "ako4x_gemm_device_status": (_INT, []),
     "ako4x_gemm_workspace_bytes": (_SZ, [_I64, _I64, _I64]),
     "ako4x_gemm_f16_nt_ws": (_INT, [_P, _P, _P, _I64, _I64, _I64, _INT, _P, _SZ, _P]),
-    "ako4x_gdn_prefill": (_INT, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _F32, _P, _P, _I64, _I64, _P]),
+    "ako4x_gdn_prefill": (_INT, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _F32, _P, _P, _I64, _I64, _P, _SZ, _P]),
+    "ako4x_gdn_prefill_workspace_bytes": (_SZ, [_I64, _I64]),
     "ako4x_gdn_decode": (_INT, [_P, _P, _P, _P, _P, _P, _P, _P, _F32, _P, _P, _I64, _P]),
     "ako4x_fp8_quantize_1x128": (_INT, [_P, _P, _P, _I64, _I64, _P]),
     "ako4x_dsa_index_k_cache_write": (_INT, [_P, _P, _P, _I64, _I64, _P]),

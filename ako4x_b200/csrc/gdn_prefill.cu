@@ -12,8 +12,9 @@
 // sequence --, q_t / k_t pass through shared memory as fp32 in double-buffered chunks of 16 tokens
 // fetched one chunk ahead. The serial chain per token is one short dot product, three or four
 // shuffle levels and the update; measured about 270 cycles per token and 100 more per token of
-// chunk hand-over, so a single sequence of 8 192 tokens takes 1.5 ms: the chunked (WY) form with
-// tensor-core products is the way past that and is not built. The state crosses HBM once each
+// chunk hand-over, so a single sequence of 8 192 tokens takes 1.5 ms. The chunked form of the
+// recurrence (gdn_prefill_chunk.cuh, fp32 on the CUDA cores) is used for one or two sequences;
+// a tensor-core form is not built. The state crosses HBM once each
 // way; outputs leave in 16- or 32-byte pieces per token and CTA. Processing two tokens per
 // reduction round (both products taken from the same state, the second delta corrected with
 // k1.k2) was built and measured slower (1.97 ms against 1.52 ms): eight values per shuffle level.
@@ -199,20 +200,47 @@ __global__ void __launch_bounds__(P_THREADS) gdn_prefill_kernel(
     __stcs(reinterpret_cast<float4*>(ns + ISTR * i), make_float4(S[4 * i], S[4 * i + 1], S[4 * i + 2], S[4 * i + 3]));
 }
 
+#include "gdn_prefill_chunk.cuh"
+
 }  // namespace
+
+extern "C" size_t ako4x_gdn_prefill_workspace_bytes(int64_t total_tokens, int64_t num_seqs) {
+  if (total_tokens <= 0 || num_seqs <= 0) return 0;
+  return (size_t)(total_tokens / C_TOK + num_seqs + 1) * P_HQ * C_GSTRIDE * sizeof(float);
+}
 
 extern "C" int ako4x_gdn_prefill(const void* q, const void* k, const void* v, const float* state, const float* A_log,
                                  const void* a, const float* dt_bias, const void* b, const int64_t* cu_seqlens,
                                  float scale, void* out, float* new_state, int64_t total_tokens, int64_t num_seqs,
-                                 void* stream) {
+                                 void* workspace, size_t workspace_bytes, void* stream) {
   if (total_tokens < 0 || num_seqs < 0 || num_seqs > 65535) return AKO4X_EINVAL;
   if (num_seqs == 0) return AKO4X_OK;
   if (!A_log || !dt_bias || !cu_seqlens || !new_state) return AKO4X_EINVAL;
   if (total_tokens > 0 && (!q || !k || !v || !a || !b || !out)) return AKO4X_EINVAL;
   if (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)out | (uintptr_t)state | (uintptr_t)new_state) & 15)
     return AKO4X_EINVAL;
-  // Few sequences: 16 lanes per row (128 CTAs per sequence, the shorter serial chain per token);
-  // many: 8 lanes per row (half the instructions per row and token).
+  // The chunked form pays per 16 tokens what the token-by-token form pays per 4-5 tokens on its
+  // serial chain, but does more work per token in total: it wins while the GPU has idle SMs (one or
+  // two sequences: 8 192 tokens in 1.18 ms against 1.52 ms) and loses once every SM holds several
+  // CTAs (8 x 1 024: 0.96 against 0.64 ms), so it is used for up to two sequences.
+  if (workspace != nullptr && num_seqs <= 2) {
+    // chunked form: the token-only tables first, then 128 CTAs per sequence over 16-token chunks
+    if (((uintptr_t)workspace & 15) || workspace_bytes < ako4x_gdn_prefill_workspace_bytes(total_tokens, num_seqs))
+      return AKO4X_EWORKSPACE;
+    if (total_tokens > 0) {
+      gdn_gram_kernel<<<dim3((unsigned)num_seqs, P_HQ, C_GRAM_Z), 256, 0, (cudaStream_t)stream>>>(
+          (const __nv_bfloat16*)q, (const __nv_bfloat16*)k, cu_seqlens, (float*)workspace);
+      AKO_CHECK_LAUNCH();
+    }
+    gdn_prefill_chunk_kernel<<<dim3(P_D / C_ROWS, P_HV, (unsigned)num_seqs), P_THREADS, 0, (cudaStream_t)stream>>>(
+        (const __nv_bfloat16*)q, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, state, A_log, (const __nv_bfloat16*)a,
+        dt_bias, (const __nv_bfloat16*)b, cu_seqlens, scale, (__nv_bfloat16*)out, new_state, (const float*)workspace);
+    AKO_CHECK_LAUNCH();
+    return AKO4X_OK;
+  }
+  // Without a workspace: the token-sequential kernel. Few sequences: 16 lanes per row (128 CTAs per
+  // sequence, the shorter serial chain per token); many: 8 lanes per row (half the instructions
+  // per row and token).
   if (num_seqs * 128 <= 4 * ako::sm_count()) {
     gdn_prefill_kernel<16><<<dim3(P_D / 8, P_HV, (unsigned)num_seqs), P_THREADS, 0, (cudaStream_t)stream>>>(
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, state, A_log, (const __nv_bfloat16*)a,

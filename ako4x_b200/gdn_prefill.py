@@ -14,7 +14,7 @@ from . import _cabi
 
 
 @torch.no_grad()
-def run(q, k, v, state, A_log, a, dt_bias, b, cu_seqlens, scale):
+def run(q, k, v, state, A_log, a, dt_bias, b, cu_seqlens, scale, _chunked=True):
     if q.dim() != 3 or tuple(q.shape[1:]) != (4, 128) or tuple(k.shape) != tuple(q.shape):
         raise _cabi.Ako4xError("gdn_prefill: q and k must be [tokens, 4, 128]")
     T = q.shape[0]
@@ -38,9 +38,14 @@ def run(q, k, v, state, A_log, a, dt_bias, b, cu_seqlens, scale):
     # tokens outside every sequence keep a defined value
     out = torch.zeros((T, 8, 128), dtype=torch.bfloat16, device=q.device)
     new_state = torch.empty((n, 8, 128, 128), dtype=torch.float32, device=q.device)
-    st = _cabi.lib().ako4x_gdn_prefill(_cabi.ptr(qc), _cabi.ptr(kc), _cabi.ptr(vc),
-                                       _cabi.ptr(sc) if sc is not None else None, _cabi.ptr(Ac), _cabi.ptr(ac),
-                                       _cabi.ptr(dc), _cabi.ptr(bc), _cabi.ptr(cu), float(scale), _cabi.ptr(out),
-                                       _cabi.ptr(new_state), T, n, _cabi.stream())
+    lib = _cabi.lib()
+    # the chunked form needs room for its per-chunk tables; _chunked=False runs token by token
+    ws_bytes = lib.ako4x_gdn_prefill_workspace_bytes(T, n) if _chunked else 0
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device) if ws_bytes else None
+    st = lib.ako4x_gdn_prefill(_cabi.ptr(qc), _cabi.ptr(kc), _cabi.ptr(vc),
+                               _cabi.ptr(sc) if sc is not None else None, _cabi.ptr(Ac), _cabi.ptr(ac),
+                               _cabi.ptr(dc), _cabi.ptr(bc), _cabi.ptr(cu), float(scale), _cabi.ptr(out),
+                               _cabi.ptr(new_state), T, n, _cabi.ptr(ws) if ws is not None else None, ws_bytes,
+                               _cabi.stream())
     _cabi.check(st, "ako4x_gdn_prefill")
     return out, new_state

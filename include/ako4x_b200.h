@@ -315,11 +315,17 @@ int ako4x_gemm_device_status(void);
  * owns tokens cu_seqlens[s] .. cu_seqlens[s+1]); out bf16 [tokens, 8, 128]; new_state like state.
  * The decode recurrence (ako4x_gdn_decode) applied to every token of a sequence in order, the
  * output taken after each update. An empty sequence gets a zero new_state (as the definition
- * does); tokens that belong to no sequence are not written. One launch, no workspace. */
+ * does); tokens that belong to no sequence are not written.
+ * With a workspace of ako4x_gdn_prefill_workspace_bytes(total_tokens, num_seqs) bytes (16-byte
+ * aligned) the recurrence runs in chunks of 16 tokens (a kernel that tabulates k_i.k_j and q_i.k_j
+ * per chunk, then the state kernel: only a 16-step substitution is serial per chunk); with a NULL
+ * workspace it runs token by token in one launch. Same results up to fp32 rounding order. */
+size_t ako4x_gdn_prefill_workspace_bytes(int64_t total_tokens, int64_t num_seqs);
 int ako4x_gdn_prefill(const void* q, const void* k, const void* v, const float* state,
                       const float* A_log, const void* a, const float* dt_bias, const void* b,
                       const int64_t* cu_seqlens, float scale, void* out, float* new_state,
-                      int64_t total_tokens, int64_t num_seqs, void* stream);
+                      int64_t total_tokens, int64_t num_seqs, void* workspace,
+                      size_t workspace_bytes, void* stream);
 
 #ifdef __cplusplus
 }

@@ -44,6 +44,20 @@ def test_against_oracle(lens):
     _check(o, s, ro, rs)
 
 
+@pytest.mark.parametrize("lens", [[70, 300], [0, 33], [129]])
+def test_both_forms_agree(lens):
+    """Up to two sequences run in the chunked form (16 tokens per step of the state), more run
+    token by token; `_chunked=False` forces the latter. Both against the oracle and each other."""
+    a = W.make_gdn_prefill(lens, shape_id=21 + len(lens))
+    args = [a[k].cuda() if a[k] is not None else None for k in KEYS]
+    o1, s1 = gdn_prefill.run(*args, a["scale"], _chunked=False)
+    o2, s2 = gdn_prefill.run(*args, a["scale"])
+    ro, rs = oracle.gdn_prefill(*[a[k] for k in KEYS], a["scale"])
+    _check(o1.cpu(), s1.cpu(), ro, rs)
+    _check(o2.cpu(), s2.cpu(), ro, rs)
+    _check(o2.cpu(), s2.cpu(), o1.cpu(), s1.cpu())
+
+
 def test_no_state_default_scale():
     a = W.make_gdn_prefill([40, 9], shape_id=5, with_state=False)
     o, s = _run(a, scale=None)
