@@ -160,6 +160,29 @@ def test_prefill_last_query_equals_decode(built_lib):
     assert torch.isfinite(lse).all()
 
 
+def test_prefill_full_size_sampled_queries(built_lib):
+    """The full-size batch (8 sequences, about 6 500 query tokens against up to 8 192 keys each):
+    24 sampled query tokens, first, last and interior ones, against the CPU oracle. A query at
+    position i of a sequence with q_len queries and kv_len keys sees the first kv_len - q_len + i + 1
+    keys, so each sample is a one-query oracle problem over a prefix of the sequence's page list."""
+    a = W.make_mla_prefill(8, shape_id=2, device="cuda")
+    o, lse = mla_prefill.run(*[a[k] for k in PKEYS])
+    qo, kv = a["qo_indptr"].cpu().long(), a["kv_indptr"].cpu().long()
+    g = torch.Generator().manual_seed(7)
+    ckv, kpe, idx = a["ckv_cache"].cpu(), a["kpe_cache"].cpu(), a["kv_indices"].cpu()
+    for s in range(8):
+        q_len, kv_len = int(qo[s + 1] - qo[s]), int(kv[s + 1] - kv[s])
+        picks = {0, q_len - 1, int(torch.randint(0, q_len, (1,), generator=g))}
+        for i in picks:
+            t = int(qo[s]) + i
+            vis = kv_len - q_len + i + 1
+            ro, rlse = oracle.mla_paged_prefill(
+                a["q_nope"][t:t + 1].cpu(), a["q_pe"][t:t + 1].cpu(), ckv, kpe, torch.tensor([0, 1], dtype=torch.int32),
+                torch.tensor([0, vis], dtype=torch.int32), idx[int(kv[s]):int(kv[s]) + vis], a["sm_scale"])
+            assert_close_bf16(o[t:t + 1].cpu(), ro)
+            assert_lse_close(lse[t:t + 1].cpu(), rlse)
+
+
 def test_prefill_repeatable_full_size(built_lib):
     """Twenty calls on the full-size ragged batch give bit-identical outputs. The batch has a last
     query tile of 7 tokens, i.e. a softmax warp with masked rows beside three warps on the short
