@@ -27,9 +27,11 @@ __global__ void __launch_bounds__(WARPS * 32) gdn_decode_kernel(
     const float* __restrict__ dt_bias, const __nv_bfloat16* __restrict__ b, float scale,
     __nv_bfloat16* __restrict__ out, float* __restrict__ new_state) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int bh = blockIdx.y;                 // sequence * 8 + v head
+  // one linear grid: the row groups of a (sequence, head) are neighbours (they share q and k)
+  constexpr int GROUPS = D / ROWS_PER_WARP / WARPS;
+  const int bh = blockIdx.x / GROUPS;        // sequence * 8 + v head
   const int bi = bh / HV, h = bh % HV;
-  const int row0 = (blockIdx.x * WARPS + warp) * ROWS_PER_WARP;
+  const int row0 = ((blockIdx.x % GROUPS) * WARPS + warp) * ROWS_PER_WARP;
   const int64_t sbase = ((int64_t)bh * D + row0) * D + lane * 4;
 
   // the state rows first: everything else hides behind these loads
@@ -113,10 +115,10 @@ extern "C" int ako4x_gdn_decode(const void* q, const void* k, const void* v, con
   // few sequences: one warp per CTA so that the 16 x batch x 8 row groups spread over all SMs;
   // many: four warps per CTA
   if (batch * HV * (D / ROWS_PER_WARP) <= 4096) {
-    gdn_decode_kernel<1><<<dim3(D / ROWS_PER_WARP, (unsigned)(batch * HV)), 32, 0, st>>>(
+    gdn_decode_kernel<1><<<(unsigned)(batch * HV * (D / ROWS_PER_WARP)), 32, 0, st>>>(
         qp, kp, vp, state, A_log, ap, dt_bias, bp, scale, (__nv_bfloat16*)out, new_state);
   } else {
-    gdn_decode_kernel<4><<<dim3(D / ROWS_PER_WARP / 4, (unsigned)(batch * HV)), 128, 0, st>>>(
+    gdn_decode_kernel<4><<<(unsigned)(batch * HV * (D / ROWS_PER_WARP / 4)), 128, 0, st>>>(
         qp, kp, vp, state, A_log, ap, dt_bias, bp, scale, (__nv_bfloat16*)out, new_state);
   }
   AKO_CHECK_LAUNCH();

@@ -45,6 +45,18 @@ def test_against_oracle(batch):
     _check(o, s, ro, rs)
 
 
+def test_large_batch_sampled_sequences():
+    """9 000 sequences (more (sequence, head) pairs than one grid dimension holds): eight sampled
+    sequences against the oracle."""
+    B = 9000
+    a = W.make_gdn_decode(B, shape_id=3, device="cuda")
+    o, s = gdn_decode.run(*[a[k] for k in KEYS], a["scale"])
+    pick = torch.tensor([0, 1, 4095, 4096, 8190, 8191, 8192, 8999])
+    sub = {k: (a[k][pick.cuda()].cpu() if a[k].shape[0] == B else a[k].cpu()) for k in KEYS}
+    ro, rs = oracle.gdn_decode(*[sub[k] for k in KEYS], a["scale"])
+    _check(o[pick.cuda()].cpu(), s[pick.cuda()].cpu(), ro, rs)
+
+
 def test_no_state_and_default_scale():
     a = W.make_gdn_decode(5, shape_id=77, with_state=False)
     args = [a[k].cuda() if a[k] is not None else None for k in KEYS]
