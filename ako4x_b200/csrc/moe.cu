@@ -11,7 +11,7 @@
 //                   expert-sorted order, so a GEMM tile's A operand is one TMA box.
 //   3. GEMM1        grouped FP8 GEMM  g = x W13^T  with 128x128 block-scale promotion in fp32
 //                   registers, fused SwiGLU  h = silu(g[2048:]) * g[:2048],  and h written as TWO
-//                   e4m3 pieces per element (h ~ s*(hi + lo/16), s a power of two per row and
+//                   e4m3 pieces per element (h ~ s*(hi + lo), lo = e4m3(h/s - hi), s a power of two per row and
 //                   128 columns), which keeps about bf16 accuracy while GEMM2 stays a pure FP8
 //                   tensor-core GEMM.
 //   4. GEMM2        the same grouped FP8 GEMM over K = 2*2048 (hi piece, lo piece) against W2.

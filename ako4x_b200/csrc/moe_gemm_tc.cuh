@@ -68,7 +68,15 @@ __device__ __forceinline__ TileInfo tc_tile_info(const GemmParams& p, const int*
 template <int WHICH>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 moe_gemm_tc_kernel(GemmParams p, const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b) {
-  constexpr int NKB = (WHICH == 1) ? KB1 : KB2;
+  // GEMM2 takes both e4m3 pieces of h (hi and lo, the same scale) against one weight block per K
+  // block: the two products accumulate in the same TMEM accumulator (eight MMAs), so a tile has 16
+  // hand-overs instead of 32 and every weight block enters shared memory once. Its stage holds two
+  // A tiles: three stages of 64 KB where GEMM1 has four of 48 KB.
+  constexpr int NKB = (WHICH == 1) ? KB1 : KB2 / 2;
+  constexpr int STAGES = (WHICH == 1) ? TC_STAGES : 3;
+  constexpr int A_BYTES = (WHICH == 1) ? TC_A_BYTES : 2 * TC_A_BYTES;
+  constexpr int STAGE_BYTES = A_BYTES + TC_B_BYTES;
+  static_assert(STAGES * STAGE_BYTES <= TC_STAGES * TC_STAGE_BYTES, "the ring must fit the allocation");
   constexpr int NT_TILES = (WHICH == 1) ? (INTER / 128) : (HID / TC_BN);
   constexpr uint32_t IDESC = ako::tc::idesc_e4m3_f32(TC_BM, TC_BN);
 
@@ -131,14 +139,15 @@ moe_gemm_tc_kernel(GemmParams p, const __grid_constant__ CUtensorMap tm_a, const
       for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
         const TileInfo ti = tc_tile_info<NT_TILES>(p, s_cum, tile);
         for (int kb = 0; kb < NKB; ++kb, ++g) {
-          const int stage = g % TC_STAGES;
-          const uint32_t ph = (g / TC_STAGES) & 1;
+          const int stage = g % STAGES;
+          const uint32_t ph = (g / STAGES) & 1;
           const uint32_t bar = ako::smem_u32(&s_full[stage]);
           if (!ako::tc::mbar_wait(ako::smem_u32(&s_empty[stage]), ph ^ 1u, p.error, kErrLoad)) { ok = false; break; }
-          const uint32_t sa = smem_base + stage * TC_STAGE_BYTES;
-          const uint32_t sb = sa + TC_A_BYTES;
-          ako::tc::mbar_arrive_expect_tx(bar, TC_STAGE_BYTES);
+          const uint32_t sa = smem_base + stage * STAGE_BYTES;
+          const uint32_t sb = sa + A_BYTES;
+          ako::tc::mbar_arrive_expect_tx(bar, STAGE_BYTES);
           ako::tc::tma_load_2d(sa, &tm_a, kb * 128, ti.row0, bar);
+          if (WHICH == 2) ako::tc::tma_load_2d(sa + TC_A_BYTES, &tm_a, INTER + kb * 128, ti.row0, bar);   // the lo piece
           if (WHICH == 1) {
             const int wr = ti.e * (2 * INTER) + ti.nt * 128;
             ako::tc::tma_load_2d(sb, &tm_b, kb * 128, wr, bar);                         // g1, h cols 0-63
@@ -146,7 +155,7 @@ moe_gemm_tc_kernel(GemmParams p, const __grid_constant__ CUtensorMap tm_a, const
             ako::tc::tma_load_2d(sb + 128 * 128, &tm_b, kb * 128, wr + 64, bar);         // g1, 64-127
             ako::tc::tma_load_2d(sb + 192 * 128, &tm_b, kb * 128, wr + INTER + 64, bar); // g2, 64-127
           } else {
-            ako::tc::tma_load_2d(sb, &tm_b, (kb & 15) * 128, ti.e * HID + ti.nt * TC_BN, bar);
+            ako::tc::tma_load_2d(sb, &tm_b, kb * 128, ti.e * HID + ti.nt * TC_BN, bar);
           }
         }
       }
@@ -157,7 +166,7 @@ moe_gemm_tc_kernel(GemmParams p, const __grid_constant__ CUtensorMap tm_a, const
     if (lane == 0) {
       // descriptor low words: +2 per K = 32 slice, bytes >> 4 per stage
       const uint32_t a_lo0 = ako::tc::smem_desc_lo(smem_base);
-      const uint32_t b_lo0 = ako::tc::smem_desc_lo(smem_base + TC_A_BYTES);
+      const uint32_t b_lo0 = ako::tc::smem_desc_lo(smem_base + A_BYTES);
       int g = 0, stage = 0;
       uint32_t ph = 0;
       bool ok = true;
@@ -168,16 +177,23 @@ moe_gemm_tc_kernel(GemmParams p, const __grid_constant__ CUtensorMap tm_a, const
           if (!ako::tc::mbar_wait(ako::smem_u32(&s_acc_empty[buf]), aph ^ 1u, p.error, kErrMmaAcc)) { ok = false; break; }
           if (!ako::tc::mbar_wait(ako::smem_u32(&s_full[stage]), ph, p.error, kErrMmaFull)) { ok = false; break; }
           ako::tc::fence_after_thread_sync();
-          const uint32_t a_lo = a_lo0 + stage * (TC_STAGE_BYTES >> 4);
-          const uint32_t b_lo = b_lo0 + stage * (TC_STAGE_BYTES >> 4);
+          const uint32_t a_lo = a_lo0 + stage * (STAGE_BYTES >> 4);
+          const uint32_t b_lo = b_lo0 + stage * (STAGE_BYTES >> 4);
           const uint32_t d = tmem_base + buf * TC_BN;
           ako::tc::mma_f8_lohi<false>(d, a_lo, b_lo, IDESC);
           ako::tc::mma_f8_lohi<true>(d, a_lo + 2, b_lo + 2, IDESC);
           ako::tc::mma_f8_lohi<true>(d, a_lo + 4, b_lo + 4, IDESC);
           ako::tc::mma_f8_lohi<true>(d, a_lo + 6, b_lo + 6, IDESC);
+          if (WHICH == 2) {   // the lo piece of h against the same weight block
+            const uint32_t a2 = a_lo + (TC_A_BYTES >> 4);
+            ako::tc::mma_f8_lohi<true>(d, a2, b_lo, IDESC);
+            ako::tc::mma_f8_lohi<true>(d, a2 + 2, b_lo + 2, IDESC);
+            ako::tc::mma_f8_lohi<true>(d, a2 + 4, b_lo + 4, IDESC);
+            ako::tc::mma_f8_lohi<true>(d, a2 + 6, b_lo + 6, IDESC);
+          }
           ako::tc::mma_commit(ako::smem_u32(&s_empty[stage]));
           ako::tc::mma_commit(ako::smem_u32(&s_acc_full[buf]));
-          if (++stage == TC_STAGES) { stage = 0; ph ^= 1u; }
+          if (++stage == STAGES) { stage = 0; ph ^= 1u; }
         }
       }
     }
@@ -211,11 +227,10 @@ moe_gemm_tc_kernel(GemmParams p, const __grid_constant__ CUtensorMap tm_a, const
       float b0_n = __ldg(bsp0), b1_n = __ldg(bsp1);
 #pragma unroll 1
       for (int kb = 0; kb < NKB; ++kb, ++g) {
-        float sa = sa_n;
-        if (WHICH == 2 && kb >= 16) sa *= 0.0625f;
+        const float sa = sa_n;
         const float s0 = sa * b0_n, s1 = sa * b1_n;
         if (kb + 1 < NKB) {
-          const int nk = (WHICH == 1) ? (kb + 1) : ((kb + 1) & 15);
+          const int nk = kb + 1;
           sa_n = live ? __ldg(asp + (int64_t)nk * p.a_scale_stride) : 0.f;
           b0_n = __ldg(bsp0 + nk);
           b1_n = __ldg(bsp1 + nk);
@@ -311,7 +326,7 @@ moe_gemm_tc_kernel(GemmParams p, const __grid_constant__ CUtensorMap tm_a, const
                 const __half2_raw hr = __nv_cvt_fp8x2_to_halfraw2(hi, __NV_E4M3);
                 const float2 hf2 = __half22float2(*reinterpret_cast<const __half2*>(&hr));
                 const __nv_fp8x2_storage_t lo = __nv_cvt_float2_to_fp8x2(
-                    make_float2((a0 - hf2.x) * 16.f, (a1 - hf2.y) * 16.f), __NV_SATFINITE, __NV_E4M3);
+                    make_float2(a0 - hf2.x, a1 - hf2.y), __NV_SATFINITE, __NV_E4M3);
                 hw |= (uint32_t)hi << (16 * hh);
                 lw |= (uint32_t)lo << (16 * hh);
               }

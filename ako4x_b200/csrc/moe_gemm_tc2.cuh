@@ -242,7 +242,6 @@ moe_gemm_tc2_kernel(GemmParams p, const __grid_constant__ CUtensorMap tm_a, cons
 #pragma unroll 1
       for (int kb = 0; kb < NKB; ++kb, ++g) {
         float sa = sa_n;
-        if (WHICH == 2 && kb >= 16) sa *= 0.0625f;
         const float s0 = sa * b0_n, s1 = sa * b1_n;
         if (kb + 1 < NKB) {
           const int nk = (WHICH == 1) ? (kb + 1) : ((kb + 1) & 15);
@@ -341,7 +340,7 @@ moe_gemm_tc2_kernel(GemmParams p, const __grid_constant__ CUtensorMap tm_a, cons
                 const __half2_raw hr = __nv_cvt_fp8x2_to_halfraw2(hi, __NV_E4M3);
                 const float2 hf2 = __half22float2(*reinterpret_cast<const __half2*>(&hr));
                 const __nv_fp8x2_storage_t lo = __nv_cvt_float2_to_fp8x2(
-                    make_float2((a0 - hf2.x) * 16.f, (a1 - hf2.y) * 16.f), __NV_SATFINITE, __NV_E4M3);
+                    make_float2(a0 - hf2.x, a1 - hf2.y), __NV_SATFINITE, __NV_E4M3);
                 hw |= (uint32_t)hi << (16 * hh);
                 lw |= (uint32_t)lo << (16 * hh);
               }
