@@ -8,12 +8,12 @@
 // :1333-1400 for its entry point). The rows S[v,:] of a state never interact, so this first
 // version runs the recurrence as it is written, token by token, with all the parallelism the rows
 // give: a row is held by 8 or 16 lanes (16 or 8 state values each, in registers for the whole
-// sequence), a CTA of four warps owns 16 or 8 rows of one (sequence, head) -- 64 or 128 CTAs per
+// sequence), four compute warps own 16 or 8 rows of one (sequence, head) -- 64 or 128 CTAs per
 // sequence --, q_t / k_t pass through shared memory as fp32 in double-buffered chunks of 16 tokens
-// fetched one chunk ahead. The serial chain per token is one short dot product, three or four
+// that a fifth warp stages one chunk ahead (it also stores the finished chunk's outputs). The serial chain per token is one short dot product, three or four
 // shuffle levels and the update; measured about 270 cycles per token and 100 more per token of
 // chunk hand-over, so a single sequence of 8 192 tokens takes 1.5 ms. The chunked form of the
-// recurrence (gdn_prefill_chunk.cuh, fp32 on the CUDA cores) is used for one or two sequences;
+// recurrence (gdn_prefill_chunk.cuh, fp32 on the CUDA cores) is used for a single sequence;
 // a tensor-core form is not built. The state crosses HBM once each
 // way; outputs leave in 16- or 32-byte pieces per token and CTA. Processing two tokens per
 // reduction round (both products taken from the same state, the second delta corrected with
@@ -24,11 +24,77 @@ namespace {
 
 constexpr int P_HQ = 4, P_HV = 8, P_D = 128;
 constexpr int P_CHUNK = 16;         // tokens per staging chunk
-constexpr int P_THREADS = 128;      // 4 warps; a row is held by LPR lanes, 32 / LPR rows per warp
+constexpr int P_CONSUMERS = 128;    // 4 warps; a row is held by LPR lanes, 32 / LPR rows per warp
+constexpr int P_THREADS = 160;      // + one producer warp that stages the next chunk and stores the last one's outputs
 
-struct Staged {       // what one thread fetches for one chunk: 32 of the chunk's 4096 q/k values
-  uint4 w[4];
-};
+// The producer warp's work for one 16-token chunk `c` of the sequence [t0, t1): q and k of head hq
+// as fp32 into kq[token][k | q][128] (token r is one coalesced 512-byte read, lane L converts its 16
+// bytes and writes 32 consecutive bytes: no bank conflict), the v values of the CTA's ROWS rows,
+// and per token the gate pair: gate[token] = g (or log2 g when LOG2) and beta[token]. Tokens past
+// the end of the sequence are staged as nothing-happens tokens (k = q = v = 0, g = 1, beta = 0).
+template <int ROWS, bool LOG2>
+__device__ __forceinline__ void gdn_stage_chunk(int lane, int c, int64_t t0, int64_t t1, int hq, int h, int rg,
+                                                const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k,
+                                                const __nv_bfloat16* __restrict__ v, const __nv_bfloat16* __restrict__ a,
+                                                const __nv_bfloat16* __restrict__ b, float neg_A, float dtb,
+                                                float (*kq)[2][P_D], float* gate, float* beta, float (*vs)[ROWS]) {
+  const int64_t tb = t0 + (int64_t)c * P_CHUNK;
+  uint4 w[P_CHUNK];
+#pragma unroll
+  for (int r = 0; r < P_CHUNK; ++r) {
+    w[r] = make_uint4(0u, 0u, 0u, 0u);
+    if (tb + r < t1) {
+      const __nv_bfloat16* src = ((lane < 16) ? k : q) + ((tb + r) * P_HQ + hq) * P_D + (lane & 15) * 8;
+      w[r] = __ldg(reinterpret_cast<const uint4*>(src));
+    }
+  }
+  // lanes 0-15: the v values of token `lane`; lanes 0-15 also a, lanes 16-31 b of token lane & 15
+  const int tok = lane & 15;
+  const bool valid = tb + tok < t1;
+  uint4 vw[ROWS / 8];
+#pragma unroll
+  for (int i = 0; i < ROWS / 8; ++i) {
+    vw[i] = make_uint4(0u, 0u, 0u, 0u);
+    if (valid && lane < 16) vw[i] = __ldg(reinterpret_cast<const uint4*>(v + ((tb + tok) * P_HV + h) * P_D + rg * ROWS) + i);
+  }
+  unsigned short graw = 0;
+  if (valid) graw = __ldg(reinterpret_cast<const unsigned short*>(((lane < 16) ? a : b) + (tb + tok) * P_HV + h));
+#pragma unroll
+  for (int r = 0; r < P_CHUNK; ++r) {
+    float* dst = &kq[r][lane >> 4][(lane & 15) * 8];
+    *reinterpret_cast<float4*>(dst) = make_float4(ako::bf16_lo(w[r].x), ako::bf16_hi(w[r].x), ako::bf16_lo(w[r].y), ako::bf16_hi(w[r].y));
+    *reinterpret_cast<float4*>(dst + 4) = make_float4(ako::bf16_lo(w[r].z), ako::bf16_hi(w[r].z), ako::bf16_lo(w[r].w), ako::bf16_hi(w[r].w));
+  }
+  if (lane < 16) {
+#pragma unroll
+    for (int i = 0; i < ROWS / 8; ++i) {
+      const uint32_t x[4] = {vw[i].x, vw[i].y, vw[i].z, vw[i].w};
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        vs[tok][8 * i + 2 * u] = ako::bf16_lo(x[u]);
+        vs[tok][8 * i + 2 * u + 1] = ako::bf16_hi(x[u]);
+      }
+    }
+    const float y = __uint_as_float((uint32_t)graw << 16) + dtb;
+    const float sp = (y > 20.f) ? y : log1pf(expf(y));
+    gate[tok] = !valid ? (LOG2 ? 0.f : 1.f) : (LOG2 ? neg_A * 1.4426950408889634f * sp : expf(neg_A * sp));
+  } else {
+    beta[tok] = valid ? 1.f / (1.f + expf(-__uint_as_float((uint32_t)graw << 16))) : 0.f;
+  }
+}
+
+// The producer's other job: the bf16 outputs of a finished chunk (ROWS values per token) to global memory.
+template <int ROWS>
+__device__ __forceinline__ void gdn_store_chunk(int lane, int c, int64_t t0, int len, int h, int rg,
+                                                const __nv_bfloat16 (*so)[ROWS], __nv_bfloat16* __restrict__ out) {
+  constexpr int PIECES = ROWS / 8;
+  const int ntok = min(P_CHUNK, len - c * P_CHUNK);
+  for (int idx = lane; idx < ntok * PIECES; idx += 32) {
+    const int j = idx / PIECES, part = idx % PIECES;
+    const int64_t t = t0 + (int64_t)c * P_CHUNK + j;
+    *reinterpret_cast<uint4*>(out + (t * P_HV + h) * P_D + rg * ROWS + part * 8) = *reinterpret_cast<const uint4*>(&so[j][part * 8]);
+  }
+}
 
 template <int LPR>
 __global__ void __launch_bounds__(P_THREADS) gdn_prefill_kernel(
@@ -44,9 +110,10 @@ __global__ void __launch_bounds__(P_THREADS) gdn_prefill_kernel(
   __shared__ __align__(16) float s_kq[2][P_CHUNK][2][P_D];     // [buffer][token][k | q][128]  32 KB
   __shared__ float s_g[2][P_CHUNK], s_beta[2][P_CHUNK];
   __shared__ float s_v[2][P_CHUNK][P_ROWS];
-  __shared__ __align__(16) __nv_bfloat16 s_out[P_CHUNK][P_ROWS];
+  __shared__ __align__(16) __nv_bfloat16 s_out[2][P_CHUNK][P_ROWS];
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const bool producer = warp == P_CONSUMERS / 32;
   const int rg = blockIdx.x, h = blockIdx.y, seq = blockIdx.z;
   const int hq = h / (P_HV / P_HQ);
   const int64_t t0 = cu_seqlens[seq], t1 = cu_seqlens[seq + 1];
@@ -61,11 +128,16 @@ __global__ void __launch_bounds__(P_THREADS) gdn_prefill_kernel(
 
   float S[EPL];
   if (len <= 0) {   // the definition leaves the new state of an empty sequence at zero
+    if (!producer) {
 #pragma unroll
-    for (int i = 0; i < NI; ++i) *reinterpret_cast<float4*>(ns + ISTR * i) = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int i = 0; i < NI; ++i) *reinterpret_cast<float4*>(ns + ISTR * i) = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
     return;
   }
-  if (state != nullptr) {
+  if (producer) {
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) S[i] = 0.f;
+  } else if (state != nullptr) {
     const float* sp = state + (((int64_t)seq * P_HV + h) * P_D + row) * P_D + seg * 4;
 #pragma unroll
     for (int i = 0; i < NI; ++i) {
@@ -79,60 +151,22 @@ __global__ void __launch_bounds__(P_THREADS) gdn_prefill_kernel(
   const float neg_A = -expf(A_log[h]);
   const float dtb = dt_bias[h];
 
-  // staging: thread `tid` fetches, for chunk token j = tid / 8 and part = tid % 8, 16 k values and
-  // 16 q values (elements part*16 .. +15 of head hq), as 2 x 16 bytes each
-  const int st_tok = tid >> 3, st_part = tid & 7;
-  // fetch() only issues loads (nothing here may depend on a loaded value: the thread would wait
-  // for HBM before it starts the chunk it already has); stash() converts and computes the gates
-  // after that chunk is done.
-  auto fetch = [&](int c, Staged& r, uint32_t& vraw, uint32_t& graw) {
-    const int64_t t = t0 + (int64_t)c * P_CHUNK + st_tok;
-    r.w[0] = r.w[1] = r.w[2] = r.w[3] = make_uint4(0u, 0u, 0u, 0u);
-    vraw = 0u;
-    graw = 0u;
-    if (t < t1) {
-      const uint4* kp = reinterpret_cast<const uint4*>(k + (t * P_HQ + hq) * P_D + st_part * 16);
-      const uint4* qp = reinterpret_cast<const uint4*>(q + (t * P_HQ + hq) * P_D + st_part * 16);
-      r.w[0] = __ldg(kp); r.w[1] = __ldg(kp + 1); r.w[2] = __ldg(qp); r.w[3] = __ldg(qp + 1);
-      // the 8 threads of a token fetch its v values, two each; thread 0 the gate input a, thread 1 b
-      if (st_part * 2 < P_ROWS)
-        vraw = __ldg(reinterpret_cast<const uint32_t*>(v + (t * P_HV + h) * P_D + rg * P_ROWS + st_part * 2));
-      if (st_part == 0) graw = __ldg(reinterpret_cast<const unsigned short*>(a + t * P_HV + h));
-      if (st_part == 1) graw = __ldg(reinterpret_cast<const unsigned short*>(b + t * P_HV + h));
-    }
-  };
-  auto stash = [&](int buf, const Staged& r, uint32_t vraw, uint32_t graw) {
-    float* kd = &s_kq[buf][st_tok][0][st_part * 16];
-    float* qd = &s_kq[buf][st_tok][1][st_part * 16];
-    const uint32_t kw[8] = {r.w[0].x, r.w[0].y, r.w[0].z, r.w[0].w, r.w[1].x, r.w[1].y, r.w[1].z, r.w[1].w};
-    const uint32_t qw[8] = {r.w[2].x, r.w[2].y, r.w[2].z, r.w[2].w, r.w[3].x, r.w[3].y, r.w[3].z, r.w[3].w};
-#pragma unroll
-    for (int i = 0; i < 8; i += 2) {
-      *reinterpret_cast<float4*>(kd + 2 * i) = make_float4(ako::bf16_lo(kw[i]), ako::bf16_hi(kw[i]), ako::bf16_lo(kw[i + 1]), ako::bf16_hi(kw[i + 1]));
-      *reinterpret_cast<float4*>(qd + 2 * i) = make_float4(ako::bf16_lo(qw[i]), ako::bf16_hi(qw[i]), ako::bf16_lo(qw[i + 1]), ako::bf16_hi(qw[i + 1]));
-    }
-    if (st_part * 2 < P_ROWS) {
-      s_v[buf][st_tok][st_part * 2] = ako::bf16_lo(vraw);
-      s_v[buf][st_tok][st_part * 2 + 1] = ako::bf16_hi(vraw);
-    }
-    const float x = __uint_as_float(graw << 16);
-    if (st_part == 0) {
-      const float y = x + dtb;
-      const float sp = (y > 20.f) ? y : log1pf(expf(y));
-      s_g[buf][st_tok] = expf(neg_A * sp);
-    }
-    if (st_part == 1) s_beta[buf][st_tok] = 1.f / (1.f + expf(-x));
-  };
-
+  // One warp runs ahead of the four that hold the state: while they compute chunk c it stores the
+  // outputs of chunk c - 1 and stages chunk c + 1 (global loads, conversion, gate math), so that a
+  // chunk costs the compute warps one barrier and nothing else.
   const int chunks = (len + P_CHUNK - 1) / P_CHUNK;
-  Staged r;
-  uint32_t vraw, graw;
-  fetch(0, r, vraw, graw);
-  stash(0, r, vraw, graw);
+  if (producer) gdn_stage_chunk<P_ROWS, false>(lane, 0, t0, t1, hq, h, rg, q, k, v, a, b, neg_A, dtb, s_kq[0], s_g[0], s_beta[0], s_v[0]);
   __syncthreads();
   for (int c = 0; c < chunks; ++c) {
     const int buf = c & 1;
-    if (c + 1 < chunks) fetch(c + 1, r, vraw, graw);     // in flight while this chunk is computed
+    if (producer) {
+      if (c > 0) gdn_store_chunk<P_ROWS>(lane, c - 1, t0, len, h, rg, s_out[buf ^ 1], out);
+      if (c + 1 < chunks)
+        gdn_stage_chunk<P_ROWS, false>(lane, c + 1, t0, t1, hq, h, rg, q, k, v, a, b, neg_A, dtb, s_kq[buf ^ 1], s_g[buf ^ 1],
+                                       s_beta[buf ^ 1], s_v[buf ^ 1]);
+      __syncthreads();
+      continue;
+    }
     const int ntok = min(P_CHUNK, len - c * P_CHUNK);
     // q_t / k_t of the next token are read while the current one is computed: the loads, the q.k
     // product and S.q are off the serial chain (S.k -> three shuffles -> delta -> update)
@@ -169,7 +203,7 @@ __global__ void __launch_bounds__(P_THREADS) gdn_prefill_kernel(
       const float delta = beta * (vval - g * e1);
 #pragma unroll
       for (int i = 0; i < EPL; ++i) S[i] = fmaf(g, S[i], delta * kk[i]);
-      if (seg == 0) s_out[j][row_local] = __float2bfloat16_rn(scale * (g * e2 + e3 * delta));
+      if (seg == 0) s_out[buf][j][row_local] = __float2bfloat16_rn(scale * (g * e2 + e3 * delta));
     };
     {
       float kA[EPL], qA[EPL], kB[EPL], qB[EPL];
@@ -183,17 +217,11 @@ __global__ void __launch_bounds__(P_THREADS) gdn_prefill_kernel(
         }
       }
     }
-    __syncthreads();                       // s_out complete; buffer buf ^ 1 no longer read
-    // outputs of the chunk: token j, P_ROWS rows = 32 or 16 bytes, moved in 16-byte pieces
-    constexpr int PIECES = P_ROWS / 8;
-    if (tid < PIECES * ntok) {
-      const int j = tid / PIECES, part = tid % PIECES;
-      const int64_t t = t0 + (int64_t)c * P_CHUNK + j;
-      *reinterpret_cast<uint4*>(out + (t * P_HV + h) * P_D + rg * P_ROWS + part * 8) =
-          *reinterpret_cast<const uint4*>(&s_out[j][part * 8]);
-    }
-    if (c + 1 < chunks) stash(buf ^ 1, r, vraw, graw);
-    __syncthreads();
+    __syncthreads();                       // chunk c done, chunk c + 1 staged
+  }
+  if (producer) {
+    gdn_store_chunk<P_ROWS>(lane, chunks - 1, t0, len, h, rg, s_out[(chunks - 1) & 1], out);
+    return;
   }
 #pragma unroll
   for (int i = 0; i < NI; ++i)
@@ -220,10 +248,10 @@ extern "C" int ako4x_gdn_prefill(const void* q, const void* k, const void* v, co
   if (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)out | (uintptr_t)state | (uintptr_t)new_state) & 15)
     return AKO4X_EINVAL;
   // The chunked form pays per 16 tokens what the token-by-token form pays per 4-5 tokens on its
-  // serial chain, but does more work per token in total: it wins while the GPU has idle SMs (one or
-  // two sequences: 8 192 tokens in 1.18 ms against 1.52 ms) and loses once every SM holds several
-  // CTAs (8 x 1 024: 0.96 against 0.64 ms), so it is used for up to two sequences.
-  if (workspace != nullptr && num_seqs <= 2) {
+  // serial chain, but does more work per token in total and holds one CTA per SM (243 registers):
+  // it wins for a single sequence (8 192 tokens: 1.00 ms against 1.40 ms) and loses from two
+  // sequences on (2 x 4 096: 0.99 against 0.90 ms), so it is used for one sequence.
+  if (workspace != nullptr && num_seqs == 1) {
     // chunked form: the token-only tables first, then 128 CTAs per sequence over 16-token chunks
     if (((uintptr_t)workspace & 15) || workspace_bytes < ako4x_gdn_prefill_workspace_bytes(total_tokens, num_seqs))
       return AKO4X_EWORKSPACE;

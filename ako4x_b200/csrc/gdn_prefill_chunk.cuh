@@ -82,9 +82,10 @@ __global__ void __launch_bounds__(P_THREADS) gdn_prefill_chunk_kernel(
   __shared__ __align__(16) float s_tab[2][2][C_TOK][C_TPAD];      // [buffer][k.k | q.k][i][j]
   __shared__ float s_lg[2][C_TOK], s_beta[2][C_TOK];              // log2 of the decay, beta
   __shared__ float s_v[2][C_TOK][C_ROWS];
-  __shared__ __align__(16) __nv_bfloat16 s_out[C_TOK][C_ROWS];
+  __shared__ __align__(16) __nv_bfloat16 s_out[2][C_TOK][C_ROWS];
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const bool producer = warp == P_CONSUMERS / 32;
   const int rg = blockIdx.x, h = blockIdx.y, seq = blockIdx.z;
   const int hq = h / (P_HV / P_HQ);
   const int64_t t0 = cu_seqlens[seq], t1 = cu_seqlens[seq + 1];
@@ -96,11 +97,16 @@ __global__ void __launch_bounds__(P_THREADS) gdn_prefill_chunk_kernel(
   float* ns = new_state + (((int64_t)seq * P_HV + h) * P_D + row) * P_D + 4 * i;
   float S[8];
   if (len <= 0) {   // the definition leaves the new state of an empty sequence at zero
-    *reinterpret_cast<float4*>(ns) = make_float4(0.f, 0.f, 0.f, 0.f);
-    *reinterpret_cast<float4*>(ns + 64) = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (!producer) {
+      *reinterpret_cast<float4*>(ns) = make_float4(0.f, 0.f, 0.f, 0.f);
+      *reinterpret_cast<float4*>(ns + 64) = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
     return;
   }
-  if (state != nullptr) {
+  if (producer) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) S[e] = 0.f;
+  } else if (state != nullptr) {
     const float* sp = state + (((int64_t)seq * P_HV + h) * P_D + row) * P_D + 4 * i;
     const float4 x = __ldcs(reinterpret_cast<const float4*>(sp)), y = __ldcs(reinterpret_cast<const float4*>(sp + 64));
     S[0] = x.x; S[1] = x.y; S[2] = x.z; S[3] = x.w; S[4] = y.x; S[5] = y.y; S[6] = y.z; S[7] = y.w;
@@ -108,71 +114,34 @@ __global__ void __launch_bounds__(P_THREADS) gdn_prefill_chunk_kernel(
 #pragma unroll
     for (int e = 0; e < 8; ++e) S[e] = 0.f;
   }
-  const float neg_A_log2e = -expf(A_log[h]) * 1.4426950408889634f;
+  const float neg_A = -expf(A_log[h]);
   const float dtb = dt_bias[h];
 
-  // staging, one chunk ahead: thread tid = (token tid / 8, part tid % 8) fetches 16 k and 16 q
-  // values, a pair of v values (parts 0-3), the gate inputs (parts 0, 1) and 16 bytes of a table.
-  // fetch() only issues loads; stash() converts after the current chunk is done.
-  const int st_tok = tid >> 3, st_part = tid & 7;
-  struct Fetched {
-    uint4 w[4];
-    uint4 tab;
-    uint32_t vraw, graw;
-  };
-  auto fetch = [&](int c, Fetched& r) {
-    const int64_t t = t0 + (int64_t)c * C_TOK + st_tok;
-    r.w[0] = r.w[1] = r.w[2] = r.w[3] = make_uint4(0u, 0u, 0u, 0u);
-    r.vraw = 0u;
-    r.graw = 0u;
-    if (t < t1) {
-      const uint4* kp = reinterpret_cast<const uint4*>(k + (t * P_HQ + hq) * P_D + st_part * 16);
-      const uint4* qp = reinterpret_cast<const uint4*>(q + (t * P_HQ + hq) * P_D + st_part * 16);
-      r.w[0] = __ldg(kp); r.w[1] = __ldg(kp + 1); r.w[2] = __ldg(qp); r.w[3] = __ldg(qp + 1);
-      if (st_part < C_ROWS / 2)
-        r.vraw = __ldg(reinterpret_cast<const uint32_t*>(v + (t * P_HV + h) * P_D + rg * C_ROWS + st_part * 2));
-      if (st_part == 0) r.graw = __ldg(reinterpret_cast<const unsigned short*>(a + t * P_HV + h));
-      if (st_part == 1) r.graw = __ldg(reinterpret_cast<const unsigned short*>(b + t * P_HV + h));
-    }
-    const float* tp = tables + (gdn_chunk_slot(t0, seq, c) * P_HQ + hq) * C_GSTRIDE;
-    r.tab = __ldg(reinterpret_cast<const uint4*>(tp) + tid);       // 128 threads x 16 bytes = both tables
-  };
-  auto stash = [&](int buf, const Fetched& r, bool valid) {
-    float* kd = &s_kq[buf][st_tok][0][st_part * 16];
-    float* qd = &s_kq[buf][st_tok][1][st_part * 16];
-    const uint32_t kw[8] = {r.w[0].x, r.w[0].y, r.w[0].z, r.w[0].w, r.w[1].x, r.w[1].y, r.w[1].z, r.w[1].w};
-    const uint32_t qw[8] = {r.w[2].x, r.w[2].y, r.w[2].z, r.w[2].w, r.w[3].x, r.w[3].y, r.w[3].z, r.w[3].w};
+  // The producer warp stages chunk c + 1 (and the chunk's two tables, 2 KB) and stores the outputs
+  // of chunk c - 1 while the four compute warps work on chunk c: one barrier per chunk.
+  auto stage = [&](int c, int buf) {
+    gdn_stage_chunk<C_ROWS, true>(lane, c, t0, t1, hq, h, rg, q, k, v, a, b, neg_A, dtb, s_kq[buf], s_lg[buf], s_beta[buf],
+                                  s_v[buf]);
+    const uint4* tp = reinterpret_cast<const uint4*>(tables + (gdn_chunk_slot(t0, seq, c) * P_HQ + hq) * C_GSTRIDE);
 #pragma unroll
-    for (int u = 0; u < 8; u += 2) {
-      *reinterpret_cast<float4*>(kd + 2 * u) = make_float4(ako::bf16_lo(kw[u]), ako::bf16_hi(kw[u]), ako::bf16_lo(kw[u + 1]), ako::bf16_hi(kw[u + 1]));
-      *reinterpret_cast<float4*>(qd + 2 * u) = make_float4(ako::bf16_lo(qw[u]), ako::bf16_hi(qw[u]), ako::bf16_lo(qw[u + 1]), ako::bf16_hi(qw[u + 1]));
+    for (int u = 0; u < 4; ++u) {
+      const int f = lane + 32 * u;                      // float4 number f of the 128 that make both tables
+      const uint4 x = __ldg(tp + f);
+      *reinterpret_cast<uint4*>(&s_tab[buf][f >> 6][(f & 63) >> 2][(f & 3) * 4]) = x;
     }
-    if (st_part < C_ROWS / 2) {
-      s_v[buf][st_tok][st_part * 2] = ako::bf16_lo(r.vraw);
-      s_v[buf][st_tok][st_part * 2 + 1] = ako::bf16_hi(r.vraw);
-    }
-    const float x = __uint_as_float(r.graw << 16);
-    if (st_part == 0) {
-      const float y = x + dtb;
-      const float sp = (y > 20.f) ? y : log1pf(expf(y));
-      s_lg[buf][st_tok] = valid ? neg_A_log2e * sp : 0.f;        // a token past the end decays nothing
-    }
-    if (st_part == 1) s_beta[buf][st_tok] = valid ? 1.f / (1.f + expf(-x)) : 0.f;
-    // 16 bytes of a table: float4 number tid & 63 of table tid >> 6, row (tid & 63) / 4
-    const int f = tid & 63;
-    *reinterpret_cast<uint4*>(&s_tab[buf][tid >> 6][f >> 2][(f & 3) * 4]) = r.tab;
   };
-
   const int chunks = (len + C_TOK - 1) / C_TOK;
-  Fetched r;
-  fetch(0, r);
-  stash(0, r, t0 + st_tok < t1);
+  if (producer) stage(0, 0);
   __syncthreads();
   const bool b3 = (i & 8) != 0, b2 = (i & 4) != 0, b1 = (i & 2) != 0, b0 = (i & 1) != 0;
   for (int c = 0; c < chunks; ++c) {
     const int buf = c & 1;
-    if (c + 1 < chunks) fetch(c + 1, r);     // in flight while this chunk is computed
-    const int ntok = min(C_TOK, len - c * C_TOK);
+    if (producer) {
+      if (c > 0) gdn_store_chunk<C_ROWS>(lane, c - 1, t0, len, h, rg, s_out[buf ^ 1], out);
+      if (c + 1 < chunks) stage(c + 1, buf ^ 1);
+      __syncthreads();
+      continue;
+    }
 
     // 1. this lane's part of S0.k_j and S0.q_j for the 16 tokens: 32 independent short dot products
     float pa[C_TOK], pc[C_TOK];
@@ -245,7 +214,7 @@ __global__ void __launch_bounds__(P_THREADS) gdn_prefill_chunk_kernel(
       rhs = fmaf(-ca[j], dj, rhs);
       o = fmaf(co[j], dj, o);
     }
-    s_out[i][row_local] = __float2bfloat16_rn(scale * o);
+    s_out[buf][i][row_local] = __float2bfloat16_rn(scale * o);
     // 5. the state at the end of the chunk
     {
       const float lend = lc[C_TOK - 1];
@@ -261,13 +230,11 @@ __global__ void __launch_bounds__(P_THREADS) gdn_prefill_chunk_kernel(
         S[4] = fmaf(w, k1.x, S[4]); S[5] = fmaf(w, k1.y, S[5]); S[6] = fmaf(w, k1.z, S[6]); S[7] = fmaf(w, k1.w, S[7]);
       }
     }
-    __syncthreads();                       // s_out complete; buffer buf ^ 1 no longer read
-    if (tid < ntok) {                      // token tid of the chunk: 8 rows = 16 bytes
-      const int64_t t = t0 + (int64_t)c * C_TOK + tid;
-      *reinterpret_cast<uint4*>(out + (t * P_HV + h) * P_D + rg * C_ROWS) = *reinterpret_cast<const uint4*>(&s_out[tid][0]);
-    }
-    if (c + 1 < chunks) stash(buf ^ 1, r, t0 + (int64_t)(c + 1) * C_TOK + st_tok < t1);
-    __syncthreads();
+    __syncthreads();                       // chunk c done, chunk c + 1 staged
+  }
+  if (producer) {
+    gdn_store_chunk<C_ROWS>(lane, chunks - 1, t0, len, h, rg, s_out[(chunks - 1) & 1], out);
+    return;
   }
   __stcs(reinterpret_cast<float4*>(ns), make_float4(S[0], S[1], S[2], S[3]));
   __stcs(reinterpret_cast<float4*>(ns + 64), make_float4(S[4], S[5], S[6], S[7]));

@@ -396,7 +396,7 @@ def ops_table(peaks, calls=15, only=None):
             del a
 
     def _gdnp():
-        for lens in ([8192], [1024] * 8, [128] * 64):
+        for lens in ([8192], [4096] * 2, [1024] * 8, [128] * 64):
             a = W.make_gdn_prefill(lens, shape_id=len(lens), device="cuda")
             args = [a[k] for k in ("q", "k", "v", "state", "A_log", "a", "dt_bias", "b", "cu_seqlens")]
             us = time_calls_cold(lambda: gdn_prefill.run(*args, a["scale"]), max(5, calls // 3))
