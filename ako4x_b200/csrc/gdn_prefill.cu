@@ -13,7 +13,7 @@
 // that a fifth warp stages one chunk ahead (it also stores the finished chunk's outputs). The serial chain per token is one short dot product, three or four
 // shuffle levels and the update; measured about 270 cycles per token and 100 more per token of
 // chunk hand-over, so a single sequence of 8 192 tokens takes 1.5 ms. The chunked form of the
-// recurrence (gdn_prefill_chunk.cuh, fp32 on the CUDA cores) is used for a single sequence;
+// recurrence (gdn_prefill_chunk.cuh, fp32 on the CUDA cores) is used for one or two sequences;
 // a tensor-core form is not built. The state crosses HBM once each
 // way; outputs leave in 16- or 32-byte pieces per token and CTA. Processing two tokens per
 // reduction round (both products taken from the same state, the second delta corrected with
@@ -248,10 +248,10 @@ extern "C" int ako4x_gdn_prefill(const void* q, const void* k, const void* v, co
   if (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)out | (uintptr_t)state | (uintptr_t)new_state) & 15)
     return AKO4X_EINVAL;
   // The chunked form pays per 16 tokens what the token-by-token form pays per 4-5 tokens on its
-  // serial chain, but does more work per token in total and holds one CTA per SM (243 registers):
-  // it wins for a single sequence (8 192 tokens: 1.00 ms against 1.40 ms) and loses from two
-  // sequences on (2 x 4 096: 0.99 against 0.90 ms), so it is used for one sequence.
-  if (workspace != nullptr && num_seqs == 1) {
+  // serial chain, but does more work per token in total: it wins while SMs would otherwise idle.
+  // Measured, chunked against token by token: 1 x 8 192 tokens 1.00 against 1.40 ms, 2 x 4 096 0.79
+  // against 0.90, 4 x 2 048 0.80 against 0.74, 64 x 128 0.64 against 0.51: used for one or two sequences.
+  if (workspace != nullptr && num_seqs <= 2) {
     // chunked form: the token-only tables first, then 128 CTAs per sequence over 16-token chunks
     if (((uintptr_t)workspace & 15) || workspace_bytes < ako4x_gdn_prefill_workspace_bytes(total_tokens, num_seqs))
       return AKO4X_EWORKSPACE;
@@ -260,9 +260,15 @@ extern "C" int ako4x_gdn_prefill(const void* q, const void* k, const void* v, co
           (const __nv_bfloat16*)q, (const __nv_bfloat16*)k, cu_seqlens, (float*)workspace);
       AKO_CHECK_LAUNCH();
     }
-    gdn_prefill_chunk_kernel<<<dim3(P_D / C_ROWS, P_HV, (unsigned)num_seqs), P_THREADS, 0, (cudaStream_t)stream>>>(
-        (const __nv_bfloat16*)q, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, state, A_log, (const __nv_bfloat16*)a,
-        dt_bias, (const __nv_bfloat16*)b, cu_seqlens, scale, (__nv_bfloat16*)out, new_state, (const float*)workspace);
+    if (num_seqs == 1) {
+      gdn_prefill_chunk_kernel<false><<<dim3(P_D / C_ROWS, P_HV, 1), P_THREADS, 0, (cudaStream_t)stream>>>(
+          (const __nv_bfloat16*)q, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, state, A_log, (const __nv_bfloat16*)a,
+          dt_bias, (const __nv_bfloat16*)b, cu_seqlens, scale, (__nv_bfloat16*)out, new_state, (const float*)workspace);
+    } else {
+      gdn_prefill_chunk_kernel<true><<<dim3(P_D / C_ROWS, P_HV, (unsigned)num_seqs), P_THREADS, 0, (cudaStream_t)stream>>>(
+          (const __nv_bfloat16*)q, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, state, A_log, (const __nv_bfloat16*)a,
+          dt_bias, (const __nv_bfloat16*)b, cu_seqlens, scale, (__nv_bfloat16*)out, new_state, (const float*)workspace);
+    }
     AKO_CHECK_LAUNCH();
     return AKO4X_OK;
   }

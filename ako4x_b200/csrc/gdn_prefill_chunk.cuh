@@ -73,6 +73,10 @@ __global__ void __launch_bounds__(256) gdn_gram_kernel(const __nv_bfloat16* __re
 constexpr int C_ROWS = 8;                 // state rows per CTA: 4 warps x 2 groups of 16 lanes
 constexpr int C_TPAD = 20;                // padded row length of the tables in shared memory
 
+// LEAN: a scheduling fence every four tokens of the product loop keeps four tokens' loads in flight
+// instead of sixteen: 124 registers instead of 243, three CTAs per SM instead of one. One sequence
+// (128 CTAs) is faster without it, two sequences with it.
+template <bool LEAN>
 __global__ void __launch_bounds__(P_THREADS) gdn_prefill_chunk_kernel(
     const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ v,
     const float* __restrict__ state, const float* __restrict__ A_log, const __nv_bfloat16* __restrict__ a,
@@ -155,6 +159,7 @@ __global__ void __launch_bounds__(P_THREADS) gdn_prefill_chunk_kernel(
               fmaf(S[4], k1.x, fmaf(S[5], k1.y, fmaf(S[6], k1.z, S[7] * k1.w)));
       pc[j] = fmaf(S[0], q0.x, fmaf(S[1], q0.y, fmaf(S[2], q0.z, S[3] * q0.w))) +
               fmaf(S[4], q1.x, fmaf(S[5], q1.y, fmaf(S[6], q1.z, S[7] * q1.w)));
+      if (LEAN && (j & 3) == 3) asm volatile("" ::: "memory");
     }
     // 2. halving butterfly over the row's 16 lanes: lane i ends with the complete sums of token i
     float ai, ci;

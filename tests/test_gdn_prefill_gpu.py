@@ -44,9 +44,9 @@ def test_against_oracle(lens):
     _check(o, s, ro, rs)
 
 
-@pytest.mark.parametrize("lens", [[370], [33], [129], [16], [5]])
+@pytest.mark.parametrize("lens", [[370], [33], [129], [16], [5], [70, 300], [0, 33], [17, 0]])
 def test_both_forms_agree(lens):
-    """A single sequence runs in the chunked form (16 tokens per step of the state), several run
+    """One or two sequences run in the chunked form (16 tokens per step of the state), more run
     token by token; `_chunked=False` forces the latter. Both against the oracle and each other."""
     a = W.make_gdn_prefill(lens, shape_id=21 + len(lens))
     args = [a[k].cuda() if a[k] is not None else None for k in KEYS]
