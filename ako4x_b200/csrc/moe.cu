@@ -139,25 +139,27 @@ __global__ void __launch_bounds__(128) moe_routing_kernel(
     rank += (og > gscore || (og == gscore && gi < my_group)) ? 1 : 0;
   }
   const bool keep = rank < TOPK_G;
-  // top-8 by (biased score desc, index asc) among kept groups
+  // top-8 by (biased score desc, index asc) among kept groups. Per round every lane offers its best
+  // unselected value as an order-preserving 32-bit key; one warp-wide integer max finds the winning
+  // score and a ballot the lanes that hold it: the lowest such lane owns the lowest expert index
+  // (lanes are in expert order, and a lane offers its lowest index among equal values).
   unsigned selmask = 0;
   for (int round = 0; round < TOPK; ++round) {
-    float bv = -INFINITY;
-    int bi = 0x7fffffff;
+    float bv = 0.f;
+    int bj = -1;
     if (keep) {
 #pragma unroll
       for (int j = 0; j < 8; ++j) {  // ascending index, strict '>' : ties keep the lower index
-        if (!((selmask >> j) & 1u) && (bi == 0x7fffffff || sb[j] > bv)) { bv = sb[j]; bi = lane * 8 + j; }
+        if (!((selmask >> j) & 1u) && (bj < 0 || sb[j] > bv)) { bv = sb[j]; bj = j; }
       }
     }
-#pragma unroll
-    for (int off = 16; off >= 1; off >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, bv, off);
-      const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
-      const bool take = (oi != 0x7fffffff) && (bi == 0x7fffffff || ov > bv || (ov == bv && oi < bi));
-      if (take) { bv = ov; bi = oi; }
-    }
-    if ((bi >> 3) == lane) selmask |= 1u << (bi & 7);
+    // floats ordered as unsigned integers: flip all bits of negatives, the sign bit of the others;
+    // a lane with nothing to offer sends 0, below every real key
+    const unsigned bits = __float_as_uint(bv + 0.f);   // -0 and +0 compare equal: one key for both
+    const unsigned key = (bj < 0) ? 0u : ((bits & 0x80000000u) ? ~bits : (bits | 0x80000000u));
+    const unsigned best = __reduce_max_sync(0xffffffffu, key);
+    const unsigned holders = __ballot_sync(0xffffffffu, key == best && bj >= 0);
+    if (holders != 0u && lane == __ffs(holders) - 1) selmask |= 1u << bj;
   }
   // ascending-id positions and weights
   float ssum = 0.f;
