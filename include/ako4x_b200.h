@@ -317,9 +317,10 @@ int ako4x_gemm_device_status(void);
  * output taken after each update. An empty sequence gets a zero new_state (as the definition
  * does); tokens that belong to no sequence are not written.
  * With a workspace of ako4x_gdn_prefill_workspace_bytes(total_tokens, num_seqs) bytes (16-byte
- * aligned) the recurrence runs in chunks of 16 tokens (a kernel that tabulates k_i.k_j and q_i.k_j
- * per chunk, then the state kernel: only a 16-step substitution is serial per chunk); with a NULL
- * workspace it runs token by token in one launch. Same results up to fp32 rounding order. */
+ * aligned) calls with one or two sequences run the recurrence in chunks of 16 tokens (a kernel
+ * that tabulates k_i.k_j and q_i.k_j per chunk, then the state kernel: only a 16-step substitution
+ * is serial per chunk); with a NULL workspace, and from three sequences on, it runs token by token
+ * in one launch. Same results up to fp32 rounding order. */
 size_t ako4x_gdn_prefill_workspace_bytes(int64_t total_tokens, int64_t num_seqs);
 int ako4x_gdn_prefill(const void* q, const void* k, const void* v, const float* state,
                       const float* A_log, const void* a, const float* dt_bias, const void* b,
